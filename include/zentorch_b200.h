@@ -1,0 +1,183 @@
+/* C ABI of libzentorch_b200.so: the quantized-linear hot path of zentorch on NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*, i.e. a
+ * cudaStream_t; NULL is the legacy default stream).  Nothing here allocates device memory, nothing
+ * synchronises the host with the device, and every call may be captured in a CUDA graph unless its
+ * comment says otherwise.  Calls return ZT_SUCCESS or an error code; zt_last_error() gives the
+ * message of the last failure on the calling thread.  There is no CPU fallback: on a machine
+ * without an sm_100 GPU the compute entry points fail with ZT_CUDA_ERROR.
+ *
+ * Each declaration cites the reference interface it stands in for (paths are those of the
+ * amd/ZenDNN-pytorch-plugin tree).
+ */
+#ifndef ZENTORCH_B200_H_
+#define ZENTORCH_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ZT_API __attribute__((visibility("default")))
+
+typedef enum {
+  ZT_SUCCESS = 0,
+  ZT_INVALID_ARGUMENT = 1,
+  ZT_UNSUPPORTED = 2,
+  ZT_CUDA_ERROR = 3,
+  ZT_WORKSPACE_TOO_SMALL = 4,
+  ZT_DEVICE_TIMEOUT = 5 /* a bounded device-side wait expired; the context stays usable */
+} zt_status_t;
+
+typedef enum { ZT_BF16 = 0, ZT_F32 = 1 } zt_dtype_t;
+
+/* Post-op ids; same values as UNARY_POST_OP / BINARY_POST_OP in src/cpu/cpp/Utils.hpp:56-72. */
+typedef enum {
+  ZT_POST_NONE = 0,
+  ZT_POST_RELU = 1,
+  ZT_POST_GELU_TANH = 2,
+  ZT_POST_GELU_ERF = 3,
+  ZT_POST_SILU = 4,
+  ZT_POST_SIGMOID = 5,
+  ZT_POST_TANH = 6,
+  ZT_POST_MUL = 7,
+  ZT_POST_ADD = 8
+} zt_post_op_t;
+
+#define ZT_MAX_POST_OPS 4
+
+/* Ordered post-op chain applied to the fp32 result after the bias (matmul_post_ops,
+ * src/cpu/cpp/MatmulUtils.hpp:36-77).  MUL/ADD consume `buffers` in order; each buffer is a
+ * contiguous [M, N] array of the output dtype. */
+typedef struct {
+  int32_t n_ops;
+  int32_t ids[ZT_MAX_POST_OPS];
+  const void *buffers[ZT_MAX_POST_OPS];
+} zt_post_ops_t;
+
+/* Kernel selection.  AUTO picks by shape; the others force one kernel and fail with
+ * ZT_UNSUPPORTED when the shape does not fit it (used by tests and the benchmark). */
+typedef enum {
+  ZT_ALGO_AUTO = 0,
+  ZT_ALGO_GENERIC = 1, /* any shape, CUDA cores */
+  ZT_ALGO_SKINNY = 2,  /* small M, HBM-bound streaming kernel */
+  ZT_ALGO_TCGEN05 = 3  /* large M, tcgen05 tensor cores with TMEM accumulators */
+} zt_algo_t;
+
+ZT_API const char *zt_last_error(void);
+ZT_API const char *zt_version(void);
+/* 1 when the current CUDA device is compute capability 10.x, else 0 (replaces the AVX-512 gate
+ * is_avx512_supported, src/cpu/cpp/Utils.hpp:28-35). */
+ZT_API int zt_device_supported(void);
+/* Reads the device-side status word that a kernel sets when one of its bounded waits expires
+ * (0 = none; 101..104 name the waiting role).  Synchronises with the device; `reset` clears it.
+ * No counterpart in the reference (its failures are host exceptions, src/cpu/cpp/Utils.hpp:21-23). */
+ZT_API int zt_poll_device_status(int *status, int reset);
+
+/* ---------------------------------------------------------------------------------------------
+ * Weight-only int4 linear.   zentorch_woq_linear_impl, src/cpu/cpp/WOQ_Linear.cpp:14-176, and the
+ * eight op variants built on it (:178-292, :482-507).
+ *
+ *   Y[M,N] = post_ops( X[M,K] . dq(Wq)[K,N] + bias[N] )
+ *
+ * wq      int32 words, N-major: the nibble of logical element (k, n) is bits [4(k%8), 4(k%8)+4) of
+ *         word n*(K/8) + k/8.  This is the storage behind the op's weight argument of shape
+ *         [K/8, N] with strides (1, K/8)  (WOQ_Linear.cpp:138-146).
+ * scales  [n_groups, N] contiguous, fp32 or bf16; group size = K / n_groups (n_groups = 1 is
+ *         per-channel).
+ * zeros   NULL: nibbles are signed (-8..7) and dq = q*s.  Otherwise same shape/dtype as scales,
+ *         nibbles are unsigned (0..15) and dq = (q-8)*s + z  (WOQ_Linear.cpp:47-49).
+ * x, y    bf16, row-major, leading dimensions K and N.
+ * workspace  device scratch of at least zt_woq_linear_workspace_bytes(M,N,K) bytes.  Its first
+ *         ZT_WOQ_COUNTER_BYTES must be zero before the first call; every call leaves them zero.
+ *         Calls that share a workspace must be ordered on one stream.
+ */
+#define ZT_WOQ_COUNTER_BYTES 16384
+
+typedef struct {
+  const void *x;
+  int64_t M, K, N;
+  const int32_t *wq;
+  const void *scales;
+  const void *zeros;
+  int32_t scale_dtype; /* zt_dtype_t, also the dtype of zeros */
+  int64_t n_groups;
+  const void *bias; /* may be NULL */
+  int32_t bias_dtype;
+  zt_post_ops_t post;
+  void *y;
+  void *workspace;
+  size_t workspace_bytes;
+  int32_t algo; /* zt_algo_t */
+} zt_woq_linear_args_t;
+
+ZT_API size_t zt_woq_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
+ZT_API int zt_woq_linear(const zt_woq_linear_args_t *args, void *stream);
+
+/* zentorch_woq_repack_weight, src/cpu/cpp/WOQ_Linear.cpp:294-357: [N,K] int8 (one 4-bit value per
+ * byte) -> [N,K/8] int32.  K must be a positive multiple of 8. */
+ZT_API int zt_woq_repack_weight(const int8_t *unpacked, int64_t N, int64_t K, int32_t *packed, void *stream);
+
+/* zentorch_woq_repack_from_int4pack, src/cpu/cpp/WOQ_Linear.cpp:361-433: PyTorch CPU int4pack
+ * layout ([N, K/2] uint8 in 64-row blocks, device copy of it) -> [N,K/8] int32.  N % 64 == 0. */
+ZT_API int zt_woq_repack_from_int4pack(const uint8_t *int4pack, int64_t N, int64_t K_half, int32_t *packed,
+                                       void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Dynamic int8 linear.   zentorch_dynamic_qlinear(_impl), src/cpu/cpp/DynamicQLinear.cpp:74-181.
+ *
+ *   s_m = max(absmax_k |x[m,k]|, 1e-12) / 127 ;  q = clamp(rint(x / s_m), -128, 127)      (s8)
+ *   acc[m,n] = sum_k q[m,k] * W[n,k]  (int32) ;  Y = post_ops( acc * (s_m * w_n) + bias[n] )
+ *
+ * act_quant ZT_ACT_U8_ASYM (not in the reference op) quantises each row to unsigned 8 bit with a
+ * zero point and corrects the accumulator with zp_m * sum_k W[n,k]; it needs `w_rowsum`.
+ * Post-ops are likewise an extension: the reference op has none.
+ *
+ * x        [M,K] bf16 or fp32 row-major;  y has the same dtype, [M,N].
+ * w        [N,K] int8 row-major (nn.Linear layout).
+ * w_scales [N] fp32 or bf16.      bias [N] fp32 or bf16, may be NULL.
+ * workspace at least zt_dynamic_qlinear_workspace_bytes(M,K) bytes: holds the quantised
+ *          activations, their scales and zero points between the two kernels.
+ */
+typedef enum { ZT_ACT_S8_SYM = 0, ZT_ACT_U8_ASYM = 1 } zt_act_quant_t;
+
+typedef struct {
+  const void *x;
+  int32_t x_dtype;
+  int64_t M, K, N;
+  const int8_t *w;
+  const void *w_scales;
+  int32_t w_scale_dtype;
+  const void *bias;
+  int32_t bias_dtype;
+  int32_t act_quant;       /* zt_act_quant_t */
+  const int32_t *w_rowsum; /* [N], required for ZT_ACT_U8_ASYM (zt_int8_weight_rowsum) */
+  zt_post_ops_t post;
+  void *y;
+  void *workspace;
+  size_t workspace_bytes;
+  int32_t algo;
+} zt_dynamic_qlinear_args_t;
+
+ZT_API size_t zt_dynamic_qlinear_workspace_bytes(int64_t M, int64_t K);
+ZT_API int zt_dynamic_qlinear(const zt_dynamic_qlinear_args_t *args, void *stream);
+
+/* The first phase of zentorch_dynamic_qlinear on its own: per-row quantisation.  q is [M,K] int8
+ * (s8) or uint8 (u8); scales [M] fp32; zero_points [M] int32 (u8 mode only, else may be NULL). */
+ZT_API int zt_dynamic_quantize(const void *x, int32_t x_dtype, int64_t M, int64_t K, int32_t act_quant, void *q,
+                               float *scales, int32_t *zero_points, void *stream);
+
+/* The second phase without its epilogue: acc[M,N] = q[M,K] . W[N,K]^T in exact int32.  Exposed so
+ * that the accumulators can be compared bit for bit. */
+ZT_API int zt_int8_gemm_s32(const void *q, int32_t q_is_u8, const int8_t *w, int64_t M, int64_t N, int64_t K,
+                            int32_t *acc, int32_t algo, void *stream);
+
+/* rowsum[n] = sum_k W[n,k]; a one-off weight-prepack by-product used by ZT_ACT_U8_ASYM. */
+ZT_API int zt_int8_weight_rowsum(const int8_t *w, int64_t N, int64_t K, int32_t *rowsum, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZENTORCH_B200_H_ */

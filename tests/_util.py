@@ -1,0 +1,76 @@
+"""Helpers shared by the tests: seeded synthetic inputs of the benchmark configs, bf16 bit views,
+and the ctypes handle of the C oracle."""
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def bf16_from_bits(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(a)).view(torch.bfloat16)
+
+
+def load_c_oracle() -> C.CDLL:
+    so = ROOT / "oracle" / "_build" / "libzentorch_oracle.so"
+    src = ROOT / "oracle" / "zentorch_oracle.c"
+    if not so.exists() or so.stat().st_mtime < src.stat().st_mtime:
+        subprocess.run(["make", "-C", str(ROOT / "oracle")], check=True, capture_output=True)
+    lib = C.CDLL(str(so))
+    p, i64, i32 = C.c_void_p, C.c_int64, C.c_int
+    lib.zt_oracle_woq_repack_weight.argtypes = [p, i64, i64, p]
+    lib.zt_oracle_unpack_int4pack.argtypes = [p, i64, i64, p]
+    lib.zt_oracle_woq_linear.argtypes = [p, i64, i64, p, i64, p, p, i64, p, i32, p, p, i32, p, p]
+    lib.zt_oracle_dynamic_quantize_s8.argtypes = [p, i64, i64, p, p]
+    lib.zt_oracle_dynamic_quantize_u8.argtypes = [p, i64, i64, p, p, p]
+    lib.zt_oracle_int8_gemm.argtypes = [p, i32, p, i64, i64, i64, p]
+    lib.zt_oracle_qlinear_epilogue.argtypes = [p, i64, i64, p, p, p, p, p, i32, p]
+    return lib
+
+
+def make_woq_case(m, k, n, gs, seed=0, asym=False, scale_dtype=torch.float32, bias=True, x_shape=None):
+    """Synthetic WOQ linear of the benchmark configs: x ~ N(0,1) bf16, W ~ N(0,0.02) quantised per
+    group of gs along K (symmetric: s = max|w|/7; asymmetric: tinygemm min/max scheme), bias ~
+    N(0,0.01) bf16.  Returns CPU tensors: x, q [N,K] int8, scales [G,N], zeros or None, bias."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(*(x_shape or (m, k)), generator=g).to(torch.bfloat16)
+    w = torch.randn(n, k, generator=g) * 0.02
+    ng = k // gs
+    wg = w.view(n, ng, gs)
+    if not asym:
+        s = (wg.abs().amax(dim=2) / 7.0).clamp(min=1e-8)
+        q = torch.clamp(torch.round(wg / s.unsqueeze(2)), -8, 7).to(torch.int8).view(n, k)
+        scales, zeros = s.t().contiguous().to(scale_dtype), None
+    else:
+        mn, mx = wg.amin(dim=2), wg.amax(dim=2)
+        s = ((mx - mn) / 15.0).clamp(min=1e-6)
+        z = mn + s * 8.0
+        q = torch.clamp(torch.round((wg - mn.unsqueeze(2)) / s.unsqueeze(2)), 0, 15).to(torch.int8).view(n, k)
+        scales, zeros = s.t().contiguous().to(scale_dtype), z.t().contiguous().to(scale_dtype)
+    b = (torch.randn(n, generator=g) * 0.01).to(torch.bfloat16) if bias else None
+    return x, q, scales, zeros, b
+
+
+def make_int8_case(m, k, n, seed=0, x_dtype=torch.bfloat16, bias_dtype=torch.float32, bias=True):
+    """Synthetic dynamic-int8 linear: x ~ N(0,1), W ~ N(0,0.02) quantised per output channel
+    (s = max|w|/127), bias ~ N(0,0.01)."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(m, k, generator=g).to(x_dtype)
+    w = torch.randn(n, k, generator=g) * 0.02
+    s = (w.abs().amax(dim=1) / 127.0).clamp(min=1e-12)
+    q = torch.clamp(torch.round(w / s.unsqueeze(1)), -127, 127).to(torch.int8)
+    b = (torch.randn(n, generator=g) * 0.01).to(bias_dtype) if bias else None
+    return x, q, s, b
+
+
+def assert_close_bf16(actual, expected, rtol=1e-2, atol=1e-2, what=""):
+    """The stated tolerance for bf16 results: 1e-2 relative with an absolute floor of 1e-2."""
+    a, e = actual.float().cpu(), expected.float().cpu()
+    diff = (a - e).abs()
+    bound = atol + rtol * e.abs()
+    bad = diff > bound
+    assert not bad.any(), (f"{what}: {int(bad.sum())} of {a.numel()} elements off; max abs diff "
+                           f"{diff.max().item():.5f} at value {e.flatten()[diff.argmax()].item():.5f}")

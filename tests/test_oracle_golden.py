@@ -1,0 +1,182 @@
+"""The CPU oracle against the golden vectors made from the reference's own test utilities
+(tests/golden/make_golden.py), and the C restatement against the Python one."""
+import ctypes as C
+
+import numpy as np
+import torch
+
+import zentorch_oracle as O
+from _util import bf16_from_bits, make_woq_case, make_int8_case
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr())
+
+
+def test_repack_matches_reference_packer(golden):
+    for key in ("pack", "packu"):
+        w = torch.from_numpy(golden[f"{key}_in"])
+        expect = torch.from_numpy(golden[f"{key}_out"])
+        got = O.woq_repack_weight(w)
+        assert got.dtype == torch.int32 and torch.equal(got, expect)
+        # and unpacking the op-layout view gives the values back
+        back = O.woq_unpack(got.t(), signed=(key == "pack"))
+        assert torch.equal(back, w)
+
+
+def test_int4pack_unpack_matches_aten(golden):
+    packed = torch.from_numpy(golden["int4pack_packed"])
+    int_data = torch.from_numpy(golden["int4pack_int_data"])
+    assert torch.equal(O.unpack_int4pack_to_int8(packed), int_data)
+    assert torch.equal(O.woq_repack_from_int4pack(packed), O.woq_repack_weight(int_data))
+
+
+def test_asymmetric_linear_matches_native_int4_mm(golden):
+    x = bf16_from_bits(golden["asym_x"])
+    scale, zero = bf16_from_bits(golden["asym_scale"]), bf16_from_bits(golden["asym_zero"])
+    packed = O.woq_repack_from_int4pack(torch.from_numpy(golden["asym_int4pack"]))
+    y = O.woq_linear(x, packed.t(), scale, zero, None)
+    ref = bf16_from_bits(golden["asym_y"])
+    # the reference accepts rtol=0.1, atol=2.0 here; the oracle is far inside that
+    assert torch.allclose(y.float(), ref.float(), rtol=0.1, atol=2.0)
+    assert (y.float() - ref.float()).abs().max() < 0.05
+
+
+def test_symmetric_per_channel_matches_reference_formula(golden):
+    x = bf16_from_bits(golden["sym_x"])
+    q = torch.from_numpy(golden["sym_q"])
+    scale = torch.from_numpy(golden["sym_scale"])
+    bias = bf16_from_bits(golden["sym_bias"])
+    packed = O.woq_repack_weight(q)
+    y = O.woq_linear(x, packed.t(), scale, None, bias)
+    ref = bf16_from_bits(golden["sym_y"])
+    assert y.shape == ref.shape and y.dtype == torch.bfloat16
+    # reference tolerance: rtol = atol = 1e-3 (test_woq_linear.py:133-136) up to one bf16 rounding
+    close = torch.isclose(y.float(), ref.float(), rtol=1e-3, atol=1e-3)
+    one_ulp = (y.view(torch.int16).int() - ref.view(torch.int16).int()).abs() <= 1
+    assert (close | one_ulp).all()
+    assert close.float().mean() > 0.98
+    a1, a2 = bf16_from_bits(golden["sym_add1"]), bf16_from_bits(golden["sym_add2"])
+    cases = {
+        "gelu_tanh": ([O.POST_GELU_TANH], []), "gelu_erf": ([O.POST_GELU_ERF], []),
+        "add_add": ([O.POST_ADD, O.POST_ADD], [a1, a2]), "mul_add": ([O.POST_MUL, O.POST_ADD], [a1, a2]),
+    }
+    for name, (ops, bufs) in cases.items():
+        yf = O.woq_linear(x, packed.t(), scale, None, bias, ops, bufs)
+        reff = bf16_from_bits(golden[f"sym_y_{name}"])
+        # fused variants: rtol = atol = 1e-2 (test_woq_linear.py:163-165); the golden applies the
+        # post-op to an already rounded bf16 linear output, the oracle rounds once at the end
+        assert torch.allclose(yf.float(), reff.float(), rtol=1e-2, atol=6e-2), name
+
+
+def test_dynamic_qlinear_matches_reference_formula(golden):
+    x = torch.from_numpy(golden["dyn_x"])
+    w = torch.from_numpy(golden["dyn_w"])
+    ws, b = torch.from_numpy(golden["dyn_ws"]), torch.from_numpy(golden["dyn_b"])
+    y = O.dynamic_qlinear(x, w, ws.unsqueeze(0), b)
+    ref = torch.from_numpy(golden["dyn_y"])
+    assert y.shape == ref.shape
+    assert torch.allclose(y, ref, atol=1e-2, rtol=1e-2)      # test_dynamic_qlinear.py:102-103
+    assert torch.allclose(y, ref, atol=1e-3, rtol=1e-5)
+
+
+def test_error_messages_follow_the_reference():
+    import pytest
+    with pytest.raises(RuntimeError, match="K must be divisible by 8"):
+        O.woq_repack_weight(torch.zeros(4, 12, dtype=torch.int8))
+    with pytest.raises(RuntimeError, match="K must be at least 8"):
+        O.woq_repack_weight(torch.zeros(4, 4, dtype=torch.int8))
+    with pytest.raises(RuntimeError, match="must have dtype int8"):
+        O.woq_repack_weight(torch.zeros(4, 8, dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="multiple of 64"):
+        O.unpack_int4pack_to_int8(torch.zeros(32, 16, dtype=torch.uint8))
+    with pytest.raises(RuntimeError, match="weight must have dtype int32"):
+        O.woq_linear(torch.zeros(1, 8, dtype=torch.bfloat16), torch.zeros(1, 4, dtype=torch.int8), torch.ones(1, 4))
+    with pytest.raises(RuntimeError, match="input must be bfloat16 or float32"):
+        O.dynamic_qlinear(torch.zeros(2, 8, dtype=torch.float16), torch.zeros(4, 8, dtype=torch.int8), torch.ones(4))
+    with pytest.raises(RuntimeError, match="bias must be 1D with size N"):
+        O.dynamic_qlinear(torch.zeros(2, 8), torch.zeros(4, 8, dtype=torch.int8), torch.ones(4), torch.zeros(3))
+
+
+# ---- C restatement == Python restatement --------------------------------------------------------------
+def test_c_oracle_repack_and_unpack(c_oracle, golden):
+    w = torch.from_numpy(golden["pack_in"]).contiguous()
+    out = torch.empty(w.shape[0], w.shape[1] // 8, dtype=torch.int32)
+    assert c_oracle.zt_oracle_woq_repack_weight(_ptr(w), w.shape[0], w.shape[1], _ptr(out)) == 0
+    assert torch.equal(out, torch.from_numpy(golden["pack_out"]))
+    assert c_oracle.zt_oracle_woq_repack_weight(_ptr(w), w.shape[0], 12, _ptr(out)) == 1
+    packed = torch.from_numpy(golden["int4pack_packed"]).contiguous()
+    un = torch.empty(packed.shape[0], packed.shape[1] * 2, dtype=torch.int8)
+    assert c_oracle.zt_oracle_unpack_int4pack(_ptr(packed), packed.shape[0], packed.shape[1], _ptr(un)) == 0
+    assert torch.equal(un, torch.from_numpy(golden["int4pack_int_data"]))
+
+
+def test_c_oracle_woq_linear_equals_python(c_oracle):
+    for asym, gs, (m, k, n) in ((False, 128, (3, 256, 40)), (True, 64, (2, 128, 24)), (False, 256, (1, 256, 16))):
+        x, q, s, z, b = make_woq_case(m, k, n, gs, seed=7, asym=asym)
+        packed = O.woq_repack_weight(q)
+        add = torch.randn(m, n).to(torch.bfloat16)
+        ops = [O.POST_SILU, O.POST_ADD]
+        y_py = O.woq_linear(x, packed.t(), s, z, b, ops, [add])
+        y_c = torch.empty(m, n, dtype=torch.bfloat16)
+        bias_f = b.float().contiguous()
+        ids = (C.c_int * 2)(*ops)
+        bufs = (C.c_void_p * 1)(add.data_ptr())
+        rc = c_oracle.zt_oracle_woq_linear(_ptr(x), m, k, _ptr(packed), n, _ptr(s), _ptr(z) if z is not None else None,
+                                           s.shape[0], _ptr(bias_f), 2, ids, bufs, 1, None, _ptr(y_c))
+        assert rc == 0
+        ulp = (y_c.view(torch.int16).int() - y_py.view(torch.int16).int()).abs()
+        assert ulp.max() <= 1 and (ulp == 0).float().mean() > 0.99
+
+
+def test_c_oracle_dynamic_qlinear_equals_python(c_oracle):
+    x, w, ws, b = make_int8_case(9, 64, 20, seed=3, x_dtype=torch.float32)
+    q_py, s_py, _, acc_py, y_py = O.dynamic_qlinear(x, w, ws, b, return_parts=True)
+    q_c = torch.empty_like(q_py)
+    s_c = torch.empty_like(s_py)
+    c_oracle.zt_oracle_dynamic_quantize_s8(_ptr(x), 9, 64, _ptr(q_c), _ptr(s_c))
+    assert torch.equal(q_c, q_py) and torch.equal(s_c, s_py)
+    acc_c = torch.empty(9, 20, dtype=torch.int32)
+    c_oracle.zt_oracle_int8_gemm(_ptr(q_c), 0, _ptr(w), 9, 20, 64, _ptr(acc_c))
+    assert torch.equal(acc_c, acc_py)
+    y_c = torch.empty(9, 20)
+    c_oracle.zt_oracle_qlinear_epilogue(_ptr(acc_c), 9, 20, _ptr(s_c), _ptr(ws), _ptr(b), None, None, 0, _ptr(y_c))
+    assert torch.allclose(y_c, y_py, rtol=1e-6, atol=1e-6)
+    # unsigned mode
+    qu_py, su_py, zp_py, accu_py, yu_py = O.dynamic_qlinear(x, w, ws, b, act_quant="u8_asym",
+                                                           post_ops=[O.POST_SILU], return_parts=True)
+    qu_c, su_c, zp_c = torch.empty_like(qu_py), torch.empty_like(su_py), torch.empty_like(zp_py)
+    c_oracle.zt_oracle_dynamic_quantize_u8(_ptr(x), 9, 64, _ptr(qu_c), _ptr(su_c), _ptr(zp_c))
+    assert torch.equal(qu_c, qu_py) and torch.equal(su_c, su_py) and torch.equal(zp_c, zp_py)
+    accu_c = torch.empty(9, 20, dtype=torch.int32)
+    c_oracle.zt_oracle_int8_gemm(_ptr(qu_c), 1, _ptr(w), 9, 20, 64, _ptr(accu_c))
+    assert torch.equal(accu_c, accu_py)
+    wsum = w.int().sum(dim=1).to(torch.int32).contiguous()
+    c_oracle.zt_oracle_qlinear_epilogue(_ptr(accu_c), 9, 20, _ptr(su_c), _ptr(ws), _ptr(b), _ptr(zp_c), _ptr(wsum), 4,
+                                        _ptr(y_c))
+    assert torch.allclose(y_c, yu_py, rtol=1e-5, atol=1e-5)
+
+
+def test_u8_quantisation_reconstructs_input():
+    x = torch.randn(16, 256) * 3 + 1
+    q, s, zp = O.dynamic_quantize_u8(x)
+    rec = (q.float() - zp.unsqueeze(1).float()) * s.unsqueeze(1)
+    assert (rec - x).abs().max() <= s.max() * 0.5 + 1e-6
+    q8, s8 = O.dynamic_quantize_s8(x)
+    assert ((q8.float() * s8.unsqueeze(1)) - x).abs().max() <= s8.max() * 0.5 + 1e-6
+
+
+def test_tp_shards_recompose():
+    x, q, s, z, b = make_woq_case(4, 512, 64, 128, seed=11)
+    packed = O.woq_repack_weight(q).t()
+    full = O.woq_linear(x, packed, s, None, b, return_fp32=True)
+    for world in (2, 4):
+        cols = [O.woq_linear(x, *O.tp_shard_woq(packed, s, None, b, "column", r, world), return_fp32=True)
+                for r in range(world)]
+        assert torch.allclose(torch.cat(cols, dim=1), full, rtol=1e-5, atol=1e-5)
+        rows = []
+        for r in range(world):
+            w_r, s_r, _, b_r = O.tp_shard_woq(packed, s, None, b, "row", r, world)
+            k0, k1 = r * 512 // world, (r + 1) * 512 // world
+            rows.append(O.woq_linear(x[:, k0:k1].contiguous(), w_r, s_r, None, b_r, return_fp32=True))
+        assert torch.allclose(sum(rows), full, rtol=1e-4, atol=1e-4)

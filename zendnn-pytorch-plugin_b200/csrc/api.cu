@@ -1,0 +1,306 @@
+// Entry points of libzentorch_b200: argument validation, kernel selection, and the process-wide
+// pieces (error message, device status word, tensor-map encoder).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <cstdlib>
+#include <cstring>
+
+#include "int8.cuh"
+#include "tc05.cuh"
+#include "woq.cuh"
+
+namespace zt {
+
+__device__ int g_device_status = 0;
+
+int *device_status_ptr() {
+  static int *ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ptrs[dev]) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+    ptrs[dev] = reinterpret_cast<int *>(p);
+  }
+  return ptrs[dev];
+}
+
+namespace {
+thread_local char g_error[512] = "";
+}
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+  set_error("CUDA error in %s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+  return ZT_CUDA_ERROR;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+int validate_post_ops(const zt_post_ops_t &p) {
+  ZT_REQUIRE(p.n_ops >= 0 && p.n_ops <= ZT_MAX_POST_OPS, ZT_INVALID_ARGUMENT, "post-op count %d out of range [0, %d]",
+             p.n_ops, ZT_MAX_POST_OPS);
+  int b = 0;
+  for (int i = 0; i < p.n_ops; ++i) {
+    ZT_REQUIRE(p.ids[i] >= ZT_POST_NONE && p.ids[i] <= ZT_POST_ADD, ZT_INVALID_ARGUMENT, "unknown post-op id %d",
+               p.ids[i]);
+    if (p.ids[i] == ZT_POST_MUL || p.ids[i] == ZT_POST_ADD) {
+      ZT_REQUIRE(p.buffers[b] != nullptr, ZT_INVALID_ARGUMENT, "post-op %d needs a binary operand buffer", i);
+      ++b;
+    }
+  }
+  return ZT_SUCCESS;
+}
+
+int make_tensor_map_2d(CUtensorMap *out, const void *base, CUtensorMapDataType dtype, uint32_t elem_bytes,
+                       uint64_t inner, uint64_t rows, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows) {
+  static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  if (!encode) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+      set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+      return ZT_CUDA_ERROR;
+    }
+    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  }
+  const cuuint64_t dims[2] = {inner, rows};
+  const cuuint64_t strides[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {box_inner, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  (void)elem_bytes;
+  CUresult r = encode(out, dtype, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner %llu, rows %llu, pitch %llu, box %u x %u)", (int)r,
+              (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)pitch_bytes, box_inner, box_rows);
+    return ZT_CUDA_ERROR;
+  }
+  return ZT_SUCCESS;
+}
+
+namespace {
+
+bool valid_dtype(int d) { return d == ZT_BF16 || d == ZT_F32; }
+
+int env_int(const char *name, int dflt) {
+  const char *v = std::getenv(name);
+  return v && *v ? std::atoi(v) : dflt;
+}
+
+// Read-once 0/1 style switches, in the manner of the reference's EnvReader
+// (src/cpu/cpp/EnvReader.hpp:41-60).
+struct Env {
+  int woq_fold;        // ZENTORCH_B200_WOQ_FOLD: 1 = subtract the nibble bias on the step sums
+  int woq_skinny_max;  // ZENTORCH_B200_WOQ_SKINNY_MAX_M: largest M given to the streaming kernel
+  int int8_bn;         // ZENTORCH_B200_INT8_BN: force the int8 tensor-core tile width
+  Env() {
+    woq_fold = env_int("ZENTORCH_B200_WOQ_FOLD", 1);
+    woq_skinny_max = env_int("ZENTORCH_B200_WOQ_SKINNY_MAX_M", 64);
+    int8_bn = env_int("ZENTORCH_B200_INT8_BN", 0);
+  }
+};
+const Env &env() {
+  static Env e;
+  return e;
+}
+
+}  // namespace
+}  // namespace zt
+
+using namespace zt;
+
+extern "C" const char *zt_last_error(void) { return g_error; }
+extern "C" const char *zt_version(void) { return "zentorch_b200 0.1 (sm_100a)"; }
+
+extern "C" int zt_device_supported(void) {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return 0;
+  return major == 10 ? 1 : 0;
+}
+
+extern "C" int zt_poll_device_status(int *status, int reset) {
+  ZT_REQUIRE(status != nullptr, ZT_INVALID_ARGUMENT, "zt_poll_device_status: null pointer");
+  ZT_CUDA_OK(cudaMemcpyFromSymbol(status, g_device_status, sizeof(int)));
+  if (reset && *status != 0) {
+    const int zero = 0;
+    ZT_CUDA_OK(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+  }
+  return ZT_SUCCESS;
+}
+
+// ---- weight-only int4 ---------------------------------------------------------------------------
+extern "C" size_t zt_woq_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return ZT_WOQ_COUNTER_BYTES;
+  const WoqSkinnyPlan pl = woq_skinny_plan(M, N, K);
+  return ZT_WOQ_COUNTER_BYTES + pl.partial_bytes;
+}
+
+extern "C" int zt_woq_linear(const zt_woq_linear_args_t *a, void *stream) {
+  ZT_REQUIRE(a != nullptr, ZT_INVALID_ARGUMENT, "zt_woq_linear: null argument block");
+  ZT_REQUIRE(a->M >= 0 && a->N >= 0 && a->K >= 0, ZT_INVALID_ARGUMENT, "zt_woq_linear: negative size");
+  ZT_REQUIRE(a->K % 8 == 0, ZT_INVALID_ARGUMENT, "K must be divisible by 8, got %lld", (long long)a->K);
+  if (a->M == 0 || a->N == 0) return ZT_SUCCESS;
+  ZT_REQUIRE(a->K >= 8, ZT_INVALID_ARGUMENT, "K must be at least 8, got %lld", (long long)a->K);
+  ZT_REQUIRE(a->x && a->wq && a->scales && a->y, ZT_INVALID_ARGUMENT, "zt_woq_linear: null tensor pointer");
+  ZT_REQUIRE(a->n_groups >= 1 && a->K % a->n_groups == 0, ZT_INVALID_ARGUMENT,
+             "zt_woq_linear: K (%lld) must be divisible by the number of scale groups (%lld)", (long long)a->K,
+             (long long)a->n_groups);
+  ZT_REQUIRE(valid_dtype(a->scale_dtype), ZT_INVALID_ARGUMENT, "zt_woq_linear: weight_scales must be float32 or bfloat16");
+  ZT_REQUIRE(!a->bias || valid_dtype(a->bias_dtype), ZT_INVALID_ARGUMENT, "zt_woq_linear: bias must be float32 or bfloat16");
+  int rc = validate_post_ops(a->post);
+  if (rc != ZT_SUCCESS) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+
+  int algo = a->algo;
+  if (algo == ZT_ALGO_AUTO) {
+    if (a->M <= env().woq_skinny_max && woq_skinny_supported(*a))
+      algo = ZT_ALGO_SKINNY;
+    else if (woq_tcgen05_supported(*a))
+      algo = ZT_ALGO_TCGEN05;
+    else if (woq_skinny_supported(*a) && a->M <= 256)
+      algo = ZT_ALGO_SKINNY;
+    else
+      algo = ZT_ALGO_GENERIC;
+  }
+  switch (algo) {
+    case ZT_ALGO_GENERIC: return woq_generic_launch(*a, st);
+    case ZT_ALGO_SKINNY:
+      ZT_REQUIRE(woq_skinny_supported(*a), ZT_UNSUPPORTED,
+                 "zt_woq_linear: the streaming kernel needs K and the group size to be multiples of 128 and 16-byte "
+                 "aligned x / weight");
+      return woq_skinny_launch(*a, env().woq_fold != 0, st);
+    case ZT_ALGO_TCGEN05:
+      ZT_REQUIRE(woq_tcgen05_supported(*a), ZT_UNSUPPORTED, "zt_woq_linear: shape not supported by the tcgen05 kernel");
+      return woq_tcgen05_launch(*a, st);
+    default: break;
+  }
+  set_error("zt_woq_linear: unknown algo %d", a->algo);
+  return ZT_INVALID_ARGUMENT;
+}
+
+// ---- dynamic int8 -------------------------------------------------------------------------------
+namespace {
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+}
+
+extern "C" size_t zt_dynamic_qlinear_workspace_bytes(int64_t M, int64_t K) {
+  if (M <= 0 || K <= 0) return 256;
+  return align_up((size_t)M * K, 256) + 2 * align_up((size_t)M * 4, 256);
+}
+
+extern "C" int zt_dynamic_quantize(const void *x, int32_t x_dtype, int64_t M, int64_t K, int32_t act_quant, void *q,
+                                   float *scales, int32_t *zero_points, void *stream) {
+  ZT_REQUIRE(M >= 0 && K >= 0, ZT_INVALID_ARGUMENT, "zt_dynamic_quantize: negative size");
+  if (M == 0 || K == 0) return ZT_SUCCESS;
+  ZT_REQUIRE(x && q && scales, ZT_INVALID_ARGUMENT, "zt_dynamic_quantize: null pointer");
+  ZT_REQUIRE(valid_dtype(x_dtype), ZT_INVALID_ARGUMENT, "zentorch_dynamic_qlinear: input must be bfloat16 or float32");
+  ZT_REQUIRE(act_quant == ZT_ACT_S8_SYM || act_quant == ZT_ACT_U8_ASYM, ZT_INVALID_ARGUMENT,
+             "zt_dynamic_quantize: unknown activation quantisation mode %d", act_quant);
+  ZT_REQUIRE(act_quant == ZT_ACT_S8_SYM || zero_points, ZT_INVALID_ARGUMENT,
+             "zt_dynamic_quantize: the u8 mode needs a zero-point output");
+  return dynamic_quantize_launch(x, x_dtype, M, K, act_quant, q, scales, zero_points, (cudaStream_t)stream);
+}
+
+namespace {
+int run_int8_gemm(Int8GemmArgs &g, int algo, cudaStream_t st) {
+  if (algo == ZT_ALGO_AUTO || algo == ZT_ALGO_SKINNY)
+    algo = int8_tcgen05_supported(g.M, g.N, g.K, g.q, g.w) ? ZT_ALGO_TCGEN05 : ZT_ALGO_GENERIC;
+  if (algo == ZT_ALGO_TCGEN05) {
+    ZT_REQUIRE(int8_tcgen05_supported(g.M, g.N, g.K, g.q, g.w), ZT_UNSUPPORTED,
+               "int8 tcgen05 kernel needs K %% 16 == 0 and 16-byte aligned operands");
+    g.force_bn = env().int8_bn;
+    return int8_tcgen05_launch(g, st);
+  }
+  if (algo == ZT_ALGO_GENERIC) return int8_generic_launch(g, st);
+  set_error("int8 gemm: unknown algo %d", algo);
+  return ZT_INVALID_ARGUMENT;
+}
+}  // namespace
+
+extern "C" int zt_int8_gemm_s32(const void *q, int32_t q_is_u8, const int8_t *w, int64_t M, int64_t N, int64_t K,
+                                int32_t *acc, int32_t algo, void *stream) {
+  ZT_REQUIRE(M >= 0 && N >= 0 && K >= 0, ZT_INVALID_ARGUMENT, "zt_int8_gemm_s32: negative size");
+  if (M == 0 || N == 0) return ZT_SUCCESS;
+  ZT_REQUIRE(q && w && acc, ZT_INVALID_ARGUMENT, "zt_int8_gemm_s32: null pointer");
+  Int8GemmArgs g{};
+  g.q = q;
+  g.q_is_u8 = q_is_u8 != 0;
+  g.w = w;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.raw_s32 = true;
+  g.y = acc;
+  return run_int8_gemm(g, algo, (cudaStream_t)stream);
+}
+
+extern "C" int zt_dynamic_qlinear(const zt_dynamic_qlinear_args_t *a, void *stream) {
+  ZT_REQUIRE(a != nullptr, ZT_INVALID_ARGUMENT, "zt_dynamic_qlinear: null argument block");
+  ZT_REQUIRE(a->M >= 0 && a->N >= 0 && a->K >= 0, ZT_INVALID_ARGUMENT, "zt_dynamic_qlinear: negative size");
+  ZT_REQUIRE(valid_dtype(a->x_dtype), ZT_INVALID_ARGUMENT, "zentorch_dynamic_qlinear: input must be bfloat16 or float32");
+  ZT_REQUIRE(valid_dtype(a->w_scale_dtype), ZT_INVALID_ARGUMENT,
+             "zentorch_dynamic_qlinear: weight_scales must be float32, bfloat16");
+  ZT_REQUIRE(!a->bias || valid_dtype(a->bias_dtype), ZT_INVALID_ARGUMENT,
+             "zentorch_dynamic_qlinear: bias must be float32 or bfloat16");
+  ZT_REQUIRE(a->act_quant == ZT_ACT_S8_SYM || a->act_quant == ZT_ACT_U8_ASYM, ZT_INVALID_ARGUMENT,
+             "zt_dynamic_qlinear: unknown activation quantisation mode %d", a->act_quant);
+  if (a->M == 0 || a->N == 0) return ZT_SUCCESS;
+  ZT_REQUIRE(a->K >= 1, ZT_INVALID_ARGUMENT, "zt_dynamic_qlinear: K must be positive");
+  ZT_REQUIRE(a->x && a->w && a->w_scales && a->y, ZT_INVALID_ARGUMENT, "zt_dynamic_qlinear: null tensor pointer");
+  ZT_REQUIRE(a->act_quant == ZT_ACT_S8_SYM || a->w_rowsum, ZT_INVALID_ARGUMENT,
+             "zt_dynamic_qlinear: the u8 mode needs w_rowsum (zt_int8_weight_rowsum)");
+  int rc = validate_post_ops(a->post);
+  if (rc != ZT_SUCCESS) return rc;
+  const size_t need = zt_dynamic_qlinear_workspace_bytes(a->M, a->K);
+  ZT_REQUIRE(a->workspace && a->workspace_bytes >= need, ZT_WORKSPACE_TOO_SMALL,
+             "zt_dynamic_qlinear: workspace of %zu bytes is smaller than the %zu required", a->workspace_bytes, need);
+  ZT_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, ZT_INVALID_ARGUMENT,
+             "zt_dynamic_qlinear: workspace must be 256-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  char *ws = reinterpret_cast<char *>(a->workspace);
+  void *q = ws;
+  float *scales = reinterpret_cast<float *>(ws + align_up((size_t)a->M * a->K, 256));
+  int32_t *zps = reinterpret_cast<int32_t *>(reinterpret_cast<char *>(scales) + align_up((size_t)a->M * 4, 256));
+  const bool u8 = a->act_quant == ZT_ACT_U8_ASYM;
+  rc = dynamic_quantize_launch(a->x, a->x_dtype, a->M, a->K, a->act_quant, q, scales, zps, st);
+  if (rc != ZT_SUCCESS) return rc;
+  Int8GemmArgs g{};
+  g.q = q;
+  g.q_is_u8 = u8;
+  g.w = a->w;
+  g.M = a->M;
+  g.N = a->N;
+  g.K = a->K;
+  g.raw_s32 = false;
+  g.src_scale = scales;
+  g.src_zp = u8 ? zps : nullptr;
+  g.w_scale = a->w_scales;
+  g.w_scale_dtype = a->w_scale_dtype;
+  g.w_rowsum = u8 ? a->w_rowsum : nullptr;
+  g.bias = a->bias;
+  g.bias_dtype = a->bias_dtype;
+  g.y_dtype = a->x_dtype;
+  g.y = a->y;
+  g.post = to_dev(a->post);
+  return run_int8_gemm(g, a->algo, st);
+}

@@ -1,0 +1,126 @@
+// Shared helpers for the sm_100a kernels of libzentorch_b200: error reporting, dtype access,
+// the post-op chain evaluated in the epilogue of every linear, and small PTX wrappers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/zentorch_b200.h"
+
+namespace zt {
+
+// ---- host-side error plumbing -----------------------------------------------------------------
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+
+#define ZT_REQUIRE(cond, code, ...)  \
+  do {                               \
+    if (!(cond)) {                   \
+      ::zt::set_error(__VA_ARGS__);  \
+      return (code);                 \
+    }                                \
+  } while (0)
+
+#define ZT_CUDA_OK(expr)                                        \
+  do {                                                          \
+    cudaError_t e__ = (expr);                                   \
+    if (e__ != cudaSuccess) return ::zt::cuda_fail(e__, #expr); \
+  } while (0)
+
+inline int launch_status(const char *kernel) {
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return cuda_fail(cudaGetLastError(), kernel);
+  return ZT_SUCCESS;
+}
+
+int sm_count();
+
+// ---- post-op chain ----------------------------------------------------------------------------
+struct PostOpsDev {
+  int n_ops;
+  int ids[ZT_MAX_POST_OPS];
+  const void *bufs[ZT_MAX_POST_OPS];
+};
+
+inline PostOpsDev to_dev(const zt_post_ops_t &p) {
+  PostOpsDev d{};
+  d.n_ops = p.n_ops;
+  for (int i = 0; i < ZT_MAX_POST_OPS; ++i) {
+    d.ids[i] = p.ids[i];
+    d.bufs[i] = p.buffers[i];
+  }
+  return d;
+}
+
+int validate_post_ops(const zt_post_ops_t &p);
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t h) { return __uint_as_float(((uint32_t)h) << 16); }
+
+__device__ __forceinline__ float load_as_float(const void *p, int64_t i, int dtype) {
+  if (dtype == ZT_F32) return reinterpret_cast<const float *>(p)[i];
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
+}
+
+__device__ __forceinline__ void store_from_float(void *p, int64_t i, int dtype, float v) {
+  if (dtype == ZT_F32)
+    reinterpret_cast<float *>(p)[i] = v;
+  else
+    reinterpret_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float unary_post(float y, int id) {
+  switch (id) {
+    case ZT_POST_RELU: return fmaxf(y, 0.f);
+    case ZT_POST_GELU_TANH: {
+      const float c = 0.7978845608028654f;
+      return 0.5f * y * (1.f + tanhf(c * (y + 0.044715f * y * y * y)));
+    }
+    case ZT_POST_GELU_ERF: return 0.5f * y * (1.f + erff(y * 0.7071067811865476f));
+    case ZT_POST_SILU: return y / (1.f + __expf(-y));
+    case ZT_POST_SIGMOID: return 1.f / (1.f + __expf(-y));
+    case ZT_POST_TANH: return tanhf(y);
+    default: return y;
+  }
+}
+
+// Applies the chain to one fp32 value; `idx` addresses the binary operands ([M,N] row-major, of
+// dtype `buf_dtype`).
+__device__ __forceinline__ float apply_post_ops(float y, const PostOpsDev &p, int64_t idx, int buf_dtype) {
+  int b = 0;
+#pragma unroll
+  for (int i = 0; i < ZT_MAX_POST_OPS; ++i) {
+    if (i < p.n_ops) {
+      const int id = p.ids[i];
+      if (id == ZT_POST_MUL) {
+        y *= load_as_float(p.bufs[b++], idx, buf_dtype);
+      } else if (id == ZT_POST_ADD) {
+        y += load_as_float(p.bufs[b++], idx, buf_dtype);
+      } else {
+        y = unary_post(y, id);
+      }
+    }
+  }
+  return y;
+}
+
+// ---- small PTX wrappers -----------------------------------------------------------------------
+__device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+template <typename T>
+__host__ __device__ constexpr T ceil_div(T a, T b) {
+  return (a + b - 1) / b;
+}
+
+}  // namespace zt

@@ -1,0 +1,205 @@
+// Per-token dynamic quantisation of activations: the first phase of zentorch_dynamic_qlinear.
+//
+// One CTA per row.  The row is read once into registers (up to 32 values per thread; longer rows
+// re-read the tail, which then comes from L2), reduced to its absolute maximum (s8) or min/max (u8)
+// with warp shuffles, and written back as 8-bit values with 8-byte stores.  The scale uses IEEE
+// division and the quantised value round-half-even, so the bytes equal those of the CPU formula
+//   s = max(absmax, 1e-12) / 127,   q = clamp(rint(x / s), -128, 127).
+#include "int8.cuh"
+
+namespace zt {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kVec = 8;        // elements per thread per chunk
+constexpr int kCached = 4;     // chunks kept in registers
+
+__device__ __forceinline__ void load8(const void *x, int dtype, int64_t off, float (&v)[8]) {
+  if (dtype == ZT_BF16) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(x) + off);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  } else {
+    const float4 a = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + off);
+    const float4 b = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + off + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+}
+
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float *scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, other) : fminf(v, other);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float r = lane < kThreads / 32 ? scratch[lane] : scratch[0];
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, r, o);
+      r = is_max ? fmaxf(r, other) : fminf(r, other);
+    }
+    if (lane == 0) scratch[8] = r;
+  }
+  __syncthreads();
+  const float out = scratch[8];
+  __syncthreads();
+  return out;
+}
+
+template <bool U8>
+__device__ __forceinline__ uint32_t quant_one(float x, float s, float zp) {
+  const float r = rintf(__fdiv_rn(x, s));
+  if (U8) {
+    const float v = fminf(fmaxf(r + zp, 0.f), 255.f);
+    return (uint32_t)(int)v;
+  }
+  const float v = fminf(fmaxf(r, -128.f), 127.f);
+  return (uint32_t)((int)v) & 0xffu;
+}
+
+// Vector path: K % 8 == 0 and 16-byte aligned rows.
+template <bool U8>
+__global__ void __launch_bounds__(kThreads) dynquant_vec_kernel(const void *__restrict__ x, int x_dtype, int64_t K,
+                                                                uint8_t *__restrict__ q, float *__restrict__ scales,
+                                                                int32_t *__restrict__ zps) {
+  __shared__ float scratch[16];
+  const int64_t row = blockIdx.x;
+  const int64_t base = row * K;
+  const int64_t chunks = K / kVec;
+  float v[kCached][8];
+  float hi = 0.f, lo = 0.f;  // u8: max(x,0), min(x,0); s8: hi = absmax
+#pragma unroll
+  for (int c = 0; c < kCached; ++c) {
+    const int64_t ch = (int64_t)c * kThreads + threadIdx.x;
+    if (ch < chunks) {
+      load8(x, x_dtype, base + ch * kVec, v[c]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (U8) {
+          hi = fmaxf(hi, v[c][i]);
+          lo = fminf(lo, v[c][i]);
+        } else {
+          hi = fmaxf(hi, fabsf(v[c][i]));
+        }
+      }
+    }
+  }
+  for (int64_t ch = (int64_t)kCached * kThreads + threadIdx.x; ch < chunks; ch += kThreads) {
+    float t[8];
+    load8(x, x_dtype, base + ch * kVec, t);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (U8) {
+        hi = fmaxf(hi, t[i]);
+        lo = fminf(lo, t[i]);
+      } else {
+        hi = fmaxf(hi, fabsf(t[i]));
+      }
+    }
+  }
+  hi = block_reduce(hi, true, scratch);
+  float s, zp = 0.f;
+  if (U8) {
+    lo = block_reduce(lo, false, scratch);
+    s = __fdiv_rn(fmaxf(hi - lo, 1e-12f), 255.0f);
+    zp = fminf(fmaxf(rintf(__fdiv_rn(-lo, s)), 0.f), 255.f);
+  } else {
+    s = __fdiv_rn(fmaxf(hi, 1e-12f), 127.0f);
+  }
+  if (threadIdx.x == 0) {
+    scales[row] = s;
+    if (U8 && zps) zps[row] = (int32_t)zp;
+  }
+  auto emit = [&](const float(&t)[8], int64_t ch) {
+    uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      w0 |= quant_one<U8>(t[i], s, zp) << (8 * i);
+      w1 |= quant_one<U8>(t[4 + i], s, zp) << (8 * i);
+    }
+    *reinterpret_cast<uint2 *>(q + base + ch * kVec) = make_uint2(w0, w1);
+  };
+#pragma unroll
+  for (int c = 0; c < kCached; ++c) {
+    const int64_t ch = (int64_t)c * kThreads + threadIdx.x;
+    if (ch < chunks) emit(v[c], ch);
+  }
+  for (int64_t ch = (int64_t)kCached * kThreads + threadIdx.x; ch < chunks; ch += kThreads) {
+    float t[8];
+    load8(x, x_dtype, base + ch * kVec, t);
+    emit(t, ch);
+  }
+}
+
+// Any K, any alignment.
+template <bool U8>
+__global__ void __launch_bounds__(kThreads) dynquant_scalar_kernel(const void *__restrict__ x, int x_dtype, int64_t K,
+                                                                   uint8_t *__restrict__ q, float *__restrict__ scales,
+                                                                   int32_t *__restrict__ zps) {
+  __shared__ float scratch[16];
+  const int64_t row = blockIdx.x;
+  const int64_t base = row * K;
+  float hi = 0.f, lo = 0.f;
+  for (int64_t k = threadIdx.x; k < K; k += kThreads) {
+    const float t = load_as_float(x, base + k, x_dtype);
+    if (U8) {
+      hi = fmaxf(hi, t);
+      lo = fminf(lo, t);
+    } else {
+      hi = fmaxf(hi, fabsf(t));
+    }
+  }
+  hi = block_reduce(hi, true, scratch);
+  float s, zp = 0.f;
+  if (U8) {
+    lo = block_reduce(lo, false, scratch);
+    s = __fdiv_rn(fmaxf(hi - lo, 1e-12f), 255.0f);
+    zp = fminf(fmaxf(rintf(__fdiv_rn(-lo, s)), 0.f), 255.f);
+  } else {
+    s = __fdiv_rn(fmaxf(hi, 1e-12f), 127.0f);
+  }
+  if (threadIdx.x == 0) {
+    scales[row] = s;
+    if (U8 && zps) zps[row] = (int32_t)zp;
+  }
+  for (int64_t k = threadIdx.x; k < K; k += kThreads)
+    q[base + k] = (uint8_t)quant_one<U8>(load_as_float(x, base + k, x_dtype), s, zp);
+}
+
+}  // namespace
+
+int dynamic_quantize_launch(const void *x, int x_dtype, int64_t M, int64_t K, int act_quant, void *q, float *scales,
+                            int32_t *zps, cudaStream_t st) {
+  if (M == 0 || K == 0) return ZT_SUCCESS;
+  ZT_REQUIRE(M <= 0x7fffffffLL, ZT_UNSUPPORTED, "zt_dynamic_quantize: M = %lld exceeds the grid limit", (long long)M);
+  const bool u8 = act_quant == ZT_ACT_U8_ASYM;
+  const size_t esz = x_dtype == ZT_BF16 ? 2 : 4;
+  const bool vec = (K % kVec == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((K * esz) % 16 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
+  uint8_t *qq = reinterpret_cast<uint8_t *>(q);
+  const dim3 grid((unsigned)M);
+  if (vec) {
+    if (u8)
+      dynquant_vec_kernel<true><<<grid, kThreads, 0, st>>>(x, x_dtype, K, qq, scales, zps);
+    else
+      dynquant_vec_kernel<false><<<grid, kThreads, 0, st>>>(x, x_dtype, K, qq, scales, zps);
+  } else {
+    if (u8)
+      dynquant_scalar_kernel<true><<<grid, kThreads, 0, st>>>(x, x_dtype, K, qq, scales, zps);
+    else
+      dynquant_scalar_kernel<false><<<grid, kThreads, 0, st>>>(x, x_dtype, K, qq, scales, zps);
+  }
+  return launch_status("dynquant_kernel");
+}
+
+}  // namespace zt

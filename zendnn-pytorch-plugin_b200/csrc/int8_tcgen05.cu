@@ -1,0 +1,377 @@
+// int8 x int8 -> int32 GEMM on tcgen05 tensor cores with the dynamic-qlinear epilogue fused.
+//
+//   acc[M,N] = Q[M,K] . W[N,K]^T          (Q: per-token quantised activations, s8 or u8; W: s8)
+//   Y = post_ops( (acc - zp_m * wsum_n) * (s_m * w_n) + bias_n )
+//
+// Both operands are K-major, so they go from global memory to shared memory with plain 2-D TMA tile
+// loads (128 bytes of K per row, 128-byte swizzle) and are consumed in place by
+// tcgen05.mma.kind::i8 (K = 32 per instruction, four per 128-byte k-block).  The int32 accumulator
+// tile of 128 x BN lives in tensor memory.  One CTA computes one 128 x BN output tile:
+//
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      allocates tensor memory, issues the MMAs (one elected lane), frees tensor memory
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (lane == output row), scale, bias, post-op,
+//               cast, 16-byte stores
+//
+// Shared-memory stages are recycled through full/empty mbarriers; tcgen05.commit releases a stage
+// when the MMAs that read it have finished.  Two CTAs fit on one SM (shared memory and tensor-memory
+// columns are sized for that), so one CTA's epilogue overlaps the other's main loop.
+#include <mutex>
+#include <unordered_map>
+
+#include "int8.cuh"
+#include "tc05.cuh"
+
+namespace zt {
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 128;  // bytes (= int8 elements) of K per stage
+constexpr int kThreads = 192;
+
+enum EpiMode { kEpiS32 = 0, kEpiLinear = 1 };
+
+struct TcParams {
+  int M, N, K;
+  // epilogue
+  const float *src_scale;  // [M]
+  const int32_t *src_zp;   // [M] or null
+  const void *w_scale;     // [N]
+  const int32_t *w_rowsum; // [N] or null
+  const void *bias;        // [N] or null
+  int w_scale_dtype, bias_dtype, y_dtype;
+  void *y;                 // [M,N] (y_dtype) or int32 for kEpiS32
+  PostOpsDev post;
+  int *status;             // device status word (bounded-wait failures)
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int kABytes = kBM * kBK;
+  static constexpr int kBBytes = BN * kBK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTileBytes = STAGES * kStageBytes;
+  static constexpr int kVecBytes = 3 * BN * 4;          // w_scale, bias, rowsum of the tile
+  static constexpr int kBarBytes = (2 * STAGES + 1) * 8 + 8;
+  static constexpr int kTotal = kTileBytes + kVecBytes + kBarBytes + 1024;  // + slack to align to 1024
+};
+
+template <int BN, int STAGES, int EPI, bool A_SIGNED>
+__global__ void __launch_bounds__(kThreads) int8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                const __grid_constant__ CUtensorMap tmap_b,
+                                                                const TcParams p) {
+  using L = SmemLayout<BN, STAGES>;
+  extern __shared__ unsigned char smem_dyn[];
+  // align on the shared-window address (what the descriptors and TMA see), not the generic one
+  unsigned char *smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+  float *s_wscale = reinterpret_cast<float *>(smem + L::kTileBytes);
+  float *s_bias = s_wscale + BN;
+  int32_t *s_rowsum = reinterpret_cast<int32_t *>(s_bias + BN);
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + L::kTileBytes + L::kVecBytes);
+  uint64_t *empty_bar = full_bar + STAGES;
+  uint64_t *accum_bar = empty_bar + STAGES;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum_bar + 1);
+
+  constexpr uint32_t kTmemCols = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * kBM;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    tc::prefetch_tensormap(&tmap_a);
+    tc::prefetch_tensormap(&tmap_b);
+    for (int s = 0; s < STAGES; ++s) {
+      tc::mbar_init(&full_bar[s], 1);
+      tc::mbar_init(&empty_bar[s], 1);
+    }
+    tc::mbar_init(accum_bar, 1);
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) tc::tmem_alloc(tmem_slot, kTmemCols);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
+          tc::report_timeout(p.status, kStatusProducerTimeout);
+          break;
+        }
+        unsigned char *a_dst = smem + s * L::kStageBytes;
+        unsigned char *b_dst = a_dst + L::kABytes;
+        tc::mbar_expect_tx(&full_bar[s], L::kStageBytes);
+        tc::tma_load_2d(a_dst, &tmap_a, &full_bar[s], kb * kBK, m0);
+        tc::tma_load_2d(b_dst, &tmap_b, &full_bar[s], kb * kBK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::instr_desc(2u, A_SIGNED ? 1u : 0u, 1u, kBM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        if (!tc::mbar_wait(&full_bar[s], ph)) {
+          tc::report_timeout(p.status, kStatusMmaTimeout);
+          ok = false;
+          break;
+        }
+        tc::fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * L::kStageBytes);
+        const uint64_t a_desc = tc::smem_desc_k_sw128(a_addr);
+        const uint64_t b_desc = tc::smem_desc_k_sw128(a_addr + L::kABytes);
+#pragma unroll
+        for (int k = 0; k < kBK / 32; ++k) {
+          // 32 bytes of K per instruction: advance both start addresses by 32 >> 4 = 2
+          tc::mma_i8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        tc::mma_commit(&empty_bar[s]);
+      }
+      // Arrive on the accumulator barrier in every case so that the epilogue never waits for a
+      // commit that will not come; after a timeout the result is garbage but the kernel ends.
+      tc::mma_commit(accum_bar);
+    }
+  } else {
+    // ---------------- epilogue warps (2..5) ----------------
+    const int et = threadIdx.x - 64;  // 0..127
+    if (EPI == kEpiLinear) {
+      for (int j = et; j < BN; j += 128) {
+        const int n = n0 + j;
+        const bool in = n < p.N;
+        s_wscale[j] = in ? load_as_float(p.w_scale, n, p.w_scale_dtype) : 0.f;
+        s_bias[j] = (in && p.bias) ? load_as_float(p.bias, n, p.bias_dtype) : 0.f;
+        s_rowsum[j] = (in && p.w_rowsum) ? p.w_rowsum[n] : 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
+    }
+    const int quarter = warp & 3;              // TMEM lanes this warp may read: 32*quarter ..
+    const int row = quarter * 32 + lane;
+    const int m = m0 + row;
+    const bool row_ok = m < p.M;
+    float s_m = 0.f;
+    int zp_m = 0;
+    if (EPI == kEpiLinear && row_ok) {
+      s_m = p.src_scale[m];
+      if (p.src_zp) zp_m = p.src_zp[m];
+    }
+    if (!tc::mbar_wait(accum_bar, 0)) tc::report_timeout(p.status, kStatusEpilogueTimeout);
+    tc::fence_after_sync();
+    const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      uint32_t r[32];
+      tc::tmem_ld_32x32b_x32(t_row + c, r);
+      tc::tmem_ld_wait();
+      const int nb = n0 + c;
+      if (!row_ok || nb >= p.N) {
+        // nothing to store for this lane; fall through to the reconvergence point below
+      } else if (EPI == kEpiS32) {
+        int32_t *dst = reinterpret_cast<int32_t *>(p.y) + (size_t)m * p.N + nb;
+        if (nb + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4 *>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        } else {
+          #pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (nb + j < p.N) dst[j] = (int32_t)r[j];
+        }
+      } else {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float af;
+          if (p.src_zp) {  // u8 activations: remove zp_m * sum_k W[n,k]
+            af = (float)((int64_t)(int32_t)r[j] - (int64_t)zp_m * s_rowsum[c + j]);
+          } else {
+            af = (float)(int32_t)r[j];
+          }
+          v[j] = af * (s_m * s_wscale[c + j]) + s_bias[c + j];
+        }
+        const int64_t base = (int64_t)m * p.N + nb;
+        if (p.post.n_ops > 0) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (nb + j < p.N) v[j] = apply_post_ops(v[j], p.post, base + j, p.y_dtype);
+        }
+        const bool full = nb + 32 <= p.N;
+        if (p.y_dtype == ZT_BF16) {
+          __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.y) + base;
+          if (full && (p.N & 7) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 o;
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+              __nv_bfloat162 t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+              __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+              __nv_bfloat162 t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+              o.x = *reinterpret_cast<uint32_t *>(&t0);
+              o.y = *reinterpret_cast<uint32_t *>(&t1);
+              o.z = *reinterpret_cast<uint32_t *>(&t2);
+              o.w = *reinterpret_cast<uint32_t *>(&t3);
+              *reinterpret_cast<uint4 *>(dst + j) = o;
+            }
+          } else {
+            #pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nb + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+          }
+        } else {
+          float *dst = reinterpret_cast<float *>(p.y) + base;
+          if (full && (p.N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            #pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nb + j < p.N) dst[j] = v[j];
+          }
+        }
+      }
+      __syncwarp();  // the next tcgen05.ld is warp-collective
+    }
+  }
+
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host ----------------------------------------------------------------------------------------
+struct MapKey {
+  const void *ptr;
+  uint64_t inner, rows;
+  uint32_t box_rows;
+  bool operator==(const MapKey &o) const {
+    return ptr == o.ptr && inner == o.inner && rows == o.rows && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey &k) const {
+    return std::hash<const void *>()(k.ptr) ^ (k.inner * 1315423911u) ^ (k.rows << 17) ^ k.box_rows;
+  }
+};
+
+// Tensor maps depend only on (pointer, shape, box); encoding one costs a driver call, so they are
+// memoised per process.
+int cached_map(CUtensorMap *out, const void *ptr, uint64_t inner, uint64_t rows, uint32_t box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{ptr, inner, rows, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return ZT_SUCCESS;
+  }
+  int rc = make_tensor_map_2d(out, ptr, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, inner, rows, inner, kBK, box_rows);
+  if (rc != ZT_SUCCESS) return rc;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return ZT_SUCCESS;
+}
+
+template <int BN, int STAGES, int EPI, bool A_SIGNED>
+int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, cudaStream_t st) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = int8_tcgen05_kernel<BN, STAGES, EPI, A_SIGNED>;
+  static bool configured = false;
+  if (!configured) {
+    ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured = true;
+  }
+  dim3 grid((unsigned)ceil_div(p.N, BN), (unsigned)ceil_div(p.M, kBM));
+  kern<<<grid, kThreads, L::kTotal, st>>>(ta, tb, p);
+  return launch_status("int8_tcgen05_kernel");
+}
+
+template <int BN, int STAGES>
+int launch_bn(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, int epi, bool a_signed, cudaStream_t st) {
+  if (epi == kEpiS32)
+    return a_signed ? launch_cfg<BN, STAGES, kEpiS32, true>(ta, tb, p, st)
+                    : launch_cfg<BN, STAGES, kEpiS32, false>(ta, tb, p, st);
+  return a_signed ? launch_cfg<BN, STAGES, kEpiLinear, true>(ta, tb, p, st)
+                  : launch_cfg<BN, STAGES, kEpiLinear, false>(ta, tb, p, st);
+}
+
+// Tile width: the candidate that minimises (waves over the SMs at two CTAs per SM) x (tile cost).
+int pick_bn(int64_t M, int64_t N) {
+  const int cands[] = {256, 224, 192, 160, 128, 96, 64};
+  const int64_t slots = 2LL * sm_count();
+  const int64_t mt = ceil_div<int64_t>(M, kBM);
+  double best = 1e30;
+  int best_bn = 128;
+  for (int bn : cands) {
+    const int64_t tiles = mt * ceil_div<int64_t>(N, bn);
+    const int64_t waves = ceil_div<int64_t>(tiles, slots);
+    // per-tile cost ~ MMA time (prop. to bn) + fixed per-tile overhead; two co-resident CTAs share
+    // the tensor core, so a wave costs 2 tiles' worth of MMA time when more than sm_count tiles run.
+    const double per_wave = (tiles > slots / 2 ? 2.0 : 1.0) * (bn + 24.0);
+    const double cost = waves * per_wave;
+    if (cost < best - 1e-9) {
+      best = cost;
+      best_bn = bn;
+    }
+  }
+  return best_bn;
+}
+
+}  // namespace
+
+bool int8_tcgen05_supported(int64_t M, int64_t N, int64_t K, const void *q, const void *w) {
+  if (M < 1 || N < 1 || K < 16 || K % 16 != 0) return false;
+  if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return false;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(w)) & 15) return false;
+  return true;
+}
+
+int int8_tcgen05_launch(const Int8GemmArgs &a, cudaStream_t st) {
+  TcParams p{};
+  p.M = (int)a.M;
+  p.N = (int)a.N;
+  p.K = (int)a.K;
+  p.src_scale = a.src_scale;
+  p.src_zp = a.src_zp;
+  p.w_scale = a.w_scale;
+  p.w_rowsum = a.w_rowsum;
+  p.bias = a.bias;
+  p.w_scale_dtype = a.w_scale_dtype;
+  p.bias_dtype = a.bias_dtype;
+  p.y_dtype = a.y_dtype;
+  p.y = a.y;
+  p.post = a.post;
+  p.status = device_status_ptr();
+  const int epi = a.raw_s32 ? kEpiS32 : kEpiLinear;
+  int bn = a.force_bn > 0 ? a.force_bn : pick_bn(a.M, a.N);
+  CUtensorMap ta, tb;
+  int rc = cached_map(&ta, a.q, (uint64_t)a.K, (uint64_t)a.M, kBM);
+  if (rc != ZT_SUCCESS) return rc;
+  rc = cached_map(&tb, a.w, (uint64_t)a.K, (uint64_t)a.N, (uint32_t)bn);
+  if (rc != ZT_SUCCESS) return rc;
+  const bool sgn = !a.q_is_u8;
+  switch (bn) {
+    case 256: return launch_bn<256, 2>(ta, tb, p, epi, sgn, st);
+    case 224: return launch_bn<224, 2>(ta, tb, p, epi, sgn, st);
+    case 192: return launch_bn<192, 2>(ta, tb, p, epi, sgn, st);
+    case 160: return launch_bn<160, 3>(ta, tb, p, epi, sgn, st);
+    case 128: return launch_bn<128, 3>(ta, tb, p, epi, sgn, st);
+    case 96: return launch_bn<96, 3>(ta, tb, p, epi, sgn, st);
+    case 64: return launch_bn<64, 4>(ta, tb, p, epi, sgn, st);
+    default: break;
+  }
+  set_error("int8_tcgen05_launch: unsupported tile width %d", bn);
+  return ZT_UNSUPPORTED;
+}
+
+}  // namespace zt

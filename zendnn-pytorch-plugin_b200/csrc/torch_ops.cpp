@@ -1,0 +1,528 @@
+// Thin PyTorch boundary: the reference's operator schemas with a CUDA dispatch key.
+//
+// The schema strings are those of src/cpu/cpp/WOQ_Linear.cpp:435-480 and
+// src/cpu/cpp/DynamicQLinear.cpp:184-189; they are defined here only when no other library has
+// defined them already (a real zentorch registers CPU kernels for the same names, and both can be
+// loaded in one process).  Every CUDA implementation marshals tensors into the plain-pointer C ABI
+// of libzentorch_b200 (include/zentorch_b200.h) and launches on the current CUDA stream; nothing
+// here computes.  The AOTInductor C shims mirror src/cpu/cpp/shim_cpu_zentorch.hpp:150-197 with the
+// device name Inductor derives for CUDA tensors.
+#include <ATen/ATen.h>
+#include <ATen/core/dispatch/Dispatcher.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <ATen/record_function.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/csrc/inductor/aoti_torch/c/shim.h>
+#include <torch/csrc/inductor/aoti_torch/utils.h>
+#include <torch/library.h>
+
+#include <map>
+#include <mutex>
+#include <optional>
+#include <string>
+#include <vector>
+
+#include "../../include/zentorch_b200.h"
+
+namespace zentorch_b200 {
+
+namespace {
+
+#define ZT_TORCH_CALL(expr)                                         \
+  do {                                                              \
+    const int rc__ = (expr);                                        \
+    TORCH_CHECK(rc__ == ZT_SUCCESS, zt_last_error());               \
+  } while (0)
+
+int to_zt_dtype(const at::Tensor &t, const char *what) {
+  if (t.scalar_type() == at::kBFloat16) return ZT_BF16;
+  if (t.scalar_type() == at::kFloat) return ZT_F32;
+  TORCH_CHECK(false, what, " must be float32 or bfloat16, got ", t.scalar_type());
+  return -1;
+}
+
+// Flattens all but the last dimension (get_contiguous_view + get_2d_size_for_tensor,
+// src/cpu/cpp/MatmulUtils.hpp:79-92, 554-563).
+at::Tensor as_2d(const at::Tensor &t) {
+  const bool zero_stride = std::any_of(t.strides().begin(), t.strides().end(), [](int64_t s) { return s == 0; });
+  at::Tensor c = (t.is_contiguous() && !zero_stride) ? t : t.contiguous();
+  const int64_t last = c.size(c.dim() - 1);
+  return c.view({last == 0 ? 0 : c.numel() / last, last});
+}
+
+// Persistent scratch per (device, stream) for the split-K kernel: the counters at its front must
+// stay zero between calls, so it cannot come from a fresh allocation every time.
+at::Tensor &woq_workspace(size_t bytes, c10::DeviceIndex dev, cudaStream_t stream) {
+  static std::mutex mu;
+  static std::map<std::pair<int, void *>, at::Tensor> pool;
+  std::lock_guard<std::mutex> lock(mu);
+  at::Tensor &t = pool[{(int)dev, (void *)stream}];
+  if (!t.defined() || (size_t)t.numel() < bytes) {
+    const size_t grow = std::max<size_t>(bytes, 1 << 20);
+    t = at::zeros({(int64_t)grow}, at::TensorOptions().dtype(at::kByte).device(at::kCUDA, dev));
+  }
+  return t;
+}
+
+struct PostSpec {
+  std::vector<int> ids;
+  std::vector<at::Tensor> operands;  // in consumption order
+};
+
+at::Tensor woq_linear_impl(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &weight_scales,
+                           const std::optional<at::Tensor> &weight_zero_points, const std::optional<at::Tensor> &bias,
+                           const PostSpec &post, const std::string &op_name) {
+  RECORD_FUNCTION(op_name, std::vector<c10::IValue>({input, weight}));
+  TORCH_CHECK(input.is_cuda(), "zentorch_woq_linear (CUDA): input must be a CUDA tensor");
+  TORCH_CHECK(weight.dtype() == at::kInt, "weight must have dtype int32, got ", weight.dtype());
+  TORCH_CHECK(weight.dim() == 2, "weight must be 2D, got ", weight.dim(), "D");
+  TORCH_CHECK(weight_scales.dim() == 2, "weight_scales must be 2D [groups, N], got ", weight_scales.dim(), "D");
+  TORCH_CHECK(weight_scales.size(1) == weight.size(1), "weight_scales dim 1 (", weight_scales.size(1),
+              ") must match weight dim 1 (", weight.size(1), ")");
+  TORCH_CHECK(input.scalar_type() == at::kBFloat16, "zentorch_woq_linear: input must be bfloat16, got ",
+              input.scalar_type());
+  const int64_t k8 = weight.size(0), N = weight.size(1), K = k8 * 8;
+  TORCH_CHECK(input.dim() >= 1 && input.size(-1) == K, "zentorch_woq_linear: input last dim (", input.size(-1),
+              ") must match the unpacked weight rows (", K, ")");
+  // The op's weight is the transposed view of the row-wise packed [N, K/8] tensor: element (k8, n)
+  // at n*(K/8) + k8.  A row-major [K/8, N] tensor has no defined meaning in the reference either
+  // (it hard-codes ldb = K, src/cpu/cpp/WOQ_Linear.cpp:100), so it is rejected rather than re-laid out.
+  TORCH_CHECK((weight.stride(0) == 1 || k8 == 1) && (weight.stride(1) == k8 || N == 1),
+              "zentorch_woq_linear: weight must be the transposed view of a contiguous [N, K/8] packed tensor "
+              "(shape [K/8, N], strides (1, K/8)); got strides (",
+              weight.stride(0), ", ", weight.stride(1), ")");
+  c10::cuda::CUDAGuard device_guard(input.device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+
+  at::Tensor x2 = as_2d(input);
+  std::vector<int64_t> out_sizes = input.sizes().vec();
+  out_sizes.back() = N;
+  at::Tensor result = at::empty(out_sizes, input.options());
+  const int64_t M = x2.size(0);
+  if (M == 0 || N == 0) return result;
+
+  at::Tensor scales = weight_scales.contiguous();
+  at::Tensor zeros;
+  if (weight_zero_points.has_value() && weight_zero_points->defined()) {
+    TORCH_CHECK(weight_zero_points->sizes() == weight_scales.sizes(),
+                "weight_zero_points must have the shape of weight_scales");
+    zeros = weight_zero_points->to(scales.scalar_type()).contiguous();
+  }
+  at::Tensor bias_c;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->dim() == 1 && bias->size(0) == N, "bias must be 1D with size N (", N, ")");
+    bias_c = bias->contiguous();
+  }
+
+  zt_woq_linear_args_t a{};
+  a.x = x2.data_ptr();
+  a.M = M;
+  a.K = K;
+  a.N = N;
+  a.wq = reinterpret_cast<const int32_t *>(weight.data_ptr());
+  a.scales = scales.data_ptr();
+  a.zeros = zeros.defined() ? zeros.data_ptr() : nullptr;
+  a.scale_dtype = to_zt_dtype(scales, "weight_scales");
+  a.n_groups = scales.size(0);
+  a.bias = bias_c.defined() ? bias_c.data_ptr() : nullptr;
+  a.bias_dtype = bias_c.defined() ? to_zt_dtype(bias_c, "bias") : ZT_BF16;
+  a.y = result.data_ptr();
+  a.algo = ZT_ALGO_AUTO;
+  std::vector<at::Tensor> keep;
+  a.post.n_ops = (int)post.ids.size();
+  size_t b = 0;
+  for (size_t i = 0; i < post.ids.size(); ++i) {
+    a.post.ids[i] = post.ids[i];
+    if (post.ids[i] == ZT_POST_MUL || post.ids[i] == ZT_POST_ADD) {
+      const at::Tensor &t = post.operands.at(b);
+      TORCH_CHECK(t.numel() == M * N, "binary post-op operand must have the shape of the result");
+      TORCH_CHECK(t.scalar_type() == input.scalar_type(), "binary post-op operand must have the dtype of the input");
+      keep.push_back(as_2d(t));
+      a.post.buffers[b] = keep.back().data_ptr();
+      ++b;
+    }
+  }
+  const size_t ws_bytes = zt_woq_linear_workspace_bytes(M, N, K);
+  at::Tensor &ws = woq_workspace(ws_bytes, input.device().index(), stream);
+  a.workspace = ws.data_ptr();
+  a.workspace_bytes = (size_t)ws.numel();
+  ZT_TORCH_CALL(zt_woq_linear(&a, stream));
+  return result;
+}
+
+template <int UNARY>
+at::Tensor woq_linear_unary(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &weight_scales,
+                            const std::optional<at::Tensor> &zp, const std::optional<at::Tensor> &bias,
+                            std::string zentorch_op_name) {
+  PostSpec ps;
+  if (UNARY != ZT_POST_NONE) ps.ids.push_back(UNARY);
+  return woq_linear_impl(input, weight, weight_scales, zp, bias, ps, zentorch_op_name);
+}
+
+at::Tensor woq_linear_add(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &weight_scales,
+                          const std::optional<at::Tensor> &zp, const at::Tensor &add_input,
+                          const std::optional<at::Tensor> &bias, std::string zentorch_op_name) {
+  PostSpec ps{{ZT_POST_ADD}, {add_input}};
+  return woq_linear_impl(input, weight, weight_scales, zp, bias, ps, zentorch_op_name);
+}
+
+template <int B1, int B2>
+at::Tensor woq_linear_binary_binary(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &weight_scales,
+                                    const std::optional<at::Tensor> &zp, const at::Tensor &binary1,
+                                    const at::Tensor &binary2, const std::optional<at::Tensor> &bias,
+                                    std::string zentorch_op_name) {
+  PostSpec ps{{B1, B2}, {binary1, binary2}};
+  return woq_linear_impl(input, weight, weight_scales, zp, bias, ps, zentorch_op_name);
+}
+
+at::Tensor woq_repack_weight(const at::Tensor &unpacked_weight) {
+  TORCH_CHECK(unpacked_weight.dtype() == at::kChar, "unpacked_weight must have dtype int8, got ",
+              unpacked_weight.dtype());
+  TORCH_CHECK(unpacked_weight.dim() == 2, "unpacked_weight must be 2D, got ", unpacked_weight.dim(), "D");
+  const int64_t N = unpacked_weight.size(0), K = unpacked_weight.size(1);
+  TORCH_CHECK(K >= 8, "K must be at least 8, got ", K);
+  TORCH_CHECK(K % 8 == 0, "K must be divisible by 8, got ", K);
+  c10::cuda::CUDAGuard device_guard(unpacked_weight.device());
+  at::Tensor w = unpacked_weight.contiguous();
+  at::Tensor out = at::empty({N, K / 8}, w.options().dtype(at::kInt));
+  ZT_TORCH_CALL(zt_woq_repack_weight(w.data_ptr<int8_t>(), N, K, out.data_ptr<int32_t>(),
+                                     at::cuda::getCurrentCUDAStream().stream()));
+  return out;
+}
+
+at::Tensor woq_repack_from_int4pack(const at::Tensor &packed_weight) {
+  TORCH_CHECK(packed_weight.dtype() == at::kByte, "packed_weight must have dtype uint8, got ", packed_weight.dtype());
+  TORCH_CHECK(packed_weight.dim() == 2, "packed_weight must be 2D, got ", packed_weight.dim(), "D");
+  const int64_t N = packed_weight.size(0), K_half = packed_weight.size(1);
+  TORCH_CHECK(N % 64 == 0, "packed_weight row count (", N, ") must be a multiple of ", 64,
+              ". The int4pack format from PyTorch pads N to BLOCK_N; "
+              "receiving an unpadded tensor indicates a packing mismatch.");
+  c10::cuda::CUDAGuard device_guard(packed_weight.device());
+  at::Tensor w = packed_weight.contiguous();
+  at::Tensor out = at::empty({N, K_half / 4}, w.options().dtype(at::kInt));
+  ZT_TORCH_CALL(zt_woq_repack_from_int4pack(w.data_ptr<uint8_t>(), N, K_half, out.data_ptr<int32_t>(),
+                                            at::cuda::getCurrentCUDAStream().stream()));
+  return out;
+}
+
+// ---- dynamic qlinear ------------------------------------------------------------------------------
+at::Tensor dynamic_qlinear_impl(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &weight_scales,
+                                const std::optional<at::Tensor> &bias, int act_quant, int post_op,
+                                const std::optional<at::Tensor> &weight_rowsum, const std::string &op_name) {
+  RECORD_FUNCTION(op_name, std::vector<c10::IValue>({input, weight}));
+  // checks and messages of check_valid_dtypes/sizes_for_dynamic_qlinear, src/cpu/cpp/DynamicQLinear.cpp:15-70
+  TORCH_CHECK(input.scalar_type() == at::kBFloat16 || input.scalar_type() == at::kFloat,
+              "zentorch_dynamic_qlinear: input must be bfloat16 or float32, got ", input.scalar_type());
+  TORCH_CHECK(weight_scales.scalar_type() == at::kFloat || weight_scales.scalar_type() == at::kBFloat16,
+              "zentorch_dynamic_qlinear: weight_scales must be float32, bfloat16, got ", weight_scales.scalar_type());
+  TORCH_CHECK(weight.scalar_type() == at::kChar, "zentorch_dynamic_qlinear: weight must be int8 (c10::kChar), got ",
+              weight.scalar_type());
+  const bool has_bias = bias.has_value() && bias->defined();
+  if (has_bias) {
+    TORCH_CHECK(bias->scalar_type() == at::kFloat || bias->scalar_type() == at::kBFloat16,
+                "zentorch_dynamic_qlinear: bias must be float32 or bfloat16, got ", bias->scalar_type());
+  }
+  TORCH_CHECK(input.dim() >= 2, "zentorch_dynamic_qlinear: input must be at least 2D");
+  TORCH_CHECK(weight.dim() == 2, "zentorch_dynamic_qlinear: weight must be 2D [N, K], got ", weight.dim(), "D");
+  const int64_t N = weight.size(0), K = weight.size(1);
+  TORCH_CHECK(input.size(input.dim() - 1) == K, "zentorch_dynamic_qlinear: input last dim (", input.size(-1),
+              ") must match weight dim 1 (", K, ")");
+  if (has_bias) {
+    TORCH_CHECK(bias->dim() == 1 && bias->size(0) == N, "zentorch_dynamic_qlinear: bias must be 1D with size N (", N,
+                ")");
+  }
+  TORCH_CHECK(weight_scales.numel() == N, "zentorch_dynamic_qlinear: weight_scales must hold N (", N, ") values");
+  TORCH_CHECK(input.is_cuda(), "zentorch_dynamic_qlinear (CUDA): input must be a CUDA tensor");
+  c10::cuda::CUDAGuard device_guard(input.device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+
+  std::vector<int64_t> out_sizes = input.sizes().vec();
+  out_sizes.back() = N;
+  at::Tensor result = at::empty(out_sizes, input.options());
+  at::Tensor x2 = as_2d(input);
+  const int64_t M = x2.size(0);
+  if (M == 0 || N == 0) return result;
+  at::Tensor w = weight.contiguous();
+  at::Tensor ws = weight_scales.contiguous();
+  at::Tensor b = has_bias ? bias->contiguous() : at::Tensor();
+  at::Tensor rowsum;
+  if (act_quant == ZT_ACT_U8_ASYM) {
+    if (weight_rowsum.has_value() && weight_rowsum->defined()) {
+      TORCH_CHECK(weight_rowsum->scalar_type() == at::kInt && weight_rowsum->numel() == N,
+                  "weight_rowsum must be int32 with N values");
+      rowsum = weight_rowsum->contiguous();
+    } else {
+      rowsum = at::empty({N}, w.options().dtype(at::kInt));
+      ZT_TORCH_CALL(zt_int8_weight_rowsum(w.data_ptr<int8_t>(), N, K, rowsum.data_ptr<int32_t>(), stream));
+    }
+  }
+  const size_t ws_bytes = zt_dynamic_qlinear_workspace_bytes(M, K);
+  at::Tensor scratch = at::empty({(int64_t)ws_bytes}, w.options().dtype(at::kByte));
+
+  zt_dynamic_qlinear_args_t a{};
+  a.x = x2.data_ptr();
+  a.x_dtype = to_zt_dtype(x2, "input");
+  a.M = M;
+  a.K = K;
+  a.N = N;
+  a.w = w.data_ptr<int8_t>();
+  a.w_scales = ws.data_ptr();
+  a.w_scale_dtype = to_zt_dtype(ws, "weight_scales");
+  a.bias = b.defined() ? b.data_ptr() : nullptr;
+  a.bias_dtype = b.defined() ? to_zt_dtype(b, "bias") : ZT_F32;
+  a.act_quant = act_quant;
+  a.w_rowsum = rowsum.defined() ? rowsum.data_ptr<int32_t>() : nullptr;
+  if (post_op != ZT_POST_NONE) {
+    a.post.n_ops = 1;
+    a.post.ids[0] = post_op;
+  }
+  a.y = result.data_ptr();
+  a.workspace = scratch.data_ptr();
+  a.workspace_bytes = ws_bytes;
+  a.algo = ZT_ALGO_AUTO;
+  ZT_TORCH_CALL(zt_dynamic_qlinear(&a, stream));
+  return result;
+}
+
+at::Tensor dynamic_qlinear(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &weight_scales,
+                           const std::optional<at::Tensor> &bias, std::string zentorch_op_name) {
+  return dynamic_qlinear_impl(input, weight, weight_scales, bias, ZT_ACT_S8_SYM, ZT_POST_NONE, std::nullopt,
+                              zentorch_op_name);
+}
+
+int post_id_from_name(const std::string &s) {
+  static const std::map<std::string, int> names = {{"none", ZT_POST_NONE},         {"relu", ZT_POST_RELU},
+                                                   {"gelu_tanh", ZT_POST_GELU_TANH}, {"gelu_erf", ZT_POST_GELU_ERF},
+                                                   {"silu", ZT_POST_SILU},         {"sigmoid", ZT_POST_SIGMOID},
+                                                   {"tanh", ZT_POST_TANH}};
+  auto it = names.find(s);
+  TORCH_CHECK(it != names.end(), "unknown post_op '", s, "'");
+  return it->second;
+}
+
+// Extension (no reference counterpart): per-token u8 asymmetric activations and a fused unary post-op.
+at::Tensor dynamic_qlinear_ext(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &weight_scales,
+                               const std::optional<at::Tensor> &bias, const std::optional<at::Tensor> &weight_rowsum,
+                               std::string act_quant, std::string post_op, std::string zentorch_op_name) {
+  TORCH_CHECK(act_quant == "s8_sym" || act_quant == "u8_asym", "act_quant must be 's8_sym' or 'u8_asym'");
+  return dynamic_qlinear_impl(input, weight, weight_scales, bias, act_quant == "u8_asym" ? ZT_ACT_U8_ASYM : ZT_ACT_S8_SYM,
+                              post_id_from_name(post_op), weight_rowsum, zentorch_op_name);
+}
+
+// ---- meta kernels (src/cpu/python/zentorch/_meta_registrations.py:552-714, 755-797) --------------------
+at::Tensor meta_woq(const at::Tensor &input, const at::Tensor &weight) {
+  std::vector<c10::SymInt> sizes = input.sym_sizes().vec();
+  sizes.back() = weight.sym_size(1);
+  return at::empty_symint(sizes, input.options());
+}
+at::Tensor meta_woq_unary(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &,
+                          const std::optional<at::Tensor> &, const std::optional<at::Tensor> &, std::string) {
+  return meta_woq(input, weight);
+}
+at::Tensor meta_woq_add(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &,
+                        const std::optional<at::Tensor> &, const at::Tensor &, const std::optional<at::Tensor> &,
+                        std::string) {
+  return meta_woq(input, weight);
+}
+at::Tensor meta_woq_binary_binary(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &,
+                                  const std::optional<at::Tensor> &, const at::Tensor &, const at::Tensor &,
+                                  const std::optional<at::Tensor> &, std::string) {
+  return meta_woq(input, weight);
+}
+at::Tensor meta_repack_weight(const at::Tensor &w) {
+  return at::empty_symint({w.sym_size(0), w.sym_size(1) / 8}, w.options().dtype(at::kInt));
+}
+at::Tensor meta_repack_from_int4pack(const at::Tensor &w) {
+  return at::empty_symint({w.sym_size(0), w.sym_size(1) * 2 / 8}, w.options().dtype(at::kInt));
+}
+at::Tensor meta_dynamic_qlinear(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &,
+                                const std::optional<at::Tensor> &, std::string) {
+  std::vector<c10::SymInt> sizes = input.sym_sizes().vec();
+  sizes.back() = weight.sym_size(0);
+  return at::empty_symint(sizes, input.options());
+}
+at::Tensor meta_dynamic_qlinear_ext(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &,
+                                    const std::optional<at::Tensor> &, const std::optional<at::Tensor> &, std::string,
+                                    std::string, std::string) {
+  std::vector<c10::SymInt> sizes = input.sym_sizes().vec();
+  sizes.back() = weight.sym_size(0);
+  return at::empty_symint(sizes, input.options());
+}
+
+bool has_schema(const char *name) {
+  return c10::Dispatcher::singleton().findSchema({std::string("zentorch::") + name, ""}).has_value();
+}
+
+struct Registrar {
+  std::vector<std::unique_ptr<torch::Library>> libs;
+  Registrar() {
+    auto frag = std::make_unique<torch::Library>(torch::Library::FRAGMENT, "zentorch", std::nullopt, __FILE__, __LINE__);
+    auto def = [&](const char *name, const char *schema, std::vector<at::Tag> tags = {}) {
+      if (!has_schema(name)) frag->def(schema, static_cast<const std::vector<at::Tag> &>(tags));
+    };
+    def("zentorch_woq_linear",
+        "zentorch_woq_linear(Tensor input, Tensor weight, Tensor weight_scales, Tensor? weight_zero_points, "
+        "Tensor? bias=None, *, str zentorch_op_name='zentorch::zentorch_woq_linear') -> Tensor");
+    def("zentorch_woq_linear_relu",
+        "zentorch_woq_linear_relu(Tensor input, Tensor weight, Tensor weight_scales, Tensor? weight_zero_points, "
+        "Tensor? bias=None, *, str zentorch_op_name='zentorch::zentorch_woq_linear_relu') -> Tensor");
+    def("zentorch_woq_linear_sigmoid",
+        "zentorch_woq_linear_sigmoid(Tensor input, Tensor weight, Tensor weight_scales, Tensor? weight_zero_points, "
+        "Tensor? bias=None, *, str zentorch_op_name='zentorch::zentorch_woq_linear_sigmoid') -> Tensor");
+    def("zentorch_woq_linear_gelu_tanh",
+        "zentorch_woq_linear_gelu_tanh(Tensor input, Tensor weight, Tensor weight_scales, Tensor? weight_zero_points, "
+        "Tensor? bias=None, *, str zentorch_op_name='zentorch::zentorch_woq_linear_gelu_tanh') -> Tensor");
+    def("zentorch_woq_linear_gelu_erf",
+        "zentorch_woq_linear_gelu_erf(Tensor input, Tensor weight, Tensor weight_scales, Tensor? weight_zero_points, "
+        "Tensor? bias=None, *, str zentorch_op_name='zentorch::zentorch_woq_linear_gelu_erf') -> Tensor");
+    def("zentorch_woq_linear_add",
+        "zentorch_woq_linear_add(Tensor input, Tensor weight, Tensor weight_scales, Tensor? weight_zero_points, "
+        "Tensor add_input, Tensor? bias=None, *, str zentorch_op_name='zentorch::zentorch_woq_linear_add') -> Tensor",
+        {at::Tag::needs_contiguous_strides});
+    def("zentorch_woq_linear_mul_add",
+        "zentorch_woq_linear_mul_add(Tensor input, Tensor weight, Tensor weight_scales, Tensor? weight_zero_points, "
+        "Tensor mul_input, Tensor add_input, Tensor? bias=None, *, str zentorch_op_name="
+        "'zentorch::zentorch_woq_linear_mul_add') -> Tensor",
+        {at::Tag::needs_fixed_stride_order});
+    def("zentorch_woq_linear_add_add",
+        "zentorch_woq_linear_add_add(Tensor input, Tensor weight, Tensor weight_scales, Tensor? weight_zero_points, "
+        "Tensor add_input, Tensor add_input_2, Tensor? bias=None, *, str zentorch_op_name="
+        "'zentorch::zentorch_woq_linear_add_add') -> Tensor",
+        {at::Tag::needs_fixed_stride_order});
+    def("zentorch_woq_repack_weight", "zentorch_woq_repack_weight(Tensor unpacked_weight) -> Tensor");
+    def("zentorch_woq_repack_from_int4pack", "zentorch_woq_repack_from_int4pack(Tensor packed_weight) -> Tensor");
+    def("zentorch_dynamic_qlinear",
+        "zentorch_dynamic_qlinear(Tensor input, Tensor weight, Tensor weight_scales, Tensor? bias=None, *, "
+        "str zentorch_op_name='zentorch::zentorch_dynamic_qlinear') -> Tensor");
+    def("zentorch_dynamic_qlinear_ext",
+        "zentorch_dynamic_qlinear_ext(Tensor input, Tensor weight, Tensor weight_scales, Tensor? bias=None, "
+        "Tensor? weight_rowsum=None, *, str act_quant='s8_sym', str post_op='none', "
+        "str zentorch_op_name='zentorch::zentorch_dynamic_qlinear_ext') -> Tensor");
+    libs.push_back(std::move(frag));
+
+    auto cuda = std::make_unique<torch::Library>(torch::Library::IMPL, "zentorch", c10::DispatchKey::CUDA, __FILE__, __LINE__);
+    cuda->impl("zentorch_woq_linear", woq_linear_unary<ZT_POST_NONE>);
+    cuda->impl("zentorch_woq_linear_relu", woq_linear_unary<ZT_POST_RELU>);
+    cuda->impl("zentorch_woq_linear_sigmoid", woq_linear_unary<ZT_POST_SIGMOID>);
+    cuda->impl("zentorch_woq_linear_gelu_tanh", woq_linear_unary<ZT_POST_GELU_TANH>);
+    cuda->impl("zentorch_woq_linear_gelu_erf", woq_linear_unary<ZT_POST_GELU_ERF>);
+    cuda->impl("zentorch_woq_linear_add", woq_linear_add);
+    cuda->impl("zentorch_woq_linear_mul_add", woq_linear_binary_binary<ZT_POST_MUL, ZT_POST_ADD>);
+    cuda->impl("zentorch_woq_linear_add_add", woq_linear_binary_binary<ZT_POST_ADD, ZT_POST_ADD>);
+    cuda->impl("zentorch_woq_repack_weight", woq_repack_weight);
+    cuda->impl("zentorch_woq_repack_from_int4pack", woq_repack_from_int4pack);
+    cuda->impl("zentorch_dynamic_qlinear", dynamic_qlinear);
+    cuda->impl("zentorch_dynamic_qlinear_ext", dynamic_qlinear_ext);
+    libs.push_back(std::move(cuda));
+
+    // A real zentorch registers its own Meta kernels from Python; only fill the gap when absent.
+    auto meta = std::make_unique<torch::Library>(torch::Library::IMPL, "zentorch", c10::DispatchKey::Meta, __FILE__, __LINE__);
+    auto has_meta = [](const char *name) {
+      auto op = c10::Dispatcher::singleton().findOp({std::string("zentorch::") + name, ""});
+      return op.has_value() && op->hasKernelForDispatchKey(c10::DispatchKey::Meta);
+    };
+#define ZT_META(name, fn) \
+  if (!has_meta(name)) meta->impl(name, fn)
+    ZT_META("zentorch_woq_linear", meta_woq_unary);
+    ZT_META("zentorch_woq_linear_relu", meta_woq_unary);
+    ZT_META("zentorch_woq_linear_sigmoid", meta_woq_unary);
+    ZT_META("zentorch_woq_linear_gelu_tanh", meta_woq_unary);
+    ZT_META("zentorch_woq_linear_gelu_erf", meta_woq_unary);
+    ZT_META("zentorch_woq_linear_add", meta_woq_add);
+    ZT_META("zentorch_woq_linear_mul_add", meta_woq_binary_binary);
+    ZT_META("zentorch_woq_linear_add_add", meta_woq_binary_binary);
+    ZT_META("zentorch_woq_repack_weight", meta_repack_weight);
+    ZT_META("zentorch_woq_repack_from_int4pack", meta_repack_from_int4pack);
+    ZT_META("zentorch_dynamic_qlinear", meta_dynamic_qlinear);
+    ZT_META("zentorch_dynamic_qlinear_ext", meta_dynamic_qlinear_ext);
+#undef ZT_META
+    libs.push_back(std::move(meta));
+  }
+};
+
+static Registrar g_registrar;
+
+}  // namespace
+
+}  // namespace zentorch_b200
+
+// ---- AOTInductor C shims -------------------------------------------------------------------------------
+// Same parameter lists as aoti_torch_cpu_zentorch_* (src/cpu/cpp/shim_cpu_zentorch.hpp:150-197);
+// inputs are borrowed handles, *ret0 receives a new owning handle (shim_cpu_zentorch.cpp:367-381).
+using torch::aot_inductor::new_tensor_handle;
+using torch::aot_inductor::pointer_to_optional;
+using torch::aot_inductor::tensor_handle_to_tensor_pointer;
+using namespace zentorch_b200;
+
+#define ZT_SHIM_UNARY(suffix, POST)                                                                          \
+  extern "C" ZT_API AOTITorchError aoti_torch_cuda_zentorch_woq_linear##suffix(                              \
+      AtenTensorHandle X, AtenTensorHandle W, AtenTensorHandle weight_scales, AtenTensorHandle *weight_zero_points, \
+      AtenTensorHandle *B, const char *zentorch_op_name, AtenTensorHandle *ret0) {                           \
+    AOTI_TORCH_CONVERT_EXCEPTION_TO_ERROR_CODE({                                                             \
+      auto tmp = woq_linear_unary<POST>(*tensor_handle_to_tensor_pointer(X), *tensor_handle_to_tensor_pointer(W), \
+                                        *tensor_handle_to_tensor_pointer(weight_scales),                     \
+                                        pointer_to_optional<at::Tensor>(weight_zero_points),                 \
+                                        pointer_to_optional<at::Tensor>(B), zentorch_op_name);               \
+      *ret0 = new_tensor_handle(std::move(tmp));                                                             \
+    });                                                                                                      \
+  }
+
+ZT_SHIM_UNARY(, ZT_POST_NONE)
+ZT_SHIM_UNARY(_relu, ZT_POST_RELU)
+ZT_SHIM_UNARY(_sigmoid, ZT_POST_SIGMOID)
+ZT_SHIM_UNARY(_gelu_tanh, ZT_POST_GELU_TANH)
+ZT_SHIM_UNARY(_gelu_erf, ZT_POST_GELU_ERF)
+
+extern "C" ZT_API AOTITorchError aoti_torch_cuda_zentorch_woq_linear_add(
+    AtenTensorHandle X, AtenTensorHandle W, AtenTensorHandle weight_scales, AtenTensorHandle *weight_zero_points,
+    AtenTensorHandle add_input, AtenTensorHandle *B, const char *zentorch_op_name, AtenTensorHandle *ret0) {
+  AOTI_TORCH_CONVERT_EXCEPTION_TO_ERROR_CODE({
+    auto tmp = woq_linear_add(*tensor_handle_to_tensor_pointer(X), *tensor_handle_to_tensor_pointer(W),
+                              *tensor_handle_to_tensor_pointer(weight_scales),
+                              pointer_to_optional<at::Tensor>(weight_zero_points),
+                              *tensor_handle_to_tensor_pointer(add_input), pointer_to_optional<at::Tensor>(B),
+                              zentorch_op_name);
+    *ret0 = new_tensor_handle(std::move(tmp));
+  });
+}
+
+extern "C" ZT_API AOTITorchError aoti_torch_cuda_zentorch_woq_linear_mul_add(
+    AtenTensorHandle X, AtenTensorHandle W, AtenTensorHandle weight_scales, AtenTensorHandle *weight_zero_points,
+    AtenTensorHandle mul_input, AtenTensorHandle add_input, AtenTensorHandle *B, const char *zentorch_op_name,
+    AtenTensorHandle *ret0) {
+  AOTI_TORCH_CONVERT_EXCEPTION_TO_ERROR_CODE({
+    auto tmp = woq_linear_binary_binary<ZT_POST_MUL, ZT_POST_ADD>(
+        *tensor_handle_to_tensor_pointer(X), *tensor_handle_to_tensor_pointer(W),
+        *tensor_handle_to_tensor_pointer(weight_scales), pointer_to_optional<at::Tensor>(weight_zero_points),
+        *tensor_handle_to_tensor_pointer(mul_input), *tensor_handle_to_tensor_pointer(add_input),
+        pointer_to_optional<at::Tensor>(B), zentorch_op_name);
+    *ret0 = new_tensor_handle(std::move(tmp));
+  });
+}
+
+extern "C" ZT_API AOTITorchError aoti_torch_cuda_zentorch_woq_linear_add_add(
+    AtenTensorHandle X, AtenTensorHandle W, AtenTensorHandle weight_scales, AtenTensorHandle *weight_zero_points,
+    AtenTensorHandle add_input, AtenTensorHandle add_input_2, AtenTensorHandle *B, const char *zentorch_op_name,
+    AtenTensorHandle *ret0) {
+  AOTI_TORCH_CONVERT_EXCEPTION_TO_ERROR_CODE({
+    auto tmp = woq_linear_binary_binary<ZT_POST_ADD, ZT_POST_ADD>(
+        *tensor_handle_to_tensor_pointer(X), *tensor_handle_to_tensor_pointer(W),
+        *tensor_handle_to_tensor_pointer(weight_scales), pointer_to_optional<at::Tensor>(weight_zero_points),
+        *tensor_handle_to_tensor_pointer(add_input), *tensor_handle_to_tensor_pointer(add_input_2),
+        pointer_to_optional<at::Tensor>(B), zentorch_op_name);
+    *ret0 = new_tensor_handle(std::move(tmp));
+  });
+}
+
+extern "C" ZT_API AOTITorchError aoti_torch_cuda_zentorch_dynamic_qlinear(AtenTensorHandle X, AtenTensorHandle W,
+                                                                         AtenTensorHandle weight_scales,
+                                                                         AtenTensorHandle *B,
+                                                                         const char *zentorch_op_name,
+                                                                         AtenTensorHandle *ret0) {
+  AOTI_TORCH_CONVERT_EXCEPTION_TO_ERROR_CODE({
+    auto tmp = dynamic_qlinear(*tensor_handle_to_tensor_pointer(X), *tensor_handle_to_tensor_pointer(W),
+                               *tensor_handle_to_tensor_pointer(weight_scales), pointer_to_optional<at::Tensor>(B),
+                               zentorch_op_name);
+    *ret0 = new_tensor_handle(std::move(tmp));
+  });
+}

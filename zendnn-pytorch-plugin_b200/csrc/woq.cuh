@@ -1,0 +1,24 @@
+// Internal interface between the dispatcher (api.cu) and the weight-only int4 kernels.
+#pragma once
+
+#include "common.cuh"
+
+namespace zt {
+
+struct WoqSkinnyPlan {
+  int mt;      // 8-row activation blocks held per CTA (1, 2, 4 or 8)
+  int kslice;  // k handled by one CTA
+  int nsplit;  // number of K-slices
+  size_t partial_bytes;
+};
+
+WoqSkinnyPlan woq_skinny_plan(int64_t M, int64_t N, int64_t K);
+bool woq_skinny_supported(const zt_woq_linear_args_t &a);
+int woq_skinny_launch(const zt_woq_linear_args_t &a, bool fold, cudaStream_t st);
+
+int woq_generic_launch(const zt_woq_linear_args_t &a, cudaStream_t st);
+
+bool woq_tcgen05_supported(const zt_woq_linear_args_t &a);
+int woq_tcgen05_launch(const zt_woq_linear_args_t &a, cudaStream_t st);
+
+}  // namespace zt

@@ -1,0 +1,235 @@
+"""ctypes binding of the C ABI declared in ``include/zentorch_b200.h``.
+
+This is the binding a maintainer of the reference would write to call the library from Python
+without going through ``torch.ops``; the parity tests use it so that what they exercise is the
+shipped C entry points themselves.  Tensors are passed as raw device pointers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libzentorch_b200.so"
+
+ZT_SUCCESS = 0
+ZT_BF16, ZT_F32 = 0, 1
+ZT_MAX_POST_OPS = 4
+ZT_WOQ_COUNTER_BYTES = 16384
+ZT_ALGO_AUTO, ZT_ALGO_GENERIC, ZT_ALGO_SKINNY, ZT_ALGO_TCGEN05 = 0, 1, 2, 3
+ZT_ACT_S8_SYM, ZT_ACT_U8_ASYM = 0, 1
+(ZT_POST_NONE, ZT_POST_RELU, ZT_POST_GELU_TANH, ZT_POST_GELU_ERF, ZT_POST_SILU, ZT_POST_SIGMOID,
+ ZT_POST_TANH, ZT_POST_MUL, ZT_POST_ADD) = range(9)
+
+# Every symbol include/zentorch_b200.h declares; the CPU test-suite checks the library exports all.
+EXPORTED_SYMBOLS = (
+    "zt_last_error", "zt_version", "zt_device_supported", "zt_poll_device_status",
+    "zt_woq_linear_workspace_bytes", "zt_woq_linear", "zt_woq_repack_weight", "zt_woq_repack_from_int4pack",
+    "zt_dynamic_qlinear_workspace_bytes", "zt_dynamic_qlinear", "zt_dynamic_quantize", "zt_int8_gemm_s32",
+    "zt_int8_weight_rowsum",
+)
+
+
+class PostOps(C.Structure):
+    _fields_ = [("n_ops", C.c_int32), ("ids", C.c_int32 * ZT_MAX_POST_OPS), ("buffers", C.c_void_p * ZT_MAX_POST_OPS)]
+
+
+class WoqLinearArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("M", C.c_int64), ("K", C.c_int64), ("N", C.c_int64),
+        ("wq", C.c_void_p), ("scales", C.c_void_p), ("zeros", C.c_void_p), ("scale_dtype", C.c_int32),
+        ("n_groups", C.c_int64), ("bias", C.c_void_p), ("bias_dtype", C.c_int32), ("post", PostOps),
+        ("y", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("algo", C.c_int32),
+    ]
+
+
+class DynamicQLinearArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("x_dtype", C.c_int32), ("M", C.c_int64), ("K", C.c_int64), ("N", C.c_int64),
+        ("w", C.c_void_p), ("w_scales", C.c_void_p), ("w_scale_dtype", C.c_int32), ("bias", C.c_void_p),
+        ("bias_dtype", C.c_int32), ("act_quant", C.c_int32), ("w_rowsum", C.c_void_p), ("post", PostOps),
+        ("y", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("algo", C.c_int32),
+    ]
+
+
+class ZtError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(message or f"zentorch_b200 error {code}")
+        self.code = code
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads libzentorch_b200.so (RTLD_GLOBAL, as the reference loads libzentorch.so:
+    src/cpu/python/zentorch/__init__.py:69-78).  Raises when it has not been built: there is no
+    fallback implementation."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m zentorch_b200._build` "
+            "(there is no CPU or PyTorch fallback for these operators)")
+    L = C.CDLL(str(LIB_PATH), mode=C.RTLD_GLOBAL)
+    L.zt_last_error.restype = C.c_char_p
+    L.zt_version.restype = C.c_char_p
+    L.zt_device_supported.restype = C.c_int
+    L.zt_poll_device_status.argtypes = [C.POINTER(C.c_int), C.c_int]
+    L.zt_woq_linear_workspace_bytes.restype = C.c_size_t
+    L.zt_woq_linear_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64]
+    L.zt_woq_linear.argtypes = [C.POINTER(WoqLinearArgs), C.c_void_p]
+    L.zt_woq_repack_weight.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
+    L.zt_woq_repack_from_int4pack.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
+    L.zt_dynamic_qlinear_workspace_bytes.restype = C.c_size_t
+    L.zt_dynamic_qlinear_workspace_bytes.argtypes = [C.c_int64, C.c_int64]
+    L.zt_dynamic_qlinear.argtypes = [C.POINTER(DynamicQLinearArgs), C.c_void_p]
+    L.zt_dynamic_quantize.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
+                                      C.c_void_p, C.c_void_p, C.c_void_p]
+    L.zt_int8_gemm_s32.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
+                                   C.c_int32, C.c_void_p]
+    L.zt_int8_weight_rowsum.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
+    _lib = L
+    return L
+
+
+def check(rc: int) -> None:
+    if rc != ZT_SUCCESS:
+        raise ZtError(rc, lib().zt_last_error().decode())
+
+
+def poll_device_status(reset: bool = True) -> int:
+    st = C.c_int(0)
+    check(lib().zt_poll_device_status(C.byref(st), 1 if reset else 0))
+    return st.value
+
+
+# ---- torch-tensor conveniences (raw pointers underneath) ------------------------------------------
+def _dtype_code(t) -> int:
+    import torch
+    if t.dtype == torch.bfloat16:
+        return ZT_BF16
+    if t.dtype == torch.float32:
+        return ZT_F32
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _stream_ptr():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _post(post_ops, buffers) -> PostOps:
+    p = PostOps()
+    p.n_ops = len(post_ops)
+    for i, op in enumerate(post_ops):
+        p.ids[i] = int(op)
+    for i, b in enumerate(buffers):
+        p.buffers[i] = b.data_ptr()
+    return p
+
+
+_woq_ws = {}
+
+
+def woq_workspace(nbytes: int, device):
+    """Zero-initialised scratch kept per device (the counters at its front must stay zero)."""
+    import torch
+    key = (device.index, torch.cuda.current_stream().cuda_stream)
+    t = _woq_ws.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _woq_ws[key] = t
+    return t
+
+
+def woq_linear(x, wq_rows, scales, zeros=None, bias=None, post_ops=(), buffers=(), algo=ZT_ALGO_AUTO):
+    """x: [M, K] bf16 CUDA; wq_rows: the contiguous [N, K/8] int32 packed tensor (i.e. the op's
+    weight argument transposed back); scales/zeros: [G, N]."""
+    import torch
+    assert x.is_cuda and x.is_contiguous() and wq_rows.is_contiguous() and scales.is_contiguous()
+    m, k = x.shape
+    n = wq_rows.shape[0]
+    y = torch.empty(m, n, dtype=x.dtype, device=x.device)
+    a = WoqLinearArgs()
+    a.x, a.M, a.K, a.N = x.data_ptr(), m, k, n
+    a.wq, a.scales = wq_rows.data_ptr(), scales.data_ptr()
+    a.zeros = zeros.data_ptr() if zeros is not None else None
+    a.scale_dtype, a.n_groups = _dtype_code(scales), scales.shape[0]
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.bias_dtype = _dtype_code(bias) if bias is not None else ZT_BF16
+    a.post = _post(post_ops, buffers)
+    a.y = y.data_ptr()
+    ws = woq_workspace(lib().zt_woq_linear_workspace_bytes(m, n, k), x.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.algo = algo
+    check(lib().zt_woq_linear(C.byref(a), _stream_ptr()))
+    return y
+
+
+def woq_repack_weight(unpacked):
+    import torch
+    n, k = unpacked.shape
+    out = torch.empty(n, max(k // 8, 0), dtype=torch.int32, device=unpacked.device)
+    check(lib().zt_woq_repack_weight(unpacked.data_ptr(), n, k, out.data_ptr(), _stream_ptr()))
+    return out
+
+
+def woq_repack_from_int4pack(packed):
+    import torch
+    n, k_half = packed.shape
+    out = torch.empty(n, k_half // 4, dtype=torch.int32, device=packed.device)
+    check(lib().zt_woq_repack_from_int4pack(packed.data_ptr(), n, k_half, out.data_ptr(), _stream_ptr()))
+    return out
+
+
+def dynamic_quantize(x, act_quant=ZT_ACT_S8_SYM):
+    import torch
+    m, k = x.shape
+    q = torch.empty(m, k, dtype=torch.uint8 if act_quant == ZT_ACT_U8_ASYM else torch.int8, device=x.device)
+    s = torch.empty(m, dtype=torch.float32, device=x.device)
+    zp = torch.zeros(m, dtype=torch.int32, device=x.device)
+    check(lib().zt_dynamic_quantize(x.data_ptr(), _dtype_code(x), m, k, act_quant, q.data_ptr(), s.data_ptr(),
+                                    zp.data_ptr(), _stream_ptr()))
+    return q, s, zp
+
+
+def int8_gemm_s32(q, w, algo=ZT_ALGO_AUTO):
+    import torch
+    m, k = q.shape
+    n = w.shape[0]
+    acc = torch.empty(m, n, dtype=torch.int32, device=q.device)
+    check(lib().zt_int8_gemm_s32(q.data_ptr(), 1 if q.dtype == torch.uint8 else 0, w.data_ptr(), m, n, k,
+                                 acc.data_ptr(), algo, _stream_ptr()))
+    return acc
+
+
+def int8_weight_rowsum(w):
+    import torch
+    n, k = w.shape
+    out = torch.empty(n, dtype=torch.int32, device=w.device)
+    check(lib().zt_int8_weight_rowsum(w.data_ptr(), n, k, out.data_ptr(), _stream_ptr()))
+    return out
+
+
+def dynamic_qlinear(x, w, w_scales, bias=None, act_quant=ZT_ACT_S8_SYM, post_ops=(), buffers=(), w_rowsum=None,
+                    algo=ZT_ALGO_AUTO):
+    import torch
+    m, k = x.shape
+    n = w.shape[0]
+    y = torch.empty(m, n, dtype=x.dtype, device=x.device)
+    nbytes = lib().zt_dynamic_qlinear_workspace_bytes(m, k)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    if act_quant == ZT_ACT_U8_ASYM and w_rowsum is None:
+        w_rowsum = int8_weight_rowsum(w)
+    a = DynamicQLinearArgs()
+    a.x, a.x_dtype, a.M, a.K, a.N = x.data_ptr(), _dtype_code(x), m, k, n
+    a.w, a.w_scales, a.w_scale_dtype = w.data_ptr(), w_scales.data_ptr(), _dtype_code(w_scales)
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.bias_dtype = _dtype_code(bias) if bias is not None else ZT_F32
+    a.act_quant = act_quant
+    a.w_rowsum = w_rowsum.data_ptr() if w_rowsum is not None else None
+    a.post = _post(post_ops, buffers)
+    a.y, a.workspace, a.workspace_bytes, a.algo = y.data_ptr(), ws.data_ptr(), nbytes, algo
+    check(lib().zt_dynamic_qlinear(C.byref(a), _stream_ptr()))
+    return y
