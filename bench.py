@@ -1,0 +1,433 @@
+#!/usr/bin/env python
+"""Benchmark of the zentorch quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE config 2): dynamic int8 linear, x bf16 [512, 4096] ~ N(0,1) quantised per token
+at run time, W int8 [11008, 4096] (per-channel scales), fp32 bias, fused SiLU.  Metric: achieved
+int8 TOP/s = 2*M*N*K / time.  One "step" is one pass over a batch of CALLS_PER_STEP such linears
+(each call = the per-token quantisation kernel + the tcgen05 GEMM with fused epilogue), rotating
+over operand sets whose total size exceeds L2 so that no call finds its weights cached.
+
+The JSON line carries, besides the driver contract's keys:
+  roofline       the tcgen05 GEMM kernel alone against the tensor roofline
+  woq_decode     the weight-only int4 GEMV (config 1, M=1) against the HBM roofline
+  cpu_baseline   the CPU oracle (torch CPU kernels) timed on this box's host cores
+  e2e            the same metric through torch.ops.zentorch with host buffers (pinned H2D of x,
+                 D2H of y inside the timed region)
+With N > 1 (torchrun) every rank runs the same workload on its own batch (data-parallel replicas,
+no collective on the data path) and the value is the sum over ranks: weak scaling.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (ROOT / "zendnn-pytorch-plugin_b200", ROOT / "oracle", ROOT / "tests"):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+M, K, N = 512, 4096, 11008
+CALLS_PER_STEP = 256
+OPS_PER_CALL = 2.0 * M * N * K
+L2_BYTES = 126 * 1024 * 1024
+METRIC = "dynamic int8 qlinear (u8 per-token act x s8 per-channel weight, fused SiLU) achieved TOP/s"
+
+
+def peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.samples, self.proc, self.thread = [], None, None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, reasons, smax = [], set(), None
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                smax = float(s[1])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": smax, "reasons": [], "samples": 0}
+        busy = [v for v in sm if v >= 0.5 * max(sm)]
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_operands(torch, device, seed):
+    """One operand set of config 2, generated on the CPU from a seed and copied to the device."""
+    from _util import make_int8_case
+    x, w, ws, b = make_int8_case(M, K, N, seed=seed)
+    return x, w, ws, b
+
+
+def time_region(torch, fn, reps):
+    """CUDA-event time in ms of `reps` back-to-back invocations of fn on the current stream."""
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(reps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import zentorch_b200
+    from zentorch_b200 import _capi
+    import ctypes as C
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert zentorch_b200.is_supported_device(), "bench.py needs an sm_100 GPU; there is no fallback path"
+    pk = peaks()
+    lib = _capi.lib()
+
+    # ---- operands: enough distinct sets that the rotation exceeds L2 ---------------------------------
+    set_bytes = N * K + M * K * 2 + M * N * 2
+    n_sets = max(4, -(-int(1.5 * L2_BYTES) // set_bytes))
+    x0, w0, ws0, b0 = make_operands(torch, dev, seed=rank)
+    sets = []
+    for i in range(n_sets):
+        xs = x0.roll(i, 0).contiguous().to(dev)
+        wsd = w0.roll(i, 0).contiguous().to(dev)
+        sets.append({
+            "x": xs, "w": wsd, "ws": ws0.roll(i, 0).contiguous().to(dev), "b": b0.roll(i, 0).contiguous().to(dev),
+            "rowsum": _capi.int8_weight_rowsum(wsd), "y": torch.empty(M, N, dtype=torch.bfloat16, device=dev),
+            "ws_buf": torch.empty(lib.zt_dynamic_qlinear_workspace_bytes(M, K), dtype=torch.uint8, device=dev),
+        })
+    stream = torch.cuda.Stream()
+    sptr = C.c_void_p(stream.cuda_stream)
+    SILU = 4
+
+    def args_for(s, act, post):
+        return _capi.dynamic_qlinear_args(s["x"], s["w"], s["ws"], s["b"], act, post, (), s["rowsum"], s["y"], s["ws_buf"],
+                                          _capi.ZT_ALGO_AUTO)
+
+    arg_u8 = [args_for(s, _capi.ZT_ACT_U8_ASYM, (SILU,)) for s in sets]
+    arg_s8 = [args_for(s, _capi.ZT_ACT_S8_SYM, ()) for s in sets]
+
+    def one_pass(arglist):
+        for i in range(CALLS_PER_STEP):
+            _capi.check(lib.zt_dynamic_qlinear(C.byref(arglist[i % n_sets]), sptr))
+
+    def capture(body):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            body()
+            stream.synchronize()
+            with torch.cuda.graph(g, stream=stream):
+                body()
+        return g
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    with torch.cuda.stream(stream):
+        graph_u8 = capture(lambda: one_pass(arg_u8))
+        graph_s8 = capture(lambda: one_pass(arg_s8))
+        for _ in range(max(args.warmup, 3)):
+            graph_u8.replay()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = time_region(torch, graph_u8.replay, args.steps)
+        if world > 1:
+            dist.barrier()
+        t = torch.tensor([ms], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_max = float(t.item())
+        for _ in range(3):
+            graph_s8.replay()
+        ms_s8 = time_region(torch, graph_s8.replay, args.steps)
+
+        # ---- roofline of the dominant kernel: the tcgen05 GEMM alone ---------------------------------
+        pre = []
+        for s in sets:
+            q, sc, zp = _capi.dynamic_quantize(s["x"], _capi.ZT_ACT_U8_ASYM)
+            pre.append((q, sc, zp))
+
+        def gemm_pass():
+            for i in range(CALLS_PER_STEP):
+                q, sc, zp = pre[i % n_sets]
+                _capi.check(lib.zt_qlinear_prequantized(C.byref(arg_u8[i % n_sets]), q.data_ptr(), sc.data_ptr(),
+                                                        zp.data_ptr(), sptr))
+
+        def quant_pass():
+            for i in range(CALLS_PER_STEP):
+                s = sets[i % n_sets]
+                q, sc, zp = pre[i % n_sets]
+                _capi.check(lib.zt_dynamic_quantize(s["x"].data_ptr(), _capi.ZT_BF16, M, K, _capi.ZT_ACT_U8_ASYM,
+                                                    q.data_ptr(), sc.data_ptr(), zp.data_ptr(), sptr))
+
+        graph_gemm, graph_quant = capture(gemm_pass), capture(quant_pass)
+        for _ in range(3):
+            graph_gemm.replay()
+            graph_quant.replay()
+        ms_gemm = time_region(torch, graph_gemm.replay, args.steps) / (args.steps * CALLS_PER_STEP)
+        ms_quant = time_region(torch, graph_quant.replay, args.steps) / (args.steps * CALLS_PER_STEP)
+
+        # ---- weight-only int4 decode GEMV (config 1, M = 1), HBM-bound ---------------------------------
+        woq = bench_woq_decode(torch, _capi, lib, dev, stream, sptr, args.steps, pk) if rank == 0 else None
+
+    # ---- end to end through torch.ops with host buffers ---------------------------------------------------
+    e2e = bench_e2e(torch, dev, sets, args.steps, world)
+    clocks = sampler.stop() if rank == 0 else None
+    torch.cuda.synchronize()
+    status = _capi.poll_device_status()
+    assert status == 0, f"a kernel reported a bounded-wait timeout (code {status})"
+
+    total_calls = args.steps * CALLS_PER_STEP
+    value = world * total_calls * OPS_PER_CALL / (ms_max * 1e-3) / 1e12
+    if world > 1:
+        te = torch.tensor([e2e["ms"]], device=dev)
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e["ms"] = float(te.item())
+    e2e_value = world * args.steps * OPS_PER_CALL / (e2e["ms"] * 1e-3) / 1e12
+
+    if rank == 0:
+        int8_peak = 2.0 * pk["bf16_tflops"]
+        cpu = cpu_baseline_sample()
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": "TOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_max / args.steps, 5), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "s8/u8 x s8 -> s32, fp32 epilogue", "data": "synthetic",
+            "config": {
+                "workload": f"BASELINE config 2: dynamic int8 linear M={M} K={K} N={N}, per-token u8 asymmetric "
+                            "activations, per-channel s8 weights, fp32 bias, fused SiLU",
+                "calls_per_step": CALLS_PER_STEP,
+                "l2": f"rotating over {n_sets} operand sets ({n_sets * set_bytes / 2**20:.0f} MiB > L2)",
+                "parallelism": f"dp{world} (independent batches per GPU, no collective on the data path)",
+                "launch": "CUDA graph of one step",
+            },
+            "variants": {
+                "s8_symmetric_no_postop (the reference op zentorch_dynamic_qlinear)": {
+                    "value": round(total_calls * OPS_PER_CALL / (ms_s8 * 1e-3) / 1e12, 2), "unit": "TOP/s"},
+                "quant_kernel_us": round(ms_quant * 1e3, 3), "gemm_kernel_us": round(ms_gemm * 1e3, 3),
+            },
+            "roofline": {
+                "kernel": "int8_tcgen05_kernel", "bound": "tensor",
+                "achieved": round(OPS_PER_CALL / (ms_gemm * 1e-3) / 1e12, 2), "peak": round(int8_peak, 1),
+                "unit": "TOP/s", "frac": round(OPS_PER_CALL / (ms_gemm * 1e-3) / 1e12 / int8_peak, 4),
+                "peak_note": f"2 x cuBLAS bf16 burst ({pk['bf16_tflops']} TF/s, {pk['source']}): kind::i8 issues at "
+                             "twice the kind::f16 rate",
+                "traffic": None,
+            },
+            "woq_decode": woq,
+            "cpu_baseline": cpu,
+            "e2e": {"value": round(e2e_value, 3), "unit": "TOP/s", "h2d_bytes_per_step": e2e["h2d"],
+                    "d2h_bytes_per_step": e2e["d2h"], "calls_per_step": 1,
+                    "api": "torch.ops.zentorch.zentorch_dynamic_qlinear_ext(act_quant='u8_asym', post_op='silu')"},
+            "gpu_launches": total_calls * 2,
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def bench_woq_decode(torch, _capi, lib, dev, stream, sptr, steps, pk):
+    """Config 1 at M = 1: y = x[1,4096] . dq(W)[4096,4096] + bias, int4 weights with fp32 scales per
+    group of 128.  Rotates over enough weight copies to exceed L2; reports algorithmic GB/s."""
+    import ctypes as C
+    from _util import make_woq_case
+    m, k, n, gs = 1, 4096, 4096, 128
+    x, q, s, _, b = make_woq_case(m, k, n, gs, seed=0)
+    alg_bytes = n * k // 2 + (k // gs) * n * 4 + m * k * 2 + m * n * 2 + n * 2
+    copies = -(-int(2.0 * L2_BYTES) // (n * k // 2 + (k // gs) * n * 4))
+    packed0 = _capi.woq_repack_weight(q.to(dev))
+    xs, bs = x.to(dev), b.to(dev)
+    ws = _capi.woq_workspace(lib.zt_woq_linear_workspace_bytes(m, n, k), dev)
+    arglist, keep = [], []
+    for i in range(copies):
+        wq = packed0.clone()
+        sc = s.to(dev).clone()
+        y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        a = _capi.WoqLinearArgs()
+        a.x, a.M, a.K, a.N = xs.data_ptr(), m, k, n
+        a.wq, a.scales, a.zeros = wq.data_ptr(), sc.data_ptr(), None
+        a.scale_dtype, a.n_groups = _capi.ZT_F32, k // gs
+        a.bias, a.bias_dtype = bs.data_ptr(), _capi.ZT_BF16
+        a.y, a.workspace, a.workspace_bytes, a.algo = y.data_ptr(), ws.data_ptr(), ws.numel(), _capi.ZT_ALGO_AUTO
+        arglist.append(a)
+        keep.append((wq, sc, y))
+
+    def one_pass():
+        for a in arglist:
+            _capi.check(lib.zt_woq_linear(C.byref(a), sptr))
+
+    g = torch.cuda.CUDAGraph()
+    one_pass()
+    stream.synchronize()
+    with torch.cuda.graph(g, stream=stream):
+        one_pass()
+    for _ in range(3):
+        g.replay()
+    reps = max(steps, 10)
+    ms = time_region(torch, g.replay, reps) / (reps * copies)
+    gbs = alg_bytes / (ms * 1e-3) / 1e9
+    return {"workload": "BASELINE config 1: WOQ int4 (group 128, fp32 scales) M=1 K=4096 N=4096, bf16 bias",
+            "kernel": "woq_skinny_kernel", "bound": "hbm", "us_per_call": round(ms * 1e3, 3),
+            "algorithmic_bytes": alg_bytes, "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+            "frac": round(gbs / pk["hbm_gbs"], 4), "peak_note": f"STREAM-style copy, {pk['source']}",
+            "l2": f"rotating over {copies} weight copies", "launch": "CUDA graph, back-to-back"}
+
+
+def bench_e2e(torch, dev, sets, steps, world):
+    """The user-facing call with host buffers: pinned x -> device, op, y -> pinned host, every step."""
+    ops = torch.ops.zentorch
+    s = sets[0]
+    x_host = s["x"].cpu().pin_memory()
+    y_host = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty_like(s["x"])
+
+    def step(i):
+        st = sets[i % len(sets)]
+        x_dev.copy_(x_host, non_blocking=True)
+        y = ops.zentorch_dynamic_qlinear_ext(x_dev, st["w"], st["ws"], st["b"], st["rowsum"], act_quant="u8_asym",
+                                             post_op="silu")
+        y_host.copy_(y, non_blocking=True)
+
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        step(i)
+    end.record()
+    torch.cuda.synchronize()
+    return {"ms": start.elapsed_time(end), "h2d": M * K * 2, "d2h": M * N * 2}
+
+
+def cpu_oracle_call():
+    """The reference's CPU path is not installable here (its kernels live in ZenDNN, fetched from the
+    network at build time), so the timed CPU arm is the oracle port on stock torch CPU kernels."""
+    import torch
+    import zentorch_oracle as O
+    from _util import make_int8_case
+    x, w, ws, b = make_int8_case(M, K, N, seed=0)
+    torch.set_num_threads(os.cpu_count() or 1)
+
+    def call():
+        return O.dynamic_qlinear(x, w, ws, b, act_quant="u8_asym", post_ops=[O.POST_SILU])
+    return call
+
+
+def cpu_baseline_sample():
+    import torch
+    call = cpu_oracle_call()
+    call()
+    n = 5
+    t0 = time.perf_counter()
+    for _ in range(n):
+        call()
+    dt = (time.perf_counter() - t0) / n
+    return {"value": round(OPS_PER_CALL / dt / 1e12, 4), "unit": "TOP/s", "cores": torch.get_num_threads(),
+            "kind": "port", "sample": f"{n} full calls of the config-2 linear (1 warm-up), {dt * 1e3:.1f} ms each",
+            "note": "oracle port on torch CPU kernels (row-wise quantise + torch._int_mm + fp32 epilogue); "
+                    "zentorch's own CPU path is unavailable on this box"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    import torch
+    call = cpu_oracle_call()
+    for _ in range(max(args.warmup, 1)):
+        call()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        call()
+    dt = time.perf_counter() - t0
+    value = args.steps * OPS_PER_CALL / dt / 1e12
+    sample = f"{args.steps} steps of one full config-2 call each"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": "TOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(dt / args.steps * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8/u8 x s8 -> s32, fp32 epilogue",
+        "data": "synthetic",
+        "config": {"workload": f"BASELINE config 2: dynamic int8 linear M={M} K={K} N={N}, per-token u8 asymmetric "
+                               "activations, per-channel s8 weights, fp32 bias, fused SiLU", "calls_per_step": 1,
+                   "parallelism": "host cores of rank 0"},
+        "cpu_baseline": {"value": round(value, 4), "unit": "TOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample,
+                         "note": "oracle port on torch CPU kernels; zentorch's own CPU path (ZenDNN) cannot be "
+                                 "built or installed here"},
+        "e2e": {"value": round(value, 4), "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -65,6 +65,9 @@ typedef enum {
   ZT_ALGO_SKINNY = 2,  /* small M, HBM-bound streaming kernel */
   ZT_ALGO_TCGEN05 = 3  /* large M, tcgen05 tensor cores with TMEM accumulators */
 } zt_algo_t;
+/* An `algo` argument may carry a tile-width hint for the tcgen05 kernels in bits 8..23 (0 = choose);
+ * tests and benchmarks use it to exercise every compiled tile shape. */
+#define ZT_ALGO_WITH_TILE(algo, tile_n) ((int32_t)(algo) | ((int32_t)(tile_n) << 8))
 
 ZT_API const char *zt_last_error(void);
 ZT_API const char *zt_version(void);
@@ -168,6 +171,13 @@ ZT_API int zt_dynamic_qlinear(const zt_dynamic_qlinear_args_t *args, void *strea
  * (s8) or uint8 (u8); scales [M] fp32; zero_points [M] int32 (u8 mode only, else may be NULL). */
 ZT_API int zt_dynamic_quantize(const void *x, int32_t x_dtype, int64_t M, int64_t K, int32_t act_quant, void *q,
                                float *scales, int32_t *zero_points, void *stream);
+
+/* The second phase on its own: the int8 GEMM with the scale/bias/post-op epilogue, on activations
+ * that were quantised before (by zt_dynamic_quantize).  `args->x` is ignored; x_dtype still names the
+ * output dtype; `q` is [M,K] s8/u8 per args->act_quant, `src_scales` [M] fp32, `src_zero_points` [M]
+ * int32 (u8 mode).  No workspace is needed. */
+ZT_API int zt_qlinear_prequantized(const zt_dynamic_qlinear_args_t *args, const void *q, const float *src_scales,
+                                   const int32_t *src_zero_points, void *stream);
 
 /* The second phase without its epilogue: acc[M,N] = q[M,K] . W[N,K]^T in exact int32.  Exposed so
  * that the accumulators can be compared bit for bit. */

@@ -215,12 +215,18 @@ def dynamic_quantize_u8(x2: torch.Tensor):
 
 
 def int_gemm(q: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """Exact int32 accumulation of q [M, K] (int8/uint8) against w [N, K] int8."""
+    """Exact int32 accumulation of q [M, K] (int8/uint8) against w [N, K] int8.  Large signed cases
+    use torch's CPU int8 GEMM; unsigned activations are shifted by 128 into the signed range and the
+    shift is put back with the weight row sums (both steps exact in integers)."""
     m, k = q.shape
-    if q.dtype == torch.int8 and m > 16 and k % 8 == 0 and w.shape[0] % 8 == 0:
+    if q.dtype == torch.uint8:
+        if m > 16 and k % 8 == 0 and w.shape[0] % 8 == 0:
+            shifted = (q.to(torch.int16) - 128).to(torch.int8)
+            return int_gemm(shifted, w) + 128 * w.sum(dim=1, dtype=torch.int32).unsqueeze(0)
+        return (q.long() @ w.long().t()).to(torch.int32)
+    if m > 16 and k % 8 == 0 and w.shape[0] % 8 == 0:
         return torch._int_mm(q.contiguous(), w.t().contiguous())
-    return (q.to(torch.int32).double() @ w.to(torch.int32).double().t()).round().to(torch.int32) \
-        if k < (1 << 20) else (q.long() @ w.long().t()).to(torch.int32)
+    return (q.long() @ w.long().t()).to(torch.int32)
 
 
 def dynamic_qlinear(x: torch.Tensor, weight: torch.Tensor, weight_scales: torch.Tensor,
@@ -248,8 +254,8 @@ def dynamic_qlinear(x: torch.Tensor, weight: torch.Tensor, weight_scales: torch.
         accf = acc.float()
     elif act_quant == "u8_asym":
         q, s, zp = dynamic_quantize_u8(x2)
-        acc = (q.long() @ weight.long().t()).to(torch.int32)
-        wsum = weight.long().sum(dim=1)                                 # [N]
+        acc = int_gemm(q, weight)
+        wsum = weight.sum(dim=1, dtype=torch.int64)                     # [N]
         accf = (acc.long() - zp.long().unsqueeze(1) * wsum.unsqueeze(0)).float()
     else:
         raise RuntimeError(f"unknown act_quant {act_quant}")

@@ -1,0 +1,105 @@
+"""Host-side checks that need no GPU: the C-ABI library loads, exports every symbol the header
+declares, validates arguments before touching the device, and the torch boundary registers the
+reference's schemas with meta kernels."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_symbols():
+    text = (ROOT / "include" / "zentorch_b200.h").read_text()
+    return sorted(set(re.findall(r"ZT_API[^;(]*?\b(zt_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(zt):
+    from zentorch_b200 import _capi
+    lib = _capi.lib()
+    declared = _declared_symbols()
+    assert len(declared) >= 12
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/zentorch_b200.h but not exported"
+    assert sorted(_capi.EXPORTED_SYMBOLS) == declared
+
+
+def test_aoti_shims_exported(zt):
+    lib = C.CDLL(str(ROOT / "zendnn-pytorch-plugin_b200" / "lib" / "libzentorch_b200_torch.so"))
+    for suffix in ("", "_relu", "_sigmoid", "_gelu_tanh", "_gelu_erf", "_add", "_mul_add", "_add_add"):
+        assert hasattr(lib, f"aoti_torch_cuda_zentorch_woq_linear{suffix}")
+    assert hasattr(lib, "aoti_torch_cuda_zentorch_dynamic_qlinear")
+    text = (ROOT / "include" / "shim_cuda_zentorch.h").read_text()
+    for name in re.findall(r"\b(aoti_torch_cuda_zentorch_\w+)\s*\(", text):
+        assert hasattr(lib, name), name
+
+
+def test_argument_validation_precedes_device_work(zt):
+    from zentorch_b200 import _capi
+    lib = _capi.lib()
+    assert lib.zt_version().startswith(b"zentorch_b200")
+    one = C.c_void_p(16)  # never dereferenced: validation fails first
+    assert lib.zt_woq_repack_weight(one, 4, 12, one, None) == 1
+    assert b"K must be divisible by 8" in lib.zt_last_error()
+    assert lib.zt_woq_repack_weight(one, 4, 4, one, None) == 1
+    assert b"K must be at least 8" in lib.zt_last_error()
+    assert lib.zt_woq_repack_from_int4pack(one, 32, 16, one, None) == 1
+    assert b"multiple of 64" in lib.zt_last_error()
+    a = _capi.WoqLinearArgs()
+    a.M, a.K, a.N = 2, 20, 8
+    assert lib.zt_woq_linear(C.byref(a), None) == 1 and b"divisible by 8" in lib.zt_last_error()
+    a.K = 64
+    assert lib.zt_woq_linear(C.byref(a), None) == 1 and b"null tensor pointer" in lib.zt_last_error()
+    d = _capi.DynamicQLinearArgs()
+    d.M, d.K, d.N, d.x_dtype = 2, 8, 4, 7
+    assert lib.zt_dynamic_qlinear(C.byref(d), None) == 1
+    assert b"input must be bfloat16 or float32" in lib.zt_last_error()
+    assert lib.zt_woq_linear_workspace_bytes(1, 4096, 4096) >= _capi.ZT_WOQ_COUNTER_BYTES
+    assert lib.zt_dynamic_qlinear_workspace_bytes(512, 4096) >= 512 * 4096 + 2 * 512 * 4
+
+
+def test_schemas_match_the_reference(zt):
+    ops = torch.ops.zentorch
+    s = str(ops.zentorch_woq_linear.default._schema)
+    assert "Tensor input, Tensor weight, Tensor weight_scales, Tensor? weight_zero_points, Tensor? bias=None" in s
+    assert 'zentorch_op_name="zentorch::zentorch_woq_linear"' in s
+    for name in ("relu", "sigmoid", "gelu_tanh", "gelu_erf"):
+        assert getattr(ops, f"zentorch_woq_linear_{name}") is not None
+    assert "Tensor add_input, Tensor? bias=None" in str(ops.zentorch_woq_linear_add.default._schema)
+    assert "Tensor mul_input, Tensor add_input, Tensor? bias=None" in str(ops.zentorch_woq_linear_mul_add.default._schema)
+    assert "Tensor add_input, Tensor add_input_2, Tensor? bias=None" in str(ops.zentorch_woq_linear_add_add.default._schema)
+    assert torch.Tag.needs_contiguous_strides in ops.zentorch_woq_linear_add.default.tags
+    assert torch.Tag.needs_fixed_stride_order in ops.zentorch_woq_linear_mul_add.default.tags
+    assert torch.Tag.needs_fixed_stride_order in ops.zentorch_woq_linear_add_add.default.tags
+    d = str(ops.zentorch_dynamic_qlinear.default._schema)
+    assert "Tensor input, Tensor weight, Tensor weight_scales, Tensor? bias=None" in d
+
+
+def test_meta_kernels(zt):
+    ops = torch.ops.zentorch
+    x = torch.empty(2, 3, 64, dtype=torch.bfloat16, device="meta")
+    w = torch.empty(8, 48, dtype=torch.int32, device="meta")
+    s = torch.empty(1, 48, device="meta")
+    other = torch.empty(2, 3, 48, dtype=torch.bfloat16, device="meta")
+    assert ops.zentorch_woq_linear(x, w, s, None, None).shape == (2, 3, 48)
+    assert ops.zentorch_woq_linear_gelu_erf(x, w, s, None, None).dtype == torch.bfloat16
+    assert ops.zentorch_woq_linear_add(x, w, s, None, other).shape == (2, 3, 48)
+    assert ops.zentorch_woq_linear_mul_add(x, w, s, None, other, other).shape == (2, 3, 48)
+    assert ops.zentorch_woq_linear_add_add(x, w, s, None, other, other).shape == (2, 3, 48)
+    assert ops.zentorch_woq_repack_weight(torch.empty(48, 64, dtype=torch.int8, device="meta")).shape == (48, 8)
+    assert ops.zentorch_woq_repack_from_int4pack(torch.empty(64, 32, dtype=torch.uint8, device="meta")).shape == (64, 8)
+    xi = torch.empty(5, 16, device="meta")
+    wi = torch.empty(10, 16, dtype=torch.int8, device="meta")
+    out = ops.zentorch_dynamic_qlinear(xi, wi, torch.empty(10, device="meta"), None)
+    assert out.shape == (5, 10) and out.dtype == torch.float32
+
+
+def test_no_cpu_fallback(zt):
+    x = torch.zeros(4, 64, dtype=torch.bfloat16)
+    w = torch.zeros(32, 8, dtype=torch.int32).t()
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        torch.ops.zentorch.zentorch_woq_linear(x, w, torch.ones(1, 32), None, None)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        torch.ops.zentorch.zentorch_dynamic_qlinear(torch.zeros(2, 8), torch.zeros(4, 8, dtype=torch.int8), torch.ones(4), None)

@@ -1,0 +1,185 @@
+"""Parity of the weight-only int4 path on a B200 against the CPU oracle, through the C ABI."""
+import pytest
+import torch
+
+import zentorch_oracle as O
+from _util import assert_close_bf16, bf16_from_bits, make_woq_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def capi(zt):
+    from zentorch_b200 import _capi
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    assert _capi.lib().zt_device_supported() == 1, "GPU tests need an sm_100 device"
+    return _capi
+
+
+def _run(capi, x, q, scales, zeros, bias, algo, post_ops=(), buffers=()):
+    dev = "cuda"
+    packed = capi.woq_repack_weight(q.to(dev))                     # [N, K/8] on device
+    y = capi.woq_linear(x.to(dev), packed, scales.to(dev), None if zeros is None else zeros.to(dev),
+                        None if bias is None else bias.to(dev), post_ops, [b.to(dev) for b in buffers], algo=algo)
+    torch.cuda.synchronize()
+    return y.cpu(), packed.cpu()
+
+
+# ---- repack ops: bit-exact -------------------------------------------------------------------------
+def test_repack_weight_bit_exact(capi, golden):
+    for key in ("pack", "packu"):
+        w = torch.from_numpy(golden[f"{key}_in"])
+        got = capi.woq_repack_weight(w.cuda()).cpu()
+        assert torch.equal(got, torch.from_numpy(golden[f"{key}_out"]))
+    g = torch.Generator().manual_seed(5)
+    for n, k in ((1, 8), (3, 24), (48, 128), (1024, 4096)):
+        w = torch.randint(-8, 8, (n, k), generator=g, dtype=torch.int8)
+        assert torch.equal(capi.woq_repack_weight(w.cuda()).cpu(), O.woq_repack_weight(w))
+    with pytest.raises(capi.ZtError, match="K must be divisible by 8"):
+        capi.woq_repack_weight(torch.zeros(4, 12, dtype=torch.int8, device="cuda"))
+    with pytest.raises(capi.ZtError, match="K must be at least 8"):
+        capi.woq_repack_weight(torch.zeros(4, 4, dtype=torch.int8, device="cuda"))
+
+
+def test_repack_from_int4pack_bit_exact(capi, golden):
+    packed = torch.from_numpy(golden["int4pack_packed"])
+    expect = O.woq_repack_weight(torch.from_numpy(golden["int4pack_int_data"]))
+    assert torch.equal(capi.woq_repack_from_int4pack(packed.cuda()).cpu(), expect)
+    int_data = torch.randint(0, 16, (192, 1024), dtype=torch.int32)
+    p = torch.ops.aten._convert_weight_to_int4pack_for_cpu(int_data, 1)
+    assert torch.equal(capi.woq_repack_from_int4pack(p.cuda()).cpu(), O.woq_repack_weight(int_data.to(torch.int8)))
+    with pytest.raises(capi.ZtError, match="multiple of 64"):
+        capi.woq_repack_from_int4pack(torch.zeros(32, 16, dtype=torch.uint8, device="cuda"))
+
+
+# ---- the reference's own test grid: per-channel symmetric, tiny shapes (generic kernel) --------------------
+@pytest.mark.parametrize("n", [32, 48, 64])
+@pytest.mark.parametrize("k", [32, 64, 128])
+@pytest.mark.parametrize("m", [1, 4, 24])
+def test_reference_grid_per_channel(capi, m, k, n):
+    g = torch.Generator().manual_seed(m * 1000 + k + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = torch.randn(n, k, generator=g).to(torch.bfloat16)
+    s = torch.clamp(w.abs().max(dim=1, keepdim=True)[0] / 8, min=1e-8).float()
+    q = torch.clamp(torch.round(w / s), -8, 7).to(torch.int8)
+    bias = torch.randn(n, generator=g).to(torch.bfloat16)
+    scales = s.t().contiguous()
+    y, packed = _run(capi, x, q, scales, None, bias, capi.ZT_ALGO_AUTO)
+    ref = O.woq_linear(x, packed.t(), scales, None, bias)
+    # reference tolerance rtol = atol = 1e-3, or the same value up to one bf16 rounding step
+    close = torch.isclose(y.float(), ref.float(), rtol=1e-3, atol=1e-3)
+    one_ulp = (y.view(torch.int16).int() - ref.view(torch.int16).int()).abs() <= 1
+    assert (close | one_ulp).all()
+
+
+def test_golden_fixture_through_capi(capi, golden):
+    x = bf16_from_bits(golden["sym_x"]).reshape(-1, 128)
+    q = torch.from_numpy(golden["sym_q"])
+    scale = torch.from_numpy(golden["sym_scale"])
+    bias = bf16_from_bits(golden["sym_bias"])
+    y, _ = _run(capi, x, q, scale, None, bias, capi.ZT_ALGO_AUTO)
+    ref = bf16_from_bits(golden["sym_y"]).reshape(-1, 48)
+    one_ulp = (y.view(torch.int16).int() - ref.view(torch.int16).int()).abs() <= 1
+    assert (torch.isclose(y.float(), ref.float(), rtol=1e-3, atol=1e-3) | one_ulp).all()
+    # asymmetric fixture (truth: aten._weight_int4pack_mm_for_cpu); reference tolerance 0.1 / 2.0
+    xa = bf16_from_bits(golden["asym_x"])
+    packed = capi.woq_repack_from_int4pack(torch.from_numpy(golden["asym_int4pack"]).cuda())
+    sa, za = bf16_from_bits(golden["asym_scale"]), bf16_from_bits(golden["asym_zero"])
+    for algo in (capi.ZT_ALGO_GENERIC, capi.ZT_ALGO_SKINNY):
+        ya = capi.woq_linear(xa.cuda(), packed, sa.cuda(), za.cuda(), None, algo=algo).cpu()
+        refa = bf16_from_bits(golden["asym_y"])
+        assert torch.allclose(ya.float(), refa.float(), rtol=0.1, atol=2.0)
+        assert (ya.float() - refa.float()).abs().max() < 0.05
+
+
+# ---- streaming kernel: every M 1..17, group sizes, asymmetric, scale dtypes, ragged N ------------------------
+@pytest.mark.parametrize("m", list(range(1, 18)) + [31, 32, 33, 64])
+def test_skinny_every_m(capi, m):
+    x, q, s, z, b = make_woq_case(m, 512, 96, 128, seed=m)
+    y, packed = _run(capi, x, q, s, None, b, capi.ZT_ALGO_SKINNY)
+    assert_close_bf16(y, O.woq_linear(x, packed.t(), s, None, b), what=f"skinny M={m}")
+    # against the exact (un-rounded dq) product the kernel is much tighter than the tolerance
+    exact = O.woq_linear(x, packed.t(), s, None, b, dq_round=None)
+    assert_close_bf16(y, exact, rtol=8e-3, atol=4e-3, what=f"skinny M={m} vs exact")
+
+
+@pytest.mark.parametrize("asym", [False, True])
+@pytest.mark.parametrize("scale_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("k,gs,n", [(256, 128, 40), (1024, 256, 100), (2048, 2048, 33), (4096, 128, 1024)])
+def test_skinny_quant_modes(capi, asym, scale_dtype, k, gs, n):
+    x, q, s, z, b = make_woq_case(5, k, n, gs, seed=k + n, asym=asym, scale_dtype=scale_dtype)
+    for algo in (capi.ZT_ALGO_SKINNY, capi.ZT_ALGO_GENERIC):
+        y, packed = _run(capi, x, q, s, z, b, algo)
+        assert_close_bf16(y, O.woq_linear(x, packed.t(), s, z, b), what=f"algo {algo}")
+
+
+def test_generic_odd_shapes(capi):
+    for (m, k, n, gs) in ((3, 24, 7, 8), (2, 64, 5, 32), (9, 136, 17, 136), (1, 8, 1, 8)):
+        x, q, s, z, b = make_woq_case(m, k, n, gs, seed=k)
+        y, packed = _run(capi, x, q, s, None, b, capi.ZT_ALGO_AUTO)
+        assert_close_bf16(y, O.woq_linear(x, packed.t(), s, None, b), what=f"{m}x{k}x{n}")
+
+
+POST_CASES = {
+    "relu": ([O.POST_RELU], 0), "sigmoid": ([O.POST_SIGMOID], 0), "gelu_tanh": ([O.POST_GELU_TANH], 0),
+    "gelu_erf": ([O.POST_GELU_ERF], 0), "silu": ([O.POST_SILU], 0), "tanh": ([O.POST_TANH], 0),
+    "add": ([O.POST_ADD], 1), "mul_add": ([O.POST_MUL, O.POST_ADD], 2), "add_add": ([O.POST_ADD, O.POST_ADD], 2),
+}
+
+
+@pytest.mark.parametrize("name", sorted(POST_CASES))
+@pytest.mark.parametrize("algo_name", ["SKINNY", "GENERIC"])
+def test_post_ops(capi, name, algo_name):
+    ops, nbuf = POST_CASES[name]
+    m, k, n = 6, 256, 72
+    x, q, s, z, b = make_woq_case(m, k, n, 128, seed=3)
+    g = torch.Generator().manual_seed(9)
+    bufs = [torch.randn(m, n, generator=g).to(torch.bfloat16) for _ in range(nbuf)]
+    y, packed = _run(capi, x, q, s, None, b, getattr(capi, f"ZT_ALGO_{algo_name}"), ops, bufs)
+    assert_close_bf16(y, O.woq_linear(x, packed.t(), s, None, b, ops, bufs), what=name)
+
+
+# ---- benchmark shapes ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 1024), (14336, 4096)])
+def test_config_shapes_vs_oracle(capi, k, n):
+    """Projection shapes of the benchmark configs at M in {1, 8, 32, 64, 128}; the weight is
+    dequantised once on the CPU and shared by all M."""
+    _, q, s, z, b = make_woq_case(1, k, n, 128, seed=0)
+    packed = capi.woq_repack_weight(q.cuda())
+    assert torch.equal(packed.cpu(), O.woq_repack_weight(q))
+    dq = O.woq_dequant(q, s, None)                                   # [N, K] fp32, bf16-rounded
+    sd, bd = s.cuda(), b.cuda()
+    for m in (1, 8, 32, 64, 128):
+        x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(torch.bfloat16)
+        y = capi.woq_linear(x.cuda(), packed, sd, None, bd).cpu()
+        ref = (x.float() @ dq.t() + b.float()).to(torch.bfloat16)
+        assert_close_bf16(y, ref, what=f"M={m} K={k} N={n}")
+
+
+def test_full_size_linearity_and_checksum(capi):
+    """Llama-3-70B down projection (K=28672, N=8192) at M=32: size-independent properties instead of
+    a full CPU product.  (1) without bias the op is linear in x; (2) the sum of each output row equals
+    x[m,:] . (sum_n dq[:,n]), which needs only one pass over the weight on the CPU."""
+    m, k, n = 32, 28672, 8192
+    x, q, s, z, b = make_woq_case(m, k, n, 128, seed=1, bias=False)
+    dev = "cuda"
+    packed = capi.woq_repack_weight(q.to(dev))
+    sd = s.to(dev)
+    y1 = capi.woq_linear(x.to(dev), packed, sd).float()
+    x2 = torch.randn(m, k, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    y2 = capi.woq_linear(x2.to(dev), packed, sd).float()
+    xs = (x.float() + x2.float()).to(torch.bfloat16)
+    ys = capi.woq_linear(xs.to(dev), packed, sd).float()
+    # x + x2 is rounded to bf16 before the call: compare against the same rounded input's parts
+    resid = (xs.float() - x.float() - x2.float()).to(dev)
+    tol = 3e-2 * (y1.abs() + y2.abs()).mean() + 1e-2
+    assert ((ys - y1 - y2).abs().mean() < tol) and resid.abs().max() < 0.1
+    colsum = torch.zeros(k, dtype=torch.float64)
+    sg = s.double()
+    for n0 in range(0, n, 1024):
+        qq = q[n0:n0 + 1024].double().view(-1, k // 128, 128) * sg[:, n0:n0 + 1024].t().unsqueeze(2)
+        colsum += qq.view(-1, k).sum(dim=0)
+    expect = x.double() @ colsum
+    got = y1.double().sum(dim=1).cpu()
+    scale = y1.abs().sum(dim=1).double().cpu()
+    assert ((got - expect).abs() <= 4e-3 * scale + 0.5).all()

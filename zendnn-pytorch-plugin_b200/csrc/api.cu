@@ -171,7 +171,7 @@ extern "C" int zt_woq_linear(const zt_woq_linear_args_t *a, void *stream) {
   if (rc != ZT_SUCCESS) return rc;
   cudaStream_t st = (cudaStream_t)stream;
 
-  int algo = a->algo;
+  int algo = a->algo & 0xff;
   if (algo == ZT_ALGO_AUTO) {
     if (a->M <= env().woq_skinny_max && woq_skinny_supported(*a))
       algo = ZT_ALGO_SKINNY;
@@ -222,13 +222,15 @@ extern "C" int zt_dynamic_quantize(const void *x, int32_t x_dtype, int64_t M, in
 }
 
 namespace {
-int run_int8_gemm(Int8GemmArgs &g, int algo, cudaStream_t st) {
+int run_int8_gemm(Int8GemmArgs &g, int algo_and_tile, cudaStream_t st) {
+  int algo = algo_and_tile & 0xff;
+  const int tile_hint = (algo_and_tile >> 8) & 0xffff;
   if (algo == ZT_ALGO_AUTO || algo == ZT_ALGO_SKINNY)
     algo = int8_tcgen05_supported(g.M, g.N, g.K, g.q, g.w) ? ZT_ALGO_TCGEN05 : ZT_ALGO_GENERIC;
   if (algo == ZT_ALGO_TCGEN05) {
     ZT_REQUIRE(int8_tcgen05_supported(g.M, g.N, g.K, g.q, g.w), ZT_UNSUPPORTED,
                "int8 tcgen05 kernel needs K %% 16 == 0 and 16-byte aligned operands");
-    g.force_bn = env().int8_bn;
+    g.force_bn = tile_hint ? tile_hint : env().int8_bn;
     return int8_tcgen05_launch(g, st);
   }
   if (algo == ZT_ALGO_GENERIC) return int8_generic_launch(g, st);
@@ -284,6 +286,23 @@ extern "C" int zt_dynamic_qlinear(const zt_dynamic_qlinear_args_t *a, void *stre
   const bool u8 = a->act_quant == ZT_ACT_U8_ASYM;
   rc = dynamic_quantize_launch(a->x, a->x_dtype, a->M, a->K, a->act_quant, q, scales, zps, st);
   if (rc != ZT_SUCCESS) return rc;
+  return zt_qlinear_prequantized(a, q, scales, zps, stream);
+}
+
+extern "C" int zt_qlinear_prequantized(const zt_dynamic_qlinear_args_t *a, const void *q, const float *src_scales,
+                                       const int32_t *src_zero_points, void *stream) {
+  ZT_REQUIRE(a != nullptr, ZT_INVALID_ARGUMENT, "zt_qlinear_prequantized: null argument block");
+  ZT_REQUIRE(a->M >= 0 && a->N >= 0 && a->K >= 0, ZT_INVALID_ARGUMENT, "zt_qlinear_prequantized: negative size");
+  ZT_REQUIRE(valid_dtype(a->x_dtype) && valid_dtype(a->w_scale_dtype) && (!a->bias || valid_dtype(a->bias_dtype)),
+             ZT_INVALID_ARGUMENT, "zt_qlinear_prequantized: dtypes must be float32 or bfloat16");
+  if (a->M == 0 || a->N == 0) return ZT_SUCCESS;
+  const bool u8 = a->act_quant == ZT_ACT_U8_ASYM;
+  ZT_REQUIRE(q && src_scales && a->w && a->w_scales && a->y, ZT_INVALID_ARGUMENT,
+             "zt_qlinear_prequantized: null tensor pointer");
+  ZT_REQUIRE(!u8 || (src_zero_points && a->w_rowsum), ZT_INVALID_ARGUMENT,
+             "zt_qlinear_prequantized: the u8 mode needs zero points and w_rowsum");
+  int rc = validate_post_ops(a->post);
+  if (rc != ZT_SUCCESS) return rc;
   Int8GemmArgs g{};
   g.q = q;
   g.q_is_u8 = u8;
@@ -292,8 +311,8 @@ extern "C" int zt_dynamic_qlinear(const zt_dynamic_qlinear_args_t *a, void *stre
   g.N = a->N;
   g.K = a->K;
   g.raw_s32 = false;
-  g.src_scale = scales;
-  g.src_zp = u8 ? zps : nullptr;
+  g.src_scale = src_scales;
+  g.src_zp = u8 ? src_zero_points : nullptr;
   g.w_scale = a->w_scales;
   g.w_scale_dtype = a->w_scale_dtype;
   g.w_rowsum = u8 ? a->w_rowsum : nullptr;
@@ -302,5 +321,5 @@ extern "C" int zt_dynamic_qlinear(const zt_dynamic_qlinear_args_t *a, void *stre
   g.y_dtype = a->x_dtype;
   g.y = a->y;
   g.post = to_dev(a->post);
-  return run_int8_gemm(g, a->algo, st);
+  return run_int8_gemm(g, a->algo, (cudaStream_t)stream);
 }

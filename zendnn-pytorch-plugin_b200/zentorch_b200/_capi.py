@@ -25,7 +25,7 @@ EXPORTED_SYMBOLS = (
     "zt_last_error", "zt_version", "zt_device_supported", "zt_poll_device_status",
     "zt_woq_linear_workspace_bytes", "zt_woq_linear", "zt_woq_repack_weight", "zt_woq_repack_from_int4pack",
     "zt_dynamic_qlinear_workspace_bytes", "zt_dynamic_qlinear", "zt_dynamic_quantize", "zt_int8_gemm_s32",
-    "zt_int8_weight_rowsum",
+    "zt_int8_weight_rowsum", "zt_qlinear_prequantized",
 )
 
 
@@ -88,6 +88,7 @@ def lib() -> C.CDLL:
                                       C.c_void_p, C.c_void_p, C.c_void_p]
     L.zt_int8_gemm_s32.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                    C.c_int32, C.c_void_p]
+    L.zt_qlinear_prequantized.argtypes = [C.POINTER(DynamicQLinearArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.zt_int8_weight_rowsum.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
     _lib = L
     return L
@@ -210,6 +211,24 @@ def int8_weight_rowsum(w):
     out = torch.empty(n, dtype=torch.int32, device=w.device)
     check(lib().zt_int8_weight_rowsum(w.data_ptr(), n, k, out.data_ptr(), _stream_ptr()))
     return out
+
+
+def dynamic_qlinear_args(x, w, w_scales, bias, act_quant, post_ops, buffers, w_rowsum, y, ws, algo):
+    """Fills the argument block of zt_dynamic_qlinear / zt_qlinear_prequantized from torch tensors."""
+    m, k = x.shape
+    n = w.shape[0]
+    a = DynamicQLinearArgs()
+    a.x, a.x_dtype, a.M, a.K, a.N = x.data_ptr(), _dtype_code(x), m, k, n
+    a.w, a.w_scales, a.w_scale_dtype = w.data_ptr(), w_scales.data_ptr(), _dtype_code(w_scales)
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.bias_dtype = _dtype_code(bias) if bias is not None else ZT_F32
+    a.act_quant = act_quant
+    a.w_rowsum = w_rowsum.data_ptr() if w_rowsum is not None else None
+    a.post = _post(post_ops, buffers)
+    a.y = y.data_ptr()
+    a.workspace, a.workspace_bytes = (ws.data_ptr(), ws.numel()) if ws is not None else (None, 0)
+    a.algo = algo
+    return a
 
 
 def dynamic_qlinear(x, w, w_scales, bias=None, act_quant=ZT_ACT_S8_SYM, post_ops=(), buffers=(), w_rowsum=None,
