@@ -5,17 +5,23 @@
 //
 // Both operands are K-major, so they go from global memory to shared memory with plain 2-D TMA tile
 // loads (128 bytes of K per row, 128-byte swizzle) and are consumed in place by
-// tcgen05.mma.kind::i8 (K = 32 per instruction, four per 128-byte k-block).  The int32 accumulator
-// tile of 128 x BN lives in tensor memory.  One CTA computes one 128 x BN output tile:
+// tcgen05.mma.kind::i8 (K = 32 per instruction, four per 128-byte k-block).  The kernel is
+// persistent: one CTA per SM walks over 128 x BN output tiles (tiles that share a weight column
+// block are adjacent in the order, so they run at the same time on neighbouring SMs and the weight
+// block is fetched from HBM once).  The int32 accumulator lives in tensor memory and is double
+// buffered, so the epilogue of tile i overlaps the main loop of tile i+1:
 //
-//   warp 0      TMA producer (one elected lane)
-//   warp 1      allocates tensor memory, issues the MMAs (one elected lane), frees tensor memory
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (lane == output row), scale, bias, post-op,
-//               cast, 16-byte stores
+//   warp 0      TMA producer (one lane): fills the shared-memory ring, across tile boundaries
+//   warp 1      allocates tensor memory, issues the MMAs (one lane), frees tensor memory
+//   warps 2..9  epilogue: tcgen05.ld the accumulator (lane == output row; two warps per 32-lane
+//               quarter, each taking every other 32-column chunk), scale, bias, post-op, cast,
+//               16-byte stores
 //
-// Shared-memory stages are recycled through full/empty mbarriers; tcgen05.commit releases a stage
-// when the MMAs that read it have finished.  Two CTAs fit on one SM (shared memory and tensor-memory
-// columns are sized for that), so one CTA's epilogue overlaps the other's main loop.
+// Ring stages are recycled through full/empty mbarriers (tcgen05.commit frees a stage when the MMAs
+// that read it retire); accumulator buffers through tmem_full/tmem_empty mbarriers.  Every wait is
+// bounded: on expiry the role records a status code and stops, the other roles run into their own
+// bounded waits, tensor memory is freed and the kernel returns.
+#include <algorithm>
 #include <mutex>
 #include <unordered_map>
 
@@ -28,12 +34,14 @@ namespace {
 
 constexpr int kBM = 128;
 constexpr int kBK = 128;  // bytes (= int8 elements) of K per stage
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + kEpiWarps * 32;
 
 enum EpiMode { kEpiS32 = 0, kEpiLinear = 1 };
 
 struct TcParams {
   int M, N, K;
+  int m_tiles, n_tiles;
   // epilogue
   const float *src_scale;  // [M]
   const int32_t *src_zp;   // [M] or null
@@ -52,32 +60,96 @@ struct SmemLayout {
   static constexpr int kBBytes = BN * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTileBytes = STAGES * kStageBytes;
-  static constexpr int kVecBytes = 3 * BN * 4;          // w_scale, bias, rowsum of the tile
-  static constexpr int kBarBytes = (2 * STAGES + 1) * 8 + 8;
+  static constexpr int kVecBytes = 2 * 3 * BN * 4;      // per accumulator buffer: w_scale, bias, rowsum
+  static constexpr int kBarBytes = (2 * STAGES + 4) * 8 + 8;
   static constexpr int kTotal = kTileBytes + kVecBytes + kBarBytes + 1024;  // + slack to align to 1024
 };
 
+// Scale, bias and post-op for 32 consecutive outputs of one row, then the store.
+template <int UNARY>
+__device__ __forceinline__ void finish_chunk(const TcParams &p, const uint32_t (&r)[32], float s_m, int zp_m,
+                                             const float *wscale, const float *bias, const int32_t *rowsum, int m,
+                                             int nb) {
+  float v[32];
+  if (p.src_zp) {
+    // u8 activations: remove zp_m * sum_k W[n,k].  |acc|, |zp*rowsum| and their difference are all
+    // bounded by 255 * 127 * K, which fits 32 bits for K <= 65536; longer rows take 64 bits.
+    if (p.K <= 65536) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (float)((int32_t)r[j] - zp_m * rowsum[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (float)((int64_t)(int32_t)r[j] - (int64_t)zp_m * rowsum[j]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = (float)(int32_t)r[j];
+  }
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = v[j] * (s_m * wscale[j]) + bias[j];
+  const int64_t base = (int64_t)m * p.N + nb;
+  if (UNARY >= 0) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = unary_post(v[j], UNARY);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (nb + j < p.N) v[j] = apply_post_ops(v[j], p.post, base + j, p.y_dtype);
+  }
+  const bool full = nb + 32 <= p.N;
+  if (p.y_dtype == ZT_BF16) {
+    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.y) + base;
+    if (full && (p.N & 7) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 o;
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+        __nv_bfloat162 t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+        __nv_bfloat162 t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        o.x = *reinterpret_cast<uint32_t *>(&t0);
+        o.y = *reinterpret_cast<uint32_t *>(&t1);
+        o.z = *reinterpret_cast<uint32_t *>(&t2);
+        o.w = *reinterpret_cast<uint32_t *>(&t3);
+        *reinterpret_cast<uint4 *>(dst + j) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else {
+    float *dst = reinterpret_cast<float *>(p.y) + base;
+    if (full && (p.N & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) dst[j] = v[j];
+    }
+  }
+}
+
 template <int BN, int STAGES, int EPI, bool A_SIGNED>
-__global__ void __launch_bounds__(kThreads) int8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                                                                const __grid_constant__ CUtensorMap tmap_b,
-                                                                const TcParams p) {
+__global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                   const __grid_constant__ CUtensorMap tmap_b,
+                                                                   const TcParams p) {
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ unsigned char smem_dyn[];
   // align on the shared-window address (what the descriptors and TMA see), not the generic one
   unsigned char *smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
-  float *s_wscale = reinterpret_cast<float *>(smem + L::kTileBytes);
-  float *s_bias = s_wscale + BN;
-  int32_t *s_rowsum = reinterpret_cast<int32_t *>(s_bias + BN);
+  float *s_vec = reinterpret_cast<float *>(smem + L::kTileBytes);  // [2][3][BN]
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + L::kTileBytes + L::kVecBytes);
   uint64_t *empty_bar = full_bar + STAGES;
-  uint64_t *accum_bar = empty_bar + STAGES;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum_bar + 1);
+  uint64_t *tmem_full = empty_bar + STAGES;   // [2]
+  uint64_t *tmem_empty = tmem_full + 2;       // [2]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
 
-  constexpr uint32_t kTmemCols = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
+  constexpr uint32_t kTmemCols = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN;
-  const int m0 = blockIdx.y * kBM;
   const int num_kb = (p.K + kBK - 1) / kBK;
+  const int total_tiles = p.m_tiles * p.n_tiles;
 
   if (threadIdx.x == 0) {
     tc::prefetch_tensormap(&tmap_a);
@@ -86,7 +158,10 @@ __global__ void __launch_bounds__(kThreads) int8_tcgen05_kernel(const __grid_con
       tc::mbar_init(&full_bar[s], 1);
       tc::mbar_init(&empty_bar[s], 1);
     }
-    tc::mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(&tmem_full[b], 1);
+      tc::mbar_init(&tmem_empty[b], kEpiWarps);
+    }
     tc::mbar_fence_init();
   }
   if (warp == 1) tc::tmem_alloc(tmem_slot, kTmemCols);
@@ -98,145 +173,150 @@ __global__ void __launch_bounds__(kThreads) int8_tcgen05_kernel(const __grid_con
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
-          tc::report_timeout(p.status, kStatusProducerTimeout);
-          break;
+      uint32_t it = 0;  // ring position, runs across tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.m_tiles) * kBM;
+        const int n0 = (tile / p.m_tiles) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
+            tc::report_timeout(p.status, kStatusProducerTimeout);
+            ok = false;
+            break;
+          }
+          unsigned char *a_dst = smem + s * L::kStageBytes;
+          unsigned char *b_dst = a_dst + L::kABytes;
+          tc::mbar_expect_tx(&full_bar[s], L::kStageBytes);
+          tc::tma_load_2d(a_dst, &tmap_a, &full_bar[s], kb * kBK, m0);
+          tc::tma_load_2d(b_dst, &tmap_b, &full_bar[s], kb * kBK, n0);
         }
-        unsigned char *a_dst = smem + s * L::kStageBytes;
-        unsigned char *b_dst = a_dst + L::kABytes;
-        tc::mbar_expect_tx(&full_bar[s], L::kStageBytes);
-        tc::tma_load_2d(a_dst, &tmap_a, &full_bar[s], kb * kBK, m0);
-        tc::tma_load_2d(b_dst, &tmap_b, &full_bar[s], kb * kBK, n0);
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = tc::instr_desc(2u, A_SIGNED ? 1u : 0u, 1u, kBM, BN);
+      uint32_t it = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!tc::mbar_wait(&full_bar[s], ph)) {
+      int local = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+        const uint32_t buf = local & 1;
+        const uint32_t use = (uint32_t)local >> 1;  // how many times this buffer was used before
+        if (ok && !tc::mbar_wait(&tmem_empty[buf], (use & 1) ^ 1)) {
           tc::report_timeout(p.status, kStatusMmaTimeout);
           ok = false;
-          break;
         }
         tc::fence_after_sync();
-        const uint32_t a_addr = smem_u32(smem + s * L::kStageBytes);
-        const uint64_t a_desc = tc::smem_desc_k_sw128(a_addr);
-        const uint64_t b_desc = tc::smem_desc_k_sw128(a_addr + L::kABytes);
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!tc::mbar_wait(&full_bar[s], ph)) {
+            tc::report_timeout(p.status, kStatusMmaTimeout);
+            ok = false;
+            break;
+          }
+          tc::fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * L::kStageBytes);
+          const uint64_t a_desc = tc::smem_desc_k_sw128(a_addr);
+          const uint64_t b_desc = tc::smem_desc_k_sw128(a_addr + L::kABytes);
 #pragma unroll
-        for (int k = 0; k < kBK / 32; ++k) {
-          // 32 bytes of K per instruction: advance both start addresses by 32 >> 4 = 2
-          tc::mma_i8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kBK / 32; ++k) {
+            // 32 bytes of K per instruction: advance both start addresses by 32 >> 4 = 2
+            tc::mma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc::mma_commit(&empty_bar[s]);
         }
-        tc::mma_commit(&empty_bar[s]);
+        // Arrive on the accumulator barrier in every case so that the epilogue never waits for a
+        // commit that will not come; after a timeout the result is garbage but the kernel ends.
+        tc::mma_commit(&tmem_full[buf]);
       }
-      // Arrive on the accumulator barrier in every case so that the epilogue never waits for a
-      // commit that will not come; after a timeout the result is garbage but the kernel ends.
-      tc::mma_commit(accum_bar);
     }
   } else {
-    // ---------------- epilogue warps (2..5) ----------------
-    const int et = threadIdx.x - 64;  // 0..127
-    if (EPI == kEpiLinear) {
-      for (int j = et; j < BN; j += 128) {
-        const int n = n0 + j;
-        const bool in = n < p.N;
-        s_wscale[j] = in ? load_as_float(p.w_scale, n, p.w_scale_dtype) : 0.f;
-        s_bias[j] = (in && p.bias) ? load_as_float(p.bias, n, p.bias_dtype) : 0.f;
-        s_rowsum[j] = (in && p.w_rowsum) ? p.w_rowsum[n] : 0;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
-    }
+    // ---------------- epilogue warps (2..9) ----------------
+    const int et = threadIdx.x - 64;           // 0..255
     const int quarter = warp & 3;              // TMEM lanes this warp may read: 32*quarter ..
+    const int parity = (warp - 2) >> 2;        // which 32-column chunks this warp takes
     const int row = quarter * 32 + lane;
-    const int m = m0 + row;
-    const bool row_ok = m < p.M;
-    float s_m = 0.f;
-    int zp_m = 0;
-    if (EPI == kEpiLinear && row_ok) {
-      s_m = p.src_scale[m];
-      if (p.src_zp) zp_m = p.src_zp[m];
-    }
-    if (!tc::mbar_wait(accum_bar, 0)) tc::report_timeout(p.status, kStatusEpilogueTimeout);
-    tc::fence_after_sync();
-    const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    // a single unary post-op is resolved once, outside the element loops
+    int unary = -1;
+    if (p.post.n_ops == 0) unary = ZT_POST_NONE;
+    else if (p.post.n_ops == 1 && p.post.ids[0] < ZT_POST_MUL) unary = p.post.ids[0];
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+      const int m0 = (tile % p.m_tiles) * kBM;
+      const int n0 = (tile / p.m_tiles) * BN;
+      const uint32_t buf = local & 1;
+      const uint32_t use = (uint32_t)local >> 1;
+      float *v_wscale = s_vec + buf * 3 * BN;
+      float *v_bias = v_wscale + BN;
+      int32_t *v_rowsum = reinterpret_cast<int32_t *>(v_bias + BN);
+      if (EPI == kEpiLinear) {
+        for (int j = et; j < BN; j += kEpiWarps * 32) {
+          const int n = n0 + j;
+          const bool in = n < p.N;
+          v_wscale[j] = in ? load_as_float(p.w_scale, n, p.w_scale_dtype) : 0.f;
+          v_bias[j] = (in && p.bias) ? load_as_float(p.bias, n, p.bias_dtype) : 0.f;
+          v_rowsum[j] = (in && p.w_rowsum) ? p.w_rowsum[n] : 0;
+        }
+      }
+      // All epilogue threads: the vectors of this tile are visible, and everybody has finished
+      // reading the vectors of the tile two back (same buffer).
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+      const int m = m0 + row;
+      const bool row_ok = m < p.M;
+      float s_m = 0.f;
+      int zp_m = 0;
+      if (EPI == kEpiLinear && row_ok) {
+        s_m = p.src_scale[m];
+        if (p.src_zp) zp_m = p.src_zp[m];
+      }
+      if (ok && !tc::mbar_wait(&tmem_full[buf], use & 1)) {
+        tc::report_timeout(p.status, kStatusEpilogueTimeout);
+        ok = false;
+      }
+      tc::fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 32) {
-      uint32_t r[32];
-      tc::tmem_ld_32x32b_x32(t_row + c, r);
-      tc::tmem_ld_wait();
-      const int nb = n0 + c;
-      if (!row_ok || nb >= p.N) {
-        // nothing to store for this lane; fall through to the reconvergence point below
-      } else if (EPI == kEpiS32) {
-        int32_t *dst = reinterpret_cast<int32_t *>(p.y) + (size_t)m * p.N + nb;
-        if (nb + 32 <= p.N && (p.N & 3) == 0) {
+      for (int c = parity * 32; c < BN; c += 64) {
+        uint32_t r[32];
+        tc::tmem_ld_32x32b_x32(t_row + c, r);
+        tc::tmem_ld_wait();
+        const int nb = n0 + c;
+        if (row_ok && nb < p.N) {
+          if (EPI == kEpiS32) {
+            int32_t *dst = reinterpret_cast<int32_t *>(p.y) + (size_t)m * p.N + nb;
+            if (nb + 32 <= p.N && (p.N & 3) == 0) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4 *>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-        } else {
-          #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (nb + j < p.N) dst[j] = (int32_t)r[j];
-        }
-      } else {
-        float v[32];
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<uint4 *>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float af;
-          if (p.src_zp) {  // u8 activations: remove zp_m * sum_k W[n,k]
-            af = (float)((int64_t)(int32_t)r[j] - (int64_t)zp_m * s_rowsum[c + j]);
-          } else {
-            af = (float)(int32_t)r[j];
-          }
-          v[j] = af * (s_m * s_wscale[c + j]) + s_bias[c + j];
-        }
-        const int64_t base = (int64_t)m * p.N + nb;
-        if (p.post.n_ops > 0) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (nb + j < p.N) v[j] = apply_post_ops(v[j], p.post, base + j, p.y_dtype);
-        }
-        const bool full = nb + 32 <= p.N;
-        if (p.y_dtype == ZT_BF16) {
-          __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.y) + base;
-          if (full && (p.N & 7) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 o;
-              __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-              __nv_bfloat162 t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-              __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-              __nv_bfloat162 t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-              o.x = *reinterpret_cast<uint32_t *>(&t0);
-              o.y = *reinterpret_cast<uint32_t *>(&t1);
-              o.z = *reinterpret_cast<uint32_t *>(&t2);
-              o.w = *reinterpret_cast<uint32_t *>(&t3);
-              *reinterpret_cast<uint4 *>(dst + j) = o;
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) dst[j] = (int32_t)r[j];
             }
           } else {
-            #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nb + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
-          }
-        } else {
-          float *dst = reinterpret_cast<float *>(p.y) + base;
-          if (full && (p.N & 3) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          } else {
-            #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nb + j < p.N) dst[j] = v[j];
+            const float *ws = v_wscale + c, *bs = v_bias + c;
+            const int32_t *rs = v_rowsum + c;
+            switch (unary) {
+              case ZT_POST_NONE: finish_chunk<ZT_POST_NONE>(p, r, s_m, zp_m, ws, bs, rs, m, nb); break;
+              case ZT_POST_RELU: finish_chunk<ZT_POST_RELU>(p, r, s_m, zp_m, ws, bs, rs, m, nb); break;
+              case ZT_POST_SILU: finish_chunk<ZT_POST_SILU>(p, r, s_m, zp_m, ws, bs, rs, m, nb); break;
+              case ZT_POST_GELU_TANH: finish_chunk<ZT_POST_GELU_TANH>(p, r, s_m, zp_m, ws, bs, rs, m, nb); break;
+              case ZT_POST_GELU_ERF: finish_chunk<ZT_POST_GELU_ERF>(p, r, s_m, zp_m, ws, bs, rs, m, nb); break;
+              default: finish_chunk<-1>(p, r, s_m, zp_m, ws, bs, rs, m, nb); break;
+            }
           }
         }
+        __syncwarp();  // the next tcgen05.ld is warp-collective
       }
-      __syncwarp();  // the next tcgen05.ld is warp-collective
+      // this warp has drained its part of the accumulator buffer
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&tmem_empty[buf]);
     }
   }
 
@@ -291,8 +371,13 @@ int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, 
     ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     configured = true;
   }
-  dim3 grid((unsigned)ceil_div(p.N, BN), (unsigned)ceil_div(p.M, kBM));
-  kern<<<grid, kThreads, L::kTotal, st>>>(ta, tb, p);
+  TcParams q = p;
+  q.m_tiles = ceil_div(p.M, kBM);
+  q.n_tiles = ceil_div(p.N, BN);
+  const int tiles = q.m_tiles * q.n_tiles;
+  const int sms = sm_count();
+  dim3 grid((unsigned)(tiles < sms ? tiles : sms));
+  kern<<<grid, kThreads, L::kTotal, st>>>(ta, tb, q);
   return launch_status("int8_tcgen05_kernel");
 }
 
@@ -305,20 +390,20 @@ int launch_bn(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, i
                   : launch_cfg<BN, STAGES, kEpiLinear, false>(ta, tb, p, st);
 }
 
-// Tile width: the candidate that minimises (waves over the SMs at two CTAs per SM) x (tile cost).
+// Tile width: the candidate that minimises (rounds over the SMs) x (time of one tile).  A tile's
+// main loop is bound by the tensor pipe (BN/2 cycles per 32-wide k-step) or, for narrow tiles, by
+// shared-memory reads of the 128-row A block that every instruction repeats (32 + BN/4 cycles).
 int pick_bn(int64_t M, int64_t N) {
   const int cands[] = {256, 224, 192, 160, 128, 96, 64};
-  const int64_t slots = 2LL * sm_count();
+  const int64_t sms = sm_count();
   const int64_t mt = ceil_div<int64_t>(M, kBM);
   double best = 1e30;
   int best_bn = 128;
   for (int bn : cands) {
     const int64_t tiles = mt * ceil_div<int64_t>(N, bn);
-    const int64_t waves = ceil_div<int64_t>(tiles, slots);
-    // per-tile cost ~ MMA time (prop. to bn) + fixed per-tile overhead; two co-resident CTAs share
-    // the tensor core, so a wave costs 2 tiles' worth of MMA time when more than sm_count tiles run.
-    const double per_wave = (tiles > slots / 2 ? 2.0 : 1.0) * (bn + 24.0);
-    const double cost = waves * per_wave;
+    const int64_t rounds = ceil_div<int64_t>(tiles, sms);
+    const double tile_cost = std::max(bn / 2.0, 32.0 + bn / 4.0) + 4.0;
+    const double cost = rounds * tile_cost;
     if (cost < best - 1e-9) {
       best = cost;
       best_bn = bn;
@@ -361,13 +446,13 @@ int int8_tcgen05_launch(const Int8GemmArgs &a, cudaStream_t st) {
   if (rc != ZT_SUCCESS) return rc;
   const bool sgn = !a.q_is_u8;
   switch (bn) {
-    case 256: return launch_bn<256, 2>(ta, tb, p, epi, sgn, st);
-    case 224: return launch_bn<224, 2>(ta, tb, p, epi, sgn, st);
-    case 192: return launch_bn<192, 2>(ta, tb, p, epi, sgn, st);
-    case 160: return launch_bn<160, 3>(ta, tb, p, epi, sgn, st);
-    case 128: return launch_bn<128, 3>(ta, tb, p, epi, sgn, st);
-    case 96: return launch_bn<96, 3>(ta, tb, p, epi, sgn, st);
-    case 64: return launch_bn<64, 4>(ta, tb, p, epi, sgn, st);
+    case 256: return launch_bn<256, 4>(ta, tb, p, epi, sgn, st);
+    case 224: return launch_bn<224, 4>(ta, tb, p, epi, sgn, st);
+    case 192: return launch_bn<192, 5>(ta, tb, p, epi, sgn, st);
+    case 160: return launch_bn<160, 6>(ta, tb, p, epi, sgn, st);
+    case 128: return launch_bn<128, 6>(ta, tb, p, epi, sgn, st);
+    case 96: return launch_bn<96, 7>(ta, tb, p, epi, sgn, st);
+    case 64: return launch_bn<64, 8>(ta, tb, p, epi, sgn, st);
     default: break;
   }
   set_error("int8_tcgen05_launch: unsupported tile width %d", bn);

@@ -12,6 +12,20 @@ struct WoqSkinnyPlan {
   size_t partial_bytes;
 };
 
+struct WoqStreamPlan {
+  int mt;      // 8-row activation blocks (1: M <= 8, 2: M <= 16)
+  int r;       // 16-column blocks per CTA
+  int kslice;  // k handled by one CTA
+  int nsplit;  // number of K-slices
+  size_t partial_bytes;
+};
+
+// Decode kernel (M <= 16).
+WoqStreamPlan woq_stream_plan(int64_t M, int64_t N, int64_t K);
+bool woq_stream_supported(const zt_woq_linear_args_t &a);
+int woq_stream_launch(const zt_woq_linear_args_t &a, cudaStream_t st);
+
+// Mid-size M (17..64 per launch) on mma.sync, weights re-read once per 64 rows.
 WoqSkinnyPlan woq_skinny_plan(int64_t M, int64_t N, int64_t K);
 bool woq_skinny_supported(const zt_woq_linear_args_t &a);
 int woq_skinny_launch(const zt_woq_linear_args_t &a, bool fold, cudaStream_t st);

@@ -146,10 +146,11 @@ int woq_generic_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
 using namespace zt;
 
 extern "C" int zt_woq_repack_weight(const int8_t *unpacked, int64_t N, int64_t K, int32_t *packed, void *stream) {
-  ZT_REQUIRE(unpacked && packed, ZT_INVALID_ARGUMENT, "zt_woq_repack_weight: null pointer");
   ZT_REQUIRE(N >= 0, ZT_INVALID_ARGUMENT, "zt_woq_repack_weight: N must be non-negative, got %lld", (long long)N);
   ZT_REQUIRE(K >= 8, ZT_INVALID_ARGUMENT, "K must be at least 8, got %lld", (long long)K);
   ZT_REQUIRE(K % 8 == 0, ZT_INVALID_ARGUMENT, "K must be divisible by 8, got %lld", (long long)K);
+  if (N == 0) return ZT_SUCCESS;
+  ZT_REQUIRE(unpacked && packed, ZT_INVALID_ARGUMENT, "zt_woq_repack_weight: null pointer");
   ZT_REQUIRE((reinterpret_cast<uintptr_t>(unpacked) & 7) == 0, ZT_INVALID_ARGUMENT,
              "zt_woq_repack_weight: unpacked weight must be 8-byte aligned");
   const int64_t words = N * (K / 8);
@@ -161,7 +162,6 @@ extern "C" int zt_woq_repack_weight(const int8_t *unpacked, int64_t N, int64_t K
 
 extern "C" int zt_woq_repack_from_int4pack(const uint8_t *int4pack, int64_t N, int64_t K_half, int32_t *packed,
                                            void *stream) {
-  ZT_REQUIRE(int4pack && packed, ZT_INVALID_ARGUMENT, "zt_woq_repack_from_int4pack: null pointer");
   ZT_REQUIRE(N % 64 == 0, ZT_INVALID_ARGUMENT, "packed_weight row count (%lld) must be a multiple of 64",
              (long long)N);
   const int64_t K = 2 * K_half;
@@ -169,6 +169,7 @@ extern "C" int zt_woq_repack_from_int4pack(const uint8_t *int4pack, int64_t N, i
   ZT_REQUIRE(K % 8 == 0, ZT_INVALID_ARGUMENT, "K must be divisible by 8, got %lld", (long long)K);
   const int64_t words = N * (K / 8);
   if (words == 0) return ZT_SUCCESS;
+  ZT_REQUIRE(int4pack && packed, ZT_INVALID_ARGUMENT, "zt_woq_repack_from_int4pack: null pointer");
   woq_repack_from_int4pack_kernel<<<(unsigned)ceil_div<int64_t>(words, 256), 256, 0, (cudaStream_t)stream>>>(
       int4pack, N, K, packed);
   return launch_status("woq_repack_from_int4pack_kernel");

@@ -1,4 +1,4 @@
-// Weight-only int4 linear for small M (decode): an HBM-bound streaming kernel.
+// Weight-only int4 linear for mid-size M (17..64 rows per launch) on mma.sync tensor cores.
 //
 // Work decomposition.  A CTA of four warps owns 32 output columns (= 32 rows of the N-major packed
 // weight) and one K-slice.  The warps take the slice's 128-wide k-steps round-robin.  Within a
@@ -312,8 +312,8 @@ int launch(const SkinnyParams &p, dim3 grid, size_t smem, cudaStream_t st) {
 
 template <int MT>
 int launch_mt(const SkinnyParams &p, bool asym, bool fold, dim3 grid, size_t smem, cudaStream_t st) {
-  if (asym) return fold ? launch<MT, true, true>(p, grid, smem, st) : launch<MT, true, false>(p, grid, smem, st);
-  return fold ? launch<MT, false, true>(p, grid, smem, st) : launch<MT, false, false>(p, grid, smem, st);
+  (void)fold;
+  return asym ? launch<MT, true, false>(p, grid, smem, st) : launch<MT, false, false>(p, grid, smem, st);
 }
 
 }  // namespace
@@ -322,7 +322,7 @@ int launch_mt(const SkinnyParams &p, bool asym, bool fold, dim3 grid, size_t sme
 WoqSkinnyPlan woq_skinny_plan(int64_t M, int64_t N, int64_t K) {
   WoqSkinnyPlan pl{};
   const int mchunk = (int)(M < 64 ? M : 64);
-  pl.mt = mchunk <= 8 ? 1 : mchunk <= 16 ? 2 : mchunk <= 32 ? 4 : 8;
+  pl.mt = mchunk <= 32 ? 4 : 8;
   const int64_t ntiles = ceil_div<int64_t>(N, kTileN);
   const int64_t want = 3LL * sm_count();
   int kslice = pl.mt <= 2 ? 2048 : (pl.mt == 4 ? 1024 : 512);
@@ -379,12 +379,10 @@ int woq_skinny_launch(const zt_woq_linear_args_t &a, bool fold, cudaStream_t st)
       if (p.post.bufs[i]) p.post.bufs[i] = reinterpret_cast<const __nv_bfloat16 *>(p.post.bufs[i]) + m0 * a.N;
     const bool asym = a.zeros != nullptr;
     int rc;
-    switch (pl.mt) {
-      case 1: rc = launch_mt<1>(p, asym, fold, grid, smem, st); break;
-      case 2: rc = launch_mt<2>(p, asym, fold, grid, smem, st); break;
-      case 4: rc = launch_mt<4>(p, asym, fold, grid, smem, st); break;
-      default: rc = launch_mt<8>(p, asym, fold, grid, smem, st); break;
-    }
+    if (pl.mt == 4)
+      rc = launch_mt<4>(p, asym, fold, grid, smem, st);
+    else
+      rc = launch_mt<8>(p, asym, fold, grid, smem, st);
     if (rc != ZT_SUCCESS) return rc;
   }
   return ZT_SUCCESS;

@@ -1,0 +1,383 @@
+// Weight-only int4 linear for decode (M <= 16): an HBM-bound streaming kernel.
+//
+// Work decomposition.  A CTA owns 16*R output columns (= rows of the N-major packed weight) and one
+// K-slice; its W warps split the slice's 128-wide k-steps round-robin, so every warp streams its own
+// part of the same rows.  A lane reads 128 bits (32 nibbles) per row and step, the four lanes of a
+// quad cover the 128 consecutive k of the step (= one quantisation group when the group size is
+// 128).  Loads run four steps ahead of the arithmetic in a register ring, together with the
+// scales (and zero points) of those steps, so that each thread keeps 4 * 2R 16-byte loads in flight.
+//
+// Arithmetic.  Nibbles become bf16 pairs in registers with one lop3 each ((w >> 4p) & 0x000f000f
+// picks nibbles p and p+4; or-ing 0x4300 into both halves gives the bf16 number 128 + u; signed
+// nibbles are xor-ed with 8 in the same lop3, so u = q + 8 in both formats).  Those pairs are the A
+// operand of mma.sync.m16n8k16 (rows = output columns); the B operand is the activation chunk,
+// staged per CTA in shared memory in the matching order (k, k+4), (k+1, k+5), ...  The bias of 136 is
+// removed on the step's partial sum: part - 136 * sum_k x[m,k] (the activation sums are produced
+// while staging), the group scale multiplies the corrected partial sum in fp32, and the zero point
+// contributes z * sum_k x.  Dequantised weights are therefore never rounded to bf16: the result is
+// the fp32-accumulated product with exact q*s.
+//
+// Reduction.  Warp partials are combined through shared memory; K-slices (only used when N alone
+// cannot fill the GPU) through a global fp32 scratch by the last CTA to arrive, in a fixed order.
+#include "common.cuh"
+#include "woq.cuh"
+
+namespace zt {
+
+namespace {
+
+constexpr int kStepK = 128;  // k per step
+constexpr int kRing = 4;     // steps in flight per warp = steps per warp and chunk
+
+struct StreamParams {
+  const __nv_bfloat16 *x;
+  const int32_t *wq;
+  const void *scales;
+  const void *zeros;
+  const void *bias;
+  __nv_bfloat16 *y;
+  float *partial;  // [nsplit][M][N]
+  int *counters;   // one per n-tile, zero on entry and on exit
+  int M, N, K;
+  int gs;
+  int kslice;
+  int nsplit;
+  int scale_dtype, bias_dtype;
+  PostOpsDev post;
+};
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+
+template <bool SIGNED>
+__device__ __forceinline__ uint32_t nib_pair_to_bf16x2(uint32_t w) {
+  uint32_t r;
+  if (SIGNED) {  // (w & 0x000f000f) ^ 0x43084308
+    asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(r) : "r"(w), "n"(0x000f000f), "n"(0x43084308));
+  } else {  // (w & 0x000f000f) | 0x43004300
+    asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(w), "n"(0x000f000f), "n"(0x43004300));
+  }
+  return r;
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 16-byte slot of activations k = 8b .. 8b+7 within a chunk row: the fields "which word of the lane's
+// 128-bit weight load" (b & 3) and "which lane of the quad" ((b >> 2) & 3) are swapped so that the
+// eight lanes of a shared-load phase hit eight different bank groups.
+__device__ __forceinline__ int x_slot(int b) { return (b & ~15) | ((b & 3) << 2) | ((b >> 2) & 3); }
+
+template <int R>
+struct RingSlot {
+  uint4 w[R][2];
+  float s[R][2];
+  float z[R][2];
+};
+
+template <int MT, int R, int W, bool ASYM>
+__global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int kThreads = W * 32;
+  constexpr int kCols = MT * 8;                        // padded M held in MMA column blocks
+  constexpr int kChunkK = W * kRing * kStepK;          // k staged per chunk
+  constexpr int kChunkSteps = W * kRing;
+  constexpr int kRowSlots = kChunkK / 8 + 4;           // +4 slots: bank skew between rows
+  constexpr int kTileN = 16 * R;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * kTileN;
+  const int split = blockIdx.y;
+  const int k0 = split * p.kslice;
+  const int k1 = min(p.K, k0 + p.kslice);
+  const int nchunks = (k1 - k0 + kChunkK - 1) / kChunkK;
+  const int mrows = min(p.M, kCols);
+
+  uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);                                    // [mrows][kRowSlots]
+  float *sx = reinterpret_cast<float *>(smem_raw + (size_t)mrows * kRowSlots * 16);   // [mrows][kChunkSteps]
+
+  const int k8 = p.K >> 3;
+  const int32_t *wrow[R][2];
+  int ncol[R][2];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int n = min(n0 + 16 * r + 8 * h + g, p.N - 1);
+      ncol[r][h] = n;
+      wrow[r][h] = p.wq + (size_t)n * k8 + 4 * t;
+    }
+
+  // step j of chunk c covers k = k0 + c*kChunkK + (j*W + warp)*128 .. +127
+  auto step_k = [&](int c, int j) { return k0 + c * kChunkK + (j * W + warp) * kStepK; };
+  RingSlot<R> ring[kRing];
+  auto prefetch = [&](RingSlot<R> &slot, int k) {
+    if (k < k1) {
+      const int gidx = k / p.gs;
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          slot.w[r][h] = ldg_nc_v4(wrow[r][h] + (k >> 3));
+          slot.s[r][h] = load_as_float(p.scales, (int64_t)gidx * p.N + ncol[r][h], p.scale_dtype);
+          if (ASYM) slot.z[r][h] = load_as_float(p.zeros, (int64_t)gidx * p.N + ncol[r][h], p.scale_dtype);
+        }
+    }
+  };
+#pragma unroll
+  for (int j = 0; j < kRing; ++j) prefetch(ring[j], step_k(0, j));
+
+  float acc[R][MT][4];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[r][m][e] = 0.f;
+
+  for (int c = 0; c < nchunks; ++c) {
+    const int kc = k0 + c * kChunkK;
+    if (c > 0) __syncthreads();  // the previous chunk's activations are no longer read
+    // ---- stage activations of this chunk, permuted, and their per-step sums -------------------------
+    for (int i = tid; i < mrows * (kChunkK / 8); i += kThreads) {
+      const int row = i / (kChunkK / 8), b = i - row * (kChunkK / 8);
+      const int k = kc + 8 * b;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (k < k1) v = *reinterpret_cast<const uint4 *>(p.x + (size_t)row * p.K + k);
+      uint4 o;
+      o.x = prmt(v.x, v.z, 0x5410);  // (x0, x4)
+      o.y = prmt(v.x, v.z, 0x7632);  // (x1, x5)
+      o.z = prmt(v.y, v.w, 0x5410);  // (x2, x6)
+      o.w = prmt(v.y, v.w, 0x7632);  // (x3, x7)
+      xs[row * kRowSlots + x_slot(b)] = o;
+      // sum of the 128 activations of a step: 16 consecutive lanes hold one step of one row
+      float sum = bf16_bits_to_float(v.x & 0xffff) + bf16_bits_to_float(v.x >> 16) + bf16_bits_to_float(v.y & 0xffff) +
+                  bf16_bits_to_float(v.y >> 16) + bf16_bits_to_float(v.z & 0xffff) + bf16_bits_to_float(v.z >> 16) +
+                  bf16_bits_to_float(v.w & 0xffff) + bf16_bits_to_float(v.w >> 16);
+#pragma unroll
+      for (int o2 = 8; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
+      if ((lane & 15) == 0) sx[row * kChunkSteps + (b >> 4)] = sum;
+    }
+    __syncthreads();
+
+    // ---- this warp's steps of the chunk ---------------------------------------------------------------
+#pragma unroll
+    for (int j = 0; j < kRing; ++j) {
+      const int k = kc + (j * W + warp) * kStepK;
+      if (k < k1) {
+        const int sidx = j * W + warp;  // step index within the chunk
+        float part[R][MT][4];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+          for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) part[r][m][e] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 bfrag[MT];
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            const int col = m * 8 + g;
+            bfrag[m] = col < mrows ? xs[col * kRowSlots + sidx * 16 + 4 * i + t] : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const uint4 &qa = ring[j].w[r][0];
+            const uint4 &qb = ring[j].w[r][1];
+            const uint32_t wa = (i == 0) ? qa.x : (i == 1) ? qa.y : (i == 2) ? qa.z : qa.w;
+            const uint32_t wb = (i == 0) ? qb.x : (i == 1) ? qb.y : (i == 2) ? qb.z : qb.w;
+            uint32_t ra[4], rb[4];
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp) {
+              ra[pp] = nib_pair_to_bf16x2<!ASYM>(wa >> (4 * pp));
+              rb[pp] = nib_pair_to_bf16x2<!ASYM>(wb >> (4 * pp));
+            }
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+              mma_bf16_16816(part[r][m], ra[0], rb[0], ra[1], rb[1], bfrag[m].x, bfrag[m].y);
+              mma_bf16_16816(part[r][m], ra[2], rb[2], ra[3], rb[3], bfrag[m].z, bfrag[m].w);
+            }
+          }
+        }
+        // fold the step: acc += s * (part - 136 * sx) + z * sx
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = m * 8 + 2 * t + e;
+            const float sxv = col < mrows ? sx[col * kChunkSteps + sidx] : 0.f;
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                float v = ring[j].s[r][h] * fmaf(-136.f, sxv, part[r][m][2 * h + e]);
+                if (ASYM) v = fmaf(ring[j].z[r][h], sxv, v);
+                acc[r][m][2 * h + e] += v;
+              }
+          }
+        }
+      }
+      prefetch(ring[j], step_k(c + 1, j));
+    }
+  }
+
+  // ---- reduce the warps (they split K) through shared memory ------------------------------------------
+  __syncthreads();
+  float *red = reinterpret_cast<float *>(smem_raw);  // [W][kCols][kTileN + 1]
+  constexpr int kRedStride = kTileN + 1;
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int nl = 16 * r + 8 * (e >> 1) + g;
+        const int ml = m * 8 + 2 * t + (e & 1);
+        red[(warp * kCols + ml) * kRedStride + nl] = acc[r][m][e];
+      }
+  __syncthreads();
+
+  __shared__ int s_ticket;
+  constexpr int kRowsPerPass = kThreads / kTileN;
+  const int nl = tid % kTileN;
+  const int n = n0 + nl;
+  if (p.nsplit > 1) {
+    for (int ml = tid / kTileN; ml < p.M; ml += kRowsPerPass) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < W; ++w) v += red[(w * kCols + ml) * kRedStride + nl];
+      if (n < p.N) p.partial[((size_t)split * p.M + ml) * p.N + n] = v;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_ticket = atomicAdd(&p.counters[blockIdx.x], 1);
+    __syncthreads();
+    if (s_ticket != p.nsplit - 1) return;
+    __threadfence();
+    if (tid == 0) p.counters[blockIdx.x] = 0;
+  }
+  for (int ml = tid / kTileN; ml < p.M; ml += kRowsPerPass) {
+    if (n >= p.N) continue;
+    float v = 0.f;
+    if (p.nsplit > 1) {
+      for (int s = 0; s < p.nsplit; ++s) v += __ldcg(&p.partial[((size_t)s * p.M + ml) * p.N + n]);
+    } else {
+#pragma unroll
+      for (int w = 0; w < W; ++w) v += red[(w * kCols + ml) * kRedStride + nl];
+    }
+    if (p.bias) v += load_as_float(p.bias, n, p.bias_dtype);
+    const int64_t idx = (int64_t)ml * p.N + n;
+    v = apply_post_ops(v, p.post, idx, ZT_BF16);
+    p.y[idx] = __float2bfloat16_rn(v);
+  }
+}
+
+template <int MT>
+constexpr int warps_for() {
+  return MT == 1 ? 8 : 4;
+}
+
+template <int MT, int R>
+size_t stream_smem_bytes(int M) {
+  constexpr int W = warps_for<MT>();
+  constexpr int kChunkK = W * kRing * kStepK;
+  const size_t mrows = (size_t)(M < MT * 8 ? M : MT * 8);
+  const size_t stage = mrows * (kChunkK / 8 + 4) * 16 + mrows * (W * kRing) * sizeof(float);
+  const size_t red = (size_t)W * MT * 8 * (16 * R + 1) * sizeof(float);
+  return stage > red ? stage : red;
+}
+
+template <int MT, int R, bool ASYM>
+int launch(const StreamParams &p, dim3 grid, cudaStream_t st) {
+  constexpr int W = warps_for<MT>();
+  auto kern = woq_stream_kernel<MT, R, W, ASYM>;
+  static bool configured = false;
+  if (!configured) {
+    ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    configured = true;
+  }
+  kern<<<grid, W * 32, stream_smem_bytes<MT, R>(p.M), st>>>(p);
+  return launch_status("woq_stream_kernel");
+}
+
+}  // namespace
+
+// R = 2 (32 columns per CTA) once N alone gives every SM two CTAs; K is split across CTAs only
+// when the column tiles cannot occupy the GPU.
+WoqStreamPlan woq_stream_plan(int64_t M, int64_t N, int64_t K) {
+  WoqStreamPlan pl{};
+  pl.mt = M <= 8 ? 1 : 2;
+  const int64_t sms = sm_count();
+  pl.r = (ceil_div<int64_t>(N, 32) >= 2 * sms) ? 2 : 1;
+  const int64_t ntiles = ceil_div<int64_t>(N, 16 * pl.r);
+  int nsplit = 1;
+  if (ntiles < (3 * sms) / 2) {
+    nsplit = (int)ceil_div<int64_t>(2 * sms, ntiles);
+    const int64_t max_split = K / 512 > 0 ? K / 512 : 1;  // at least four steps per CTA
+    if (nsplit > max_split) nsplit = (int)max_split;
+  }
+  int64_t kslice = ceil_div<int64_t>(ceil_div<int64_t>(K, nsplit), kStepK) * kStepK;
+  pl.kslice = (int)kslice;
+  pl.nsplit = (int)ceil_div<int64_t>(K, kslice);
+  if (ntiles * (int64_t)sizeof(int) > ZT_WOQ_COUNTER_BYTES) {
+    pl.nsplit = 1;
+    pl.kslice = (int)K;
+  }
+  pl.partial_bytes = pl.nsplit > 1 ? (size_t)pl.nsplit * M * N * sizeof(float) : 0;
+  return pl;
+}
+
+bool woq_stream_supported(const zt_woq_linear_args_t &a) {
+  if (a.M < 1 || a.M > 16 || a.N < 1) return false;
+  if (a.K % kStepK != 0 || a.n_groups <= 0 || a.K % a.n_groups != 0) return false;
+  const int64_t gs = a.K / a.n_groups;
+  if (gs % kStepK != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.wq)) & 15) return false;
+  return a.K <= (1 << 30) && a.N <= (1 << 30);
+}
+
+int woq_stream_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
+  const WoqStreamPlan pl = woq_stream_plan(a.M, a.N, a.K);
+  if (pl.nsplit > 1) {
+    ZT_REQUIRE(a.workspace != nullptr && a.workspace_bytes >= ZT_WOQ_COUNTER_BYTES + pl.partial_bytes,
+               ZT_WORKSPACE_TOO_SMALL, "zt_woq_linear: workspace of %zu bytes is smaller than the %zu required",
+               a.workspace_bytes, (size_t)ZT_WOQ_COUNTER_BYTES + pl.partial_bytes);
+  }
+  StreamParams p{};
+  p.M = (int)a.M;
+  p.N = (int)a.N;
+  p.K = (int)a.K;
+  p.x = reinterpret_cast<const __nv_bfloat16 *>(a.x);
+  p.y = reinterpret_cast<__nv_bfloat16 *>(a.y);
+  p.wq = a.wq;
+  p.scales = a.scales;
+  p.zeros = a.zeros;
+  p.bias = a.bias;
+  p.scale_dtype = a.scale_dtype;
+  p.bias_dtype = a.bias_dtype;
+  p.gs = (int)(a.K / a.n_groups);
+  p.kslice = pl.kslice;
+  p.nsplit = pl.nsplit;
+  p.counters = reinterpret_cast<int *>(a.workspace);
+  p.partial = reinterpret_cast<float *>(reinterpret_cast<char *>(a.workspace) + ZT_WOQ_COUNTER_BYTES);
+  p.post = to_dev(a.post);
+  const dim3 grid((unsigned)ceil_div<int64_t>(a.N, 16 * pl.r), (unsigned)pl.nsplit);
+  const bool asym = a.zeros != nullptr;
+  if (pl.mt == 1) {
+    if (pl.r == 1) return asym ? launch<1, 1, true>(p, grid, st) : launch<1, 1, false>(p, grid, st);
+    return asym ? launch<1, 2, true>(p, grid, st) : launch<1, 2, false>(p, grid, st);
+  }
+  if (pl.r == 1) return asym ? launch<2, 1, true>(p, grid, st) : launch<2, 1, false>(p, grid, st);
+  return asym ? launch<2, 2, true>(p, grid, st) : launch<2, 2, false>(p, grid, st);
+}
+
+}  // namespace zt
