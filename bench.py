@@ -322,7 +322,7 @@ def bench_woq_decode(torch, _capi, lib, dev, stream, sptr, steps, pk):
     ms = time_region(torch, g.replay, reps) / (reps * copies)
     gbs = alg_bytes / (ms * 1e-3) / 1e9
     return {"workload": "BASELINE config 1: WOQ int4 (group 128, fp32 scales) M=1 K=4096 N=4096, bf16 bias",
-            "kernel": "woq_skinny_kernel", "bound": "hbm", "us_per_call": round(ms * 1e3, 3),
+            "kernel": "woq_stream_kernel", "bound": "hbm", "us_per_call": round(ms * 1e3, 3),
             "algorithmic_bytes": alg_bytes, "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
             "frac": round(gbs / pk["hbm_gbs"], 4), "peak_note": f"STREAM-style copy, {pk['source']}",
             "l2": f"rotating over {copies} weight copies", "launch": "CUDA graph, back-to-back"}
@@ -353,6 +353,46 @@ def bench_e2e(torch, dev, sets, steps, world):
     end.record()
     torch.cuda.synchronize()
     return {"ms": start.elapsed_time(end), "h2d": M * K * 2, "d2h": M * N * 2}
+
+
+def run_profile_case(name):
+    """A few plain launches (no CUDA graph) of one kernel on a case that is small enough to profile
+    with `ncu --set full` and still larger than L2:  python bench.py --profile int8_gemm|woq_decode|dynquant"""
+    import ctypes as C
+    import torch
+    import zentorch_b200  # noqa: F401
+    from zentorch_b200 import _capi
+    from _util import make_woq_case
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    lib = _capi.lib()
+    if name in ("int8_gemm", "dynquant"):
+        x0, w0, ws0, b0 = make_operands(torch, dev, seed=0)
+        sets = []
+        for i in range(4):
+            w = w0.roll(i, 0).contiguous().to(dev)
+            sets.append((x0.roll(i, 0).contiguous().to(dev), w, ws0.to(dev), b0.to(dev), _capi.int8_weight_rowsum(w)))
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        for i in range(8):
+            x, w, ws, b, rs = sets[i % 4]
+            q, sc, zp = _capi.dynamic_quantize(x, _capi.ZT_ACT_U8_ASYM)
+            if name == "int8_gemm":
+                a = _capi.dynamic_qlinear_args(x, w, ws, b, _capi.ZT_ACT_U8_ASYM, (4,), (), rs, y, None, _capi.ZT_ALGO_AUTO)
+                _capi.check(lib.zt_qlinear_prequantized(C.byref(a), q.data_ptr(), sc.data_ptr(), zp.data_ptr(), None))
+    elif name == "woq_decode":
+        m, k, n, gs = 1, 8192, 28672, 128
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        bias = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        copies = [(torch.randint(-2**31, 2**31 - 1, (n, k // 8), dtype=torch.int32, device=dev),
+                   torch.rand(k // gs, n, device=dev) * 0.01) for _ in range(2)]
+        for i in range(6):
+            wq, sc = copies[i % 2]
+            _capi.woq_linear(x, wq, sc, None, bias)
+    else:
+        raise SystemExit(f"unknown profile case {name}")
+    torch.cuda.synchronize()
+    assert _capi.poll_device_status() == 0
+    print(json.dumps({"profile_case": name, "status": "ok"}))
 
 
 def cpu_oracle_call():
@@ -422,8 +462,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile", default=None, help="run a few plain launches of one kernel (for ncu): "
+                                                    "int8_gemm | woq_decode | dynquant")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile:
+        run_profile_case(args.profile)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
