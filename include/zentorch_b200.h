@@ -167,6 +167,32 @@ typedef struct {
 ZT_API size_t zt_dynamic_qlinear_workspace_bytes(int64_t M, int64_t K);
 ZT_API int zt_dynamic_qlinear(const zt_dynamic_qlinear_args_t *args, void *stream);
 
+/* zt_dynamic_qlinear for callers that cannot allocate device memory.
+ *
+ * This entry point has no counterpart in the reference.  Some hosts of this library cannot call
+ * cudaMalloc at the point where they run a linear: a runtime that hands out all device memory up
+ * front from its own arena and forbids later driver allocations, code running inside a region where
+ * allocation is illegal, or a plugin loaded into a process whose allocator it may not touch.  For
+ * them the scratch that zt_dynamic_qlinear needs between its two kernels (the quantised activations,
+ * their scales and zero points) lives in a fixed array inside the library's device image instead of a
+ * caller-provided workspace: `workspace` / `workspace_bytes` of the argument block are ignored, inputs
+ * and outputs are still the caller's.
+ *
+ * Limits: M * K <= ZT_STATIC_SCRATCH_Q_BYTES (8 MiB of quantised activations, e.g. 2048 x 4096) and
+ * M <= ZT_STATIC_SCRATCH_MAX_ROWS; larger problems are rejected with ZT_UNSUPPORTED and a message
+ * naming the limit.  Every GPU on which the library is loaded holds the array (8 MiB + 128 KiB) until
+ * the process exits.  The call performs no cudaMalloc / cudaFree and calls no allocating library
+ * routine.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current) and caches it; make that first call before starting any stream capture.  All calls
+ * on a device share the one array and every call overwrites what it uses of it, so two calls that can
+ * overlap on the GPU (different streams without an ordering between them) race on it: order them.
+ * Nothing in the array has to be zero on entry. */
+#define ZT_STATIC_SCRATCH_Q_BYTES (8u << 20)
+#define ZT_STATIC_SCRATCH_MAX_ROWS 16384
+ZT_API int zt_dynamic_qlinear_static(const zt_dynamic_qlinear_args_t *args, void *stream);
+
 /* The first phase of zentorch_dynamic_qlinear on its own: per-row quantisation.  q is [M,K] int8
  * (s8) or uint8 (u8); scales [M] fp32; zero_points [M] int32 (u8 mode only, else may be NULL). */
 ZT_API int zt_dynamic_quantize(const void *x, int32_t x_dtype, int64_t M, int64_t K, int32_t act_quant, void *q,

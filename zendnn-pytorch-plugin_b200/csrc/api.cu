@@ -326,3 +326,49 @@ extern "C" int zt_qlinear_prequantized(const zt_dynamic_qlinear_args_t *a, const
   g.post = to_dev(a->post);
   return run_int8_gemm(g, a->algo, (cudaStream_t)stream);
 }
+
+// ---- allocation-free variant of zt_dynamic_qlinear ------------------------------------------------------
+// The scratch lives in the library's device image.  In host code the array's name is only a handle
+// for the runtime, not a device address: the address is looked up once per device with
+// cudaGetSymbolAddress (that device being current) and only that pointer is handed to kernels.
+namespace {
+constexpr size_t kStaticRowBytes = (size_t)ZT_STATIC_SCRATCH_MAX_ROWS * 4;  // scales, then zero points
+constexpr size_t kStaticScratchBytes = (size_t)ZT_STATIC_SCRATCH_Q_BYTES + 2 * kStaticRowBytes;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int static_scratch_ptr(void **out) {
+  static void *ptrs[64] = {nullptr};
+  int dev = 0;
+  ZT_CUDA_OK(cudaGetDevice(&dev));
+  ZT_REQUIRE(dev >= 0 && dev < 64, ZT_UNSUPPORTED, "zt_dynamic_qlinear_static: device index %d out of range", dev);
+  if (!ptrs[dev]) {
+    void *p = nullptr;
+    ZT_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
+    ZT_REQUIRE(p != nullptr, ZT_CUDA_ERROR, "zt_dynamic_qlinear_static: no device address for the scratch array");
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return ZT_SUCCESS;
+}
+}  // namespace
+
+extern "C" int zt_dynamic_qlinear_static(const zt_dynamic_qlinear_args_t *a, void *stream) {
+  ZT_REQUIRE(a != nullptr, ZT_INVALID_ARGUMENT, "zt_dynamic_qlinear_static: null argument block");
+  ZT_REQUIRE(a->M >= 0 && a->N >= 0 && a->K >= 0, ZT_INVALID_ARGUMENT, "zt_dynamic_qlinear_static: negative size");
+  ZT_REQUIRE(a->M <= ZT_STATIC_SCRATCH_MAX_ROWS, ZT_UNSUPPORTED,
+             "zt_dynamic_qlinear_static: M = %lld exceeds the built-in scratch (at most %d rows); use "
+             "zt_dynamic_qlinear with a caller workspace",
+             (long long)a->M, ZT_STATIC_SCRATCH_MAX_ROWS);
+  ZT_REQUIRE(a->K == 0 || a->M <= (int64_t)ZT_STATIC_SCRATCH_Q_BYTES / a->K, ZT_UNSUPPORTED,
+             "zt_dynamic_qlinear_static: M*K = %lld x %lld exceeds the built-in scratch (at most %u bytes of "
+             "quantised activations); use zt_dynamic_qlinear with a caller workspace",
+             (long long)a->M, (long long)a->K, (unsigned)ZT_STATIC_SCRATCH_Q_BYTES);
+  void *scratch = nullptr;
+  int rc = static_scratch_ptr(&scratch);
+  if (rc != ZT_SUCCESS) return rc;
+  // Same layout as the caller-workspace path expects: q | scales | zero points, each 256-byte aligned.
+  zt_dynamic_qlinear_args_t b = *a;
+  b.workspace = scratch;
+  b.workspace_bytes = kStaticScratchBytes;
+  return zt_dynamic_qlinear(&b, stream);
+}

@@ -17,6 +17,7 @@ ZT_MAX_POST_OPS = 4
 ZT_WOQ_COUNTER_BYTES = 16384
 ZT_ALGO_AUTO, ZT_ALGO_GENERIC, ZT_ALGO_SKINNY, ZT_ALGO_TCGEN05 = 0, 1, 2, 3
 ZT_ACT_S8_SYM, ZT_ACT_U8_ASYM = 0, 1
+ZT_STATIC_SCRATCH_Q_BYTES, ZT_STATIC_SCRATCH_MAX_ROWS = 8 << 20, 16384
 (ZT_POST_NONE, ZT_POST_RELU, ZT_POST_GELU_TANH, ZT_POST_GELU_ERF, ZT_POST_SILU, ZT_POST_SIGMOID,
  ZT_POST_TANH, ZT_POST_MUL, ZT_POST_ADD) = range(9)
 
@@ -25,7 +26,7 @@ EXPORTED_SYMBOLS = (
     "zt_last_error", "zt_version", "zt_device_supported", "zt_poll_device_status",
     "zt_woq_linear_workspace_bytes", "zt_woq_linear", "zt_woq_repack_weight", "zt_woq_repack_from_int4pack",
     "zt_dynamic_qlinear_workspace_bytes", "zt_dynamic_qlinear", "zt_dynamic_quantize", "zt_int8_gemm_s32",
-    "zt_int8_weight_rowsum", "zt_qlinear_prequantized",
+    "zt_int8_weight_rowsum", "zt_qlinear_prequantized", "zt_dynamic_qlinear_static",
 )
 
 
@@ -84,6 +85,7 @@ def lib() -> C.CDLL:
     L.zt_dynamic_qlinear_workspace_bytes.restype = C.c_size_t
     L.zt_dynamic_qlinear_workspace_bytes.argtypes = [C.c_int64, C.c_int64]
     L.zt_dynamic_qlinear.argtypes = [C.POINTER(DynamicQLinearArgs), C.c_void_p]
+    L.zt_dynamic_qlinear_static.argtypes = [C.POINTER(DynamicQLinearArgs), C.c_void_p]
     L.zt_dynamic_quantize.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p]
     L.zt_int8_gemm_s32.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
@@ -251,4 +253,18 @@ def dynamic_qlinear(x, w, w_scales, bias=None, act_quant=ZT_ACT_S8_SYM, post_ops
     a.post = _post(post_ops, buffers)
     a.y, a.workspace, a.workspace_bytes, a.algo = y.data_ptr(), ws.data_ptr(), nbytes, algo
     check(lib().zt_dynamic_qlinear(C.byref(a), _stream_ptr()))
+    return y
+
+
+def dynamic_qlinear_static(x, w, w_scales, bias=None, act_quant=ZT_ACT_S8_SYM, post_ops=(), buffers=(), w_rowsum=None,
+                           algo=ZT_ALGO_AUTO):
+    """zt_dynamic_qlinear_static: same result as dynamic_qlinear, but the library's built-in scratch is
+    used, so nothing is allocated for the call besides the output the caller asks for here.  The u8 mode
+    needs `w_rowsum` from the caller (it is an input, not scratch)."""
+    import torch
+    m, _ = x.shape
+    n = w.shape[0]
+    y = torch.empty(m, n, dtype=x.dtype, device=x.device)
+    a = dynamic_qlinear_args(x, w, w_scales, bias, act_quant, post_ops, buffers, w_rowsum, y, None, algo)
+    check(lib().zt_dynamic_qlinear_static(C.byref(a), _stream_ptr()))
     return y
