@@ -25,6 +25,13 @@ def _run(capi, x, q, scales, zeros, bias, algo, post_ops=(), buffers=()):
     return y.cpu(), packed.cpu()
 
 
+POST_CASES = {  # used by the streaming-kernel and the tensor-core-kernel tests
+    "relu": ([O.POST_RELU], 0), "sigmoid": ([O.POST_SIGMOID], 0), "gelu_tanh": ([O.POST_GELU_TANH], 0),
+    "gelu_erf": ([O.POST_GELU_ERF], 0), "silu": ([O.POST_SILU], 0), "tanh": ([O.POST_TANH], 0),
+    "add": ([O.POST_ADD], 1), "mul_add": ([O.POST_MUL, O.POST_ADD], 2), "add_add": ([O.POST_ADD, O.POST_ADD], 2),
+}
+
+
 # ---- repack ops: bit-exact -------------------------------------------------------------------------
 def test_repack_weight_bit_exact(capi, golden):
     for key in ("pack", "packu"):
@@ -120,11 +127,6 @@ def test_generic_odd_shapes(capi):
         assert_close_bf16(y, O.woq_linear(x, packed.t(), s, None, b), what=f"{m}x{k}x{n}")
 
 
-POST_CASES = {
-    "relu": ([O.POST_RELU], 0), "sigmoid": ([O.POST_SIGMOID], 0), "gelu_tanh": ([O.POST_GELU_TANH], 0),
-    "gelu_erf": ([O.POST_GELU_ERF], 0), "silu": ([O.POST_SILU], 0), "tanh": ([O.POST_TANH], 0),
-    "add": ([O.POST_ADD], 1), "mul_add": ([O.POST_MUL, O.POST_ADD], 2), "add_add": ([O.POST_ADD, O.POST_ADD], 2),
-}
 
 
 @pytest.mark.parametrize("name", sorted(POST_CASES))
@@ -137,6 +139,44 @@ def test_post_ops(capi, name, algo_name):
     bufs = [torch.randn(m, n, generator=g).to(torch.bfloat16) for _ in range(nbuf)]
     y, packed = _run(capi, x, q, s, None, b, getattr(capi, f"ZT_ALGO_{algo_name}"), ops, bufs)
     assert_close_bf16(y, O.woq_linear(x, packed.t(), s, None, b, ops, bufs), what=name)
+
+
+# ---- tensor-core kernel (M > 16): every token-tile width, ragged M / N, both quantisation forms ------------
+@pytest.mark.parametrize("tile", [0, 32, 64, 128, 256])
+@pytest.mark.parametrize("asym,scale_dtype", [(False, torch.float32), (False, torch.bfloat16), (True, torch.float32),
+                                              (True, torch.bfloat16)])
+def test_tcgen05_kernel(capi, tile, asym, scale_dtype):
+    for (m, k, n, gs) in ((17, 256, 128, 128), (100, 512, 200, 64), (300, 1024, 136, 128), (64, 128, 8, 32),
+                          (257, 2048, 384, 2048)):
+        x, q, s, z, b = make_woq_case(m, k, n, gs, seed=m + n, asym=asym, scale_dtype=scale_dtype)
+        algo = capi.ZT_ALGO_TCGEN05 | (tile << 8)
+        y, packed = _run(capi, x, q, s, z, b, algo)
+        ref = O.woq_linear(x, packed.t(), s, z, b)
+        assert_close_bf16(y, ref, what=f"tcgen05 tile={tile} {m}x{k}x{n} gs={gs}")
+        # this kernel rounds dq to bf16 like the oracle: agreement is much tighter than the tolerance
+        tight = 1.5e-2 if asym else 8e-3
+        assert (y.float() - ref.float()).abs().max() <= tight * max(1.0, float(ref.float().abs().max())), (m, k, n)
+
+
+@pytest.mark.parametrize("name", sorted(["relu", "gelu_erf", "silu", "add", "mul_add", "add_add"]))
+def test_tcgen05_post_ops(capi, name):
+    ops, nbuf = POST_CASES[name]
+    m, k, n = 150, 512, 264
+    x, q, s, z, b = make_woq_case(m, k, n, 128, seed=4)
+    g = torch.Generator().manual_seed(10)
+    bufs = [torch.randn(m, n, generator=g).to(torch.bfloat16) for _ in range(nbuf)]
+    y, packed = _run(capi, x, q, s, None, b, capi.ZT_ALGO_TCGEN05, ops, bufs)
+    assert_close_bf16(y, O.woq_linear(x, packed.t(), s, None, b, ops, bufs), what=name)
+
+
+def test_prefill_shape_vs_oracle(capi):
+    """Llama-3-8B q projection at prefill M=2048 (config 3) against the full CPU oracle."""
+    m, k, n = 2048, 4096, 4096
+    x, q, s, z, b = make_woq_case(m, k, n, 128, seed=5)
+    packed = capi.woq_repack_weight(q.cuda())
+    y = capi.woq_linear(x.cuda(), packed, s.cuda(), None, b.cuda()).cpu()
+    ref = (x.float() @ O.woq_dequant(q, s, None).t() + b.float()).to(torch.bfloat16)
+    assert_close_bf16(y, ref, what="prefill 2048x4096x4096")
 
 
 # ---- benchmark shapes ---------------------------------------------------------------------------------

@@ -4,18 +4,21 @@
 // K-slice; its W warps split the slice's 128-wide k-steps round-robin, so every warp streams its own
 // part of the same rows.  A lane reads 128 bits (32 nibbles) per row and step, the four lanes of a
 // quad cover the 128 consecutive k of the step (= one quantisation group when the group size is
-// 128).  Loads run four steps ahead of the arithmetic in a register ring, together with the
+// 128).  Weight loads run four steps ahead of the arithmetic in a register ring, together with the
 // scales (and zero points) of those steps, so that each thread keeps 4 * 2R 16-byte loads in flight.
+// Activations are staged asynchronously (cp.async, double buffered, one chunk = two steps per warp)
+// so that staging never stalls the weight stream.
 //
 // Arithmetic.  Nibbles become bf16 pairs in registers with one lop3 each ((w >> 4p) & 0x000f000f
 // picks nibbles p and p+4; or-ing 0x4300 into both halves gives the bf16 number 128 + u; signed
 // nibbles are xor-ed with 8 in the same lop3, so u = q + 8 in both formats).  Those pairs are the A
-// operand of mma.sync.m16n8k16 (rows = output columns); the B operand is the activation chunk,
-// staged per CTA in shared memory in the matching order (k, k+4), (k+1, k+5), ...  The bias of 136 is
-// removed on the step's partial sum: part - 136 * sum_k x[m,k] (the activation sums are produced
-// while staging), the group scale multiplies the corrected partial sum in fp32, and the zero point
-// contributes z * sum_k x.  Dequantised weights are therefore never rounded to bf16: the result is
-// the fp32-accumulated product with exact q*s.
+// operand of mma.sync.m16n8k16 (rows = output columns); the B operand is read from the staged
+// activations and permuted to the matching order (k, k+4), (k+1, k+5), ... with four byte-permutes
+// per 16 bytes.  A second MMA per k-block with an all-ones A operand yields sum_k x[m,k] of the step
+// in the same fragment layout; with it the bias of 136 is removed on the step's partial sum
+// (part - 136 * sum), the group scale multiplies the corrected partial sum in fp32, and the zero point
+// contributes z * sum.  Dequantised weights are therefore never rounded to bf16: the result is the
+// fp32-accumulated product with exact q*s.
 //
 // Reduction.  Warp partials are combined through shared memory; K-slices (only used when N alone
 // cannot fill the GPU) through a global fp32 scratch by the last CTA to arrive, in a fixed order.
@@ -27,7 +30,8 @@ namespace zt {
 namespace {
 
 constexpr int kStepK = 128;  // k per step
-constexpr int kRing = 4;     // steps in flight per warp = steps per warp and chunk
+constexpr int kRing = 4;     // weight steps in flight per warp
+constexpr int kSPC = 2;      // steps per warp and activation chunk
 
 struct StreamParams {
   const __nv_bfloat16 *x;
@@ -71,6 +75,13 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // 16-byte slot of activations k = 8b .. 8b+7 within a chunk row: the fields "which word of the lane's
 // 128-bit weight load" (b & 3) and "which lane of the quad" ((b >> 2) & 3) are swapped so that the
 // eight lanes of a shared-load phase hit eight different bank groups.
@@ -88,8 +99,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int kThreads = W * 32;
   constexpr int kCols = MT * 8;                        // padded M held in MMA column blocks
-  constexpr int kChunkK = W * kRing * kStepK;          // k staged per chunk
-  constexpr int kChunkSteps = W * kRing;
+  constexpr int kChunkK = W * kSPC * kStepK;           // k staged per chunk
   constexpr int kRowSlots = kChunkK / 8 + 4;           // +4 slots: bank skew between rows
   constexpr int kTileN = 16 * R;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -100,9 +110,8 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   const int k1 = min(p.K, k0 + p.kslice);
   const int nchunks = (k1 - k0 + kChunkK - 1) / kChunkK;
   const int mrows = min(p.M, kCols);
-
-  uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);                                    // [mrows][kRowSlots]
-  float *sx = reinterpret_cast<float *>(smem_raw + (size_t)mrows * kRowSlots * 16);   // [mrows][kChunkSteps]
+  uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);     // [2][mrows][kRowSlots]
+  const int buf_slots = mrows * kRowSlots;
 
   const int k8 = p.K >> 3;
   const int32_t *wrow[R][2];
@@ -132,8 +141,21 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
         }
     }
   };
+  auto stage = [&](int c, int buf) {
+    const int kc = k0 + c * kChunkK;
+    for (int i = tid; i < mrows * (kChunkK / 8); i += kThreads) {
+      const int row = i / (kChunkK / 8), b = i - row * (kChunkK / 8);
+      const int k = kc + 8 * b;
+      const bool in = k < k1;
+      cp_async_16(&xs[buf * buf_slots + row * kRowSlots + x_slot(b)], p.x + (size_t)row * p.K + (in ? k : 0),
+                  in ? 16 : 0);  // beyond the slice: zero-fill
+    }
+    cp_async_commit();
+  };
+
 #pragma unroll
-  for (int j = 0; j < kRing; ++j) prefetch(ring[j], step_k(0, j));
+  for (int s = 0; s < kRing; ++s) prefetch(ring[s], step_k(s / kSPC, s % kSPC));
+  stage(0, 0);
 
   float acc[R][MT][4];
 #pragma unroll
@@ -143,90 +165,85 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[r][m][e] = 0.f;
 
-  for (int c = 0; c < nchunks; ++c) {
-    const int kc = k0 + c * kChunkK;
-    if (c > 0) __syncthreads();  // the previous chunk's activations are no longer read
-    // ---- stage activations of this chunk, permuted, and their per-step sums -------------------------
-    for (int i = tid; i < mrows * (kChunkK / 8); i += kThreads) {
-      const int row = i / (kChunkK / 8), b = i - row * (kChunkK / 8);
-      const int k = kc + 8 * b;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (k < k1) v = *reinterpret_cast<const uint4 *>(p.x + (size_t)row * p.K + k);
-      uint4 o;
-      o.x = prmt(v.x, v.z, 0x5410);  // (x0, x4)
-      o.y = prmt(v.x, v.z, 0x7632);  // (x1, x5)
-      o.z = prmt(v.y, v.w, 0x5410);  // (x2, x6)
-      o.w = prmt(v.y, v.w, 0x7632);  // (x3, x7)
-      xs[row * kRowSlots + x_slot(b)] = o;
-      // sum of the 128 activations of a step: 16 consecutive lanes hold one step of one row
-      float sum = bf16_bits_to_float(v.x & 0xffff) + bf16_bits_to_float(v.x >> 16) + bf16_bits_to_float(v.y & 0xffff) +
-                  bf16_bits_to_float(v.y >> 16) + bf16_bits_to_float(v.z & 0xffff) + bf16_bits_to_float(v.z >> 16) +
-                  bf16_bits_to_float(v.w & 0xffff) + bf16_bits_to_float(v.w >> 16);
+  for (int c2 = 0; c2 < nchunks; c2 += 2) {
 #pragma unroll
-      for (int o2 = 8; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
-      if ((lane & 15) == 0) sx[row * kChunkSteps + (b >> 4)] = sum;
-    }
-    __syncthreads();
-
-    // ---- this warp's steps of the chunk ---------------------------------------------------------------
+    for (int h2 = 0; h2 < 2; ++h2) {
+      const int c = c2 + h2;
+      if (c < nchunks) {
+        cp_async_wait_all();
+        __syncthreads();  // chunk c has landed for everybody; chunk c-1 (other buffer) is no longer read
+        if (c + 1 < nchunks) stage(c + 1, h2 ^ 1);
+        const uint4 *xb = xs + h2 * buf_slots;
 #pragma unroll
-    for (int j = 0; j < kRing; ++j) {
-      const int k = kc + (j * W + warp) * kStepK;
-      if (k < k1) {
-        const int sidx = j * W + warp;  // step index within the chunk
-        float part[R][MT][4];
+        for (int j = 0; j < kSPC; ++j) {
+          RingSlot<R> &slot = ring[h2 * kSPC + j];
+          const int k = step_k(c, j);
+          if (k < k1) {
+            const int sidx = j * W + warp;  // step index within the chunk
+            float part[R][MT][4];
+            float xsum[MT][4];
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+            for (int m = 0; m < MT; ++m)
 #pragma unroll
-          for (int m = 0; m < MT; ++m)
+              for (int e = 0; e < 4; ++e) {
+                xsum[m][e] = 0.f;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) part[r][m][e] = 0.f;
+                for (int r = 0; r < R; ++r) part[r][m][e] = 0.f;
+              }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 bfrag[MT];
+            for (int i = 0; i < 4; ++i) {
+              uint32_t bf[MT][4];
 #pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            const int col = m * 8 + g;
-            bfrag[m] = col < mrows ? xs[col * kRowSlots + sidx * 16 + 4 * i + t] : make_uint4(0u, 0u, 0u, 0u);
-          }
+              for (int m = 0; m < MT; ++m) {
+                const int col = m * 8 + g;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (col < mrows) v = xb[col * kRowSlots + sidx * 16 + 4 * i + t];
+                bf[m][0] = prmt(v.x, v.z, 0x5410);  // (x0, x4)
+                bf[m][1] = prmt(v.x, v.z, 0x7632);  // (x1, x5)
+                bf[m][2] = prmt(v.y, v.w, 0x5410);  // (x2, x6)
+                bf[m][3] = prmt(v.y, v.w, 0x7632);  // (x3, x7)
+                constexpr uint32_t kOnes = 0x3f803f80u;  // bf16 (1.0, 1.0)
+                mma_bf16_16816(xsum[m], kOnes, kOnes, kOnes, kOnes, bf[m][0], bf[m][1]);
+                mma_bf16_16816(xsum[m], kOnes, kOnes, kOnes, kOnes, bf[m][2], bf[m][3]);
+              }
 #pragma unroll
-          for (int r = 0; r < R; ++r) {
-            const uint4 &qa = ring[j].w[r][0];
-            const uint4 &qb = ring[j].w[r][1];
-            const uint32_t wa = (i == 0) ? qa.x : (i == 1) ? qa.y : (i == 2) ? qa.z : qa.w;
-            const uint32_t wb = (i == 0) ? qb.x : (i == 1) ? qb.y : (i == 2) ? qb.z : qb.w;
-            uint32_t ra[4], rb[4];
+              for (int r = 0; r < R; ++r) {
+                const uint4 &qa = slot.w[r][0];
+                const uint4 &qb = slot.w[r][1];
+                const uint32_t wa = (i == 0) ? qa.x : (i == 1) ? qa.y : (i == 2) ? qa.z : qa.w;
+                const uint32_t wb = (i == 0) ? qb.x : (i == 1) ? qb.y : (i == 2) ? qb.z : qb.w;
+                uint32_t ra[4], rb[4];
 #pragma unroll
-            for (int pp = 0; pp < 4; ++pp) {
-              ra[pp] = nib_pair_to_bf16x2<!ASYM>(wa >> (4 * pp));
-              rb[pp] = nib_pair_to_bf16x2<!ASYM>(wb >> (4 * pp));
+                for (int pp = 0; pp < 4; ++pp) {
+                  ra[pp] = nib_pair_to_bf16x2<!ASYM>(wa >> (4 * pp));
+                  rb[pp] = nib_pair_to_bf16x2<!ASYM>(wb >> (4 * pp));
+                }
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                  mma_bf16_16816(part[r][m], ra[0], rb[0], ra[1], rb[1], bf[m][0], bf[m][1]);
+                  mma_bf16_16816(part[r][m], ra[2], rb[2], ra[3], rb[3], bf[m][2], bf[m][3]);
+                }
+              }
             }
+            // fold the step: acc += s * (part - 136 * sum_x) + z * sum_x   (sum_x per output column m)
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-              mma_bf16_16816(part[r][m], ra[0], rb[0], ra[1], rb[1], bfrag[m].x, bfrag[m].y);
-              mma_bf16_16816(part[r][m], ra[2], rb[2], ra[3], rb[3], bfrag[m].z, bfrag[m].w);
-            }
-          }
-        }
-        // fold the step: acc += s * (part - 136 * sx) + z * sx
+            for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
+              for (int e = 0; e < 2; ++e) {
+                const float sxv = xsum[m][e];  // every row of the ones-MMA holds the column sums
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = m * 8 + 2 * t + e;
-            const float sxv = col < mrows ? sx[col * kChunkSteps + sidx] : 0.f;
+                for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                float v = ring[j].s[r][h] * fmaf(-136.f, sxv, part[r][m][2 * h + e]);
-                if (ASYM) v = fmaf(ring[j].z[r][h], sxv, v);
-                acc[r][m][2 * h + e] += v;
+                  for (int h = 0; h < 2; ++h) {
+                    float v = slot.s[r][h] * fmaf(-136.f, sxv, part[r][m][2 * h + e]);
+                    if (ASYM) v = fmaf(slot.z[r][h], sxv, v);
+                    acc[r][m][2 * h + e] += v;
+                  }
               }
           }
+          prefetch(slot, step_k(c + 2, j));
         }
       }
-      prefetch(ring[j], step_k(c + 1, j));
     }
   }
 
@@ -289,9 +306,9 @@ constexpr int warps_for() {
 template <int MT, int R>
 size_t stream_smem_bytes(int M) {
   constexpr int W = warps_for<MT>();
-  constexpr int kChunkK = W * kRing * kStepK;
+  constexpr int kChunkK = W * kSPC * kStepK;
   const size_t mrows = (size_t)(M < MT * 8 ? M : MT * 8);
-  const size_t stage = mrows * (kChunkK / 8 + 4) * 16 + mrows * (W * kRing) * sizeof(float);
+  const size_t stage = 2 * mrows * (kChunkK / 8 + 4) * 16;
   const size_t red = (size_t)W * MT * 8 * (16 * R + 1) * sizeof(float);
   return stage > red ? stage : red;
 }
