@@ -120,6 +120,21 @@ def test_skinny_quant_modes(capi, asym, scale_dtype, k, gs, n):
         assert_close_bf16(y, O.woq_linear(x, packed.t(), s, z, b), what=f"algo {algo}")
 
 
+@pytest.mark.parametrize("cfg", [0, 1, 2])
+@pytest.mark.parametrize("m", [1, 7, 13])
+def test_stream_kernel_shapes(capi, cfg, m, monkeypatch):
+    """Every compiled shape of the decode kernel (16 / 32 / 64 columns per CTA), with and without a
+    K split across CTAs, ragged N, a K that is not a multiple of the activation chunk."""
+    monkeypatch.setenv("ZENTORCH_B200_WOQ_STREAM_CFG", str(cfg))
+    for (k, n, gs, asym, sdt) in ((4096, 200, 128, False, torch.float32), (1152, 1000, 128, True, torch.bfloat16),
+                                  (8192, 72, 256, False, torch.bfloat16), (2048, 4100, 128, True, torch.float32)):
+        x, q, s, z, b = make_woq_case(m, k, n, gs, seed=cfg * 100 + m, asym=asym, scale_dtype=sdt)
+        y, packed = _run(capi, x, q, s, z, b, capi.ZT_ALGO_SKINNY)
+        assert_close_bf16(y, O.woq_linear(x, packed.t(), s, z, b), what=f"cfg {cfg} M={m} K={k} N={n}")
+        exact = O.woq_linear(x, packed.t(), s, z, b, dq_round=None)
+        assert_close_bf16(y, exact, rtol=8e-3, atol=4e-3, what=f"cfg {cfg} M={m} K={k} N={n} vs exact")
+
+
 def test_generic_odd_shapes(capi):
     for (m, k, n, gs) in ((3, 24, 7, 8), (2, 64, 5, 32), (9, 136, 17, 136), (1, 8, 1, 8)):
         x, q, s, z, b = make_woq_case(m, k, n, gs, seed=k)

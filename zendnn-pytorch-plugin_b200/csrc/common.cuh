@@ -80,8 +80,8 @@ __device__ __forceinline__ float unary_post(float y, int id) {
       return 0.5f * y * (1.f + tanhf(c * (y + 0.044715f * y * y * y)));
     }
     case ZT_POST_GELU_ERF: return 0.5f * y * (1.f + erff(y * 0.7071067811865476f));
-    case ZT_POST_SILU: return y / (1.f + __expf(-y));
-    case ZT_POST_SIGMOID: return 1.f / (1.f + __expf(-y));
+    case ZT_POST_SILU: return __fdividef(y, 1.f + __expf(-y));
+    case ZT_POST_SIGMOID: return __fdividef(1.f, 1.f + __expf(-y));
     case ZT_POST_TANH: return tanhf(y);
     default: return y;
   }

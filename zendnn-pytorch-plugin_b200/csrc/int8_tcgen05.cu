@@ -71,12 +71,27 @@ __device__ __forceinline__ void finish_chunk(const TcParams &p, const uint32_t (
                                              const float *wscale, const float *bias, const int32_t *rowsum, int m,
                                              int nb) {
   float v[32];
+  // per-column vectors of the chunk, read as 16-byte shared loads (same address in every lane: broadcast)
+  float wsc[32], bia[32];
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 a = *reinterpret_cast<const float4 *>(wscale + j);
+    const float4 b = *reinterpret_cast<const float4 *>(bias + j);
+    wsc[j] = a.x; wsc[j + 1] = a.y; wsc[j + 2] = a.z; wsc[j + 3] = a.w;
+    bia[j] = b.x; bia[j + 1] = b.y; bia[j + 2] = b.z; bia[j + 3] = b.w;
+  }
   if (p.src_zp) {
     // u8 activations: remove zp_m * sum_k W[n,k].  |acc|, |zp*rowsum| and their difference are all
     // bounded by 255 * 127 * K, which fits 32 bits for K <= 65536; longer rows take 64 bits.
     if (p.K <= 65536) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = (float)((int32_t)r[j] - zp_m * rowsum[j]);
+      for (int j = 0; j < 32; j += 4) {
+        const int4 rs = *reinterpret_cast<const int4 *>(rowsum + j);
+        v[j] = (float)((int32_t)r[j] - zp_m * rs.x);
+        v[j + 1] = (float)((int32_t)r[j + 1] - zp_m * rs.y);
+        v[j + 2] = (float)((int32_t)r[j + 2] - zp_m * rs.z);
+        v[j + 3] = (float)((int32_t)r[j + 3] - zp_m * rs.w);
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = (float)((int64_t)(int32_t)r[j] - (int64_t)zp_m * rowsum[j]);
@@ -86,7 +101,7 @@ __device__ __forceinline__ void finish_chunk(const TcParams &p, const uint32_t (
     for (int j = 0; j < 32; ++j) v[j] = (float)(int32_t)r[j];
   }
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = v[j] * (s_m * wscale[j]) + bias[j];
+  for (int j = 0; j < 32; ++j) v[j] = v[j] * (s_m * wsc[j]) + bia[j];
   const int64_t base = (int64_t)m * p.N + nb;
   if (UNARY >= 0) {
 #pragma unroll

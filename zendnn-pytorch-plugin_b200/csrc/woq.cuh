@@ -14,7 +14,7 @@ struct WoqSkinnyPlan {
 
 struct WoqStreamPlan {
   int mt;      // 8-row activation blocks (1: M <= 8, 2: M <= 16)
-  int r;       // 16-column blocks per CTA
+  int r;       // kernel shape index: 0 = 16, 1 = 32, 2 = 64 columns per CTA
   int kslice;  // k handled by one CTA
   int nsplit;  // number of K-slices
   size_t partial_bytes;

@@ -4,8 +4,9 @@
 // K-slice; its W warps split the slice's 128-wide k-steps round-robin, so every warp streams its own
 // part of the same rows.  A lane reads 128 bits (32 nibbles) per row and step, the four lanes of a
 // quad cover the 128 consecutive k of the step (= one quantisation group when the group size is
-// 128).  Weight loads run four steps ahead of the arithmetic in a register ring, together with the
-// scales (and zero points) of those steps, so that each thread keeps 4 * 2R 16-byte loads in flight.
+// 128).  Weight loads run RING steps ahead of the arithmetic in a register ring, together with the
+// scales (and zero points) of those steps, so that each thread keeps RING * 2R 16-byte loads in flight
+// (R = 4 with RING = 2 for wide layers: the activation-side work of a step is shared by 64 columns).
 // Activations are staged asynchronously (cp.async, double buffered, one chunk = two steps per warp)
 // so that staging never stalls the weight stream.
 //
@@ -22,6 +23,9 @@
 //
 // Reduction.  Warp partials are combined through shared memory; K-slices (only used when N alone
 // cannot fill the GPU) through a global fp32 scratch by the last CTA to arrive, in a fixed order.
+#include <cstdlib>
+#include <type_traits>
+
 #include "common.cuh"
 #include "woq.cuh"
 
@@ -30,7 +34,6 @@ namespace zt {
 namespace {
 
 constexpr int kStepK = 128;  // k per step
-constexpr int kRing = 4;     // weight steps in flight per warp
 constexpr int kSPC = 2;      // steps per warp and activation chunk
 
 struct StreamParams {
@@ -94,7 +97,7 @@ struct RingSlot {
   float z[R][2];
 };
 
-template <int MT, int R, int W, bool ASYM>
+template <int MT, int R, int RING, int W, bool ASYM, bool SF32>
 __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int kThreads = W * 32;
@@ -102,6 +105,9 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   constexpr int kChunkK = W * kSPC * kStepK;           // k staged per chunk
   constexpr int kRowSlots = kChunkK / 8 + 4;           // +4 slots: bank skew between rows
   constexpr int kTileN = 16 * R;
+  constexpr int kUnroll = RING / kSPC;  // chunks per trip of the main loop (ring slots are static)
+  static_assert(RING % kSPC == 0 && (kUnroll == 1 || kUnroll == 2), "ring must hold one or two chunks");
+  using ScaleT = typename std::conditional<SF32, float, __nv_bfloat16>::type;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * kTileN;
@@ -113,31 +119,37 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);     // [2][mrows][kRowSlots]
   const int buf_slots = mrows * kRowSlots;
 
-  const int k8 = p.K >> 3;
-  const int32_t *wrow[R][2];
-  int ncol[R][2];
+  // per-row base pointers: weights as 16-byte vectors (4*t words into the step), scales at column n
+  const uint4 *wrow[R][2];
+  const ScaleT *srow[R][2];
+  const ScaleT *zrow[R][2];
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int n = min(n0 + 16 * r + 8 * h + g, p.N - 1);
-      ncol[r][h] = n;
-      wrow[r][h] = p.wq + (size_t)n * k8 + 4 * t;
+      wrow[r][h] = reinterpret_cast<const uint4 *>(p.wq + (size_t)n * (p.K >> 3)) + t;
+      srow[r][h] = reinterpret_cast<const ScaleT *>(p.scales) + n;
+      zrow[r][h] = ASYM ? reinterpret_cast<const ScaleT *>(p.zeros) + n : nullptr;
     }
 
   // step j of chunk c covers k = k0 + c*kChunkK + (j*W + warp)*128 .. +127
   auto step_k = [&](int c, int j) { return k0 + c * kChunkK + (j * W + warp) * kStepK; };
-  RingSlot<R> ring[kRing];
+  RingSlot<R> ring[RING];
   auto prefetch = [&](RingSlot<R> &slot, int k) {
     if (k < k1) {
-      const int gidx = k / p.gs;
+      const uint32_t woff = (uint32_t)k >> 5;                       // 16-byte vectors into the row
+      const uint32_t soff = (uint32_t)(k / p.gs) * (uint32_t)p.N;  // group row of the scale table
 #pragma unroll
       for (int r = 0; r < R; ++r)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          slot.w[r][h] = ldg_nc_v4(wrow[r][h] + (k >> 3));
-          slot.s[r][h] = load_as_float(p.scales, (int64_t)gidx * p.N + ncol[r][h], p.scale_dtype);
-          if (ASYM) slot.z[r][h] = load_as_float(p.zeros, (int64_t)gidx * p.N + ncol[r][h], p.scale_dtype);
+          slot.w[r][h] = ldg_nc_v4(wrow[r][h] + woff);
+          slot.s[r][h] = SF32 ? (float)__ldg(reinterpret_cast<const float *>(srow[r][h]) + soff)
+                              : __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16 *>(srow[r][h]) + soff));
+          if (ASYM)
+            slot.z[r][h] = SF32 ? (float)__ldg(reinterpret_cast<const float *>(zrow[r][h]) + soff)
+                                : __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16 *>(zrow[r][h]) + soff));
         }
     }
   };
@@ -154,7 +166,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   };
 
 #pragma unroll
-  for (int s = 0; s < kRing; ++s) prefetch(ring[s], step_k(s / kSPC, s % kSPC));
+  for (int s = 0; s < RING; ++s) prefetch(ring[s], step_k(s / kSPC, s % kSPC));
   stage(0, 0);
 
   float acc[R][MT][4];
@@ -165,10 +177,11 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[r][m][e] = 0.f;
 
-  for (int c2 = 0; c2 < nchunks; c2 += 2) {
+  for (int c2 = 0; c2 < nchunks; c2 += kUnroll) {
 #pragma unroll
-    for (int h2 = 0; h2 < 2; ++h2) {
-      const int c = c2 + h2;
+    for (int u = 0; u < kUnroll; ++u) {
+      const int c = c2 + u;
+      const int h2 = c & 1;  // activation buffer of this chunk
       if (c < nchunks) {
         cp_async_wait_all();
         __syncthreads();  // chunk c has landed for everybody; chunk c-1 (other buffer) is no longer read
@@ -176,7 +189,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
         const uint4 *xb = xs + h2 * buf_slots;
 #pragma unroll
         for (int j = 0; j < kSPC; ++j) {
-          RingSlot<R> &slot = ring[h2 * kSPC + j];
+          RingSlot<R> &slot = ring[u * kSPC + j];
           const int k = step_k(c, j);
           if (k < k1) {
             const int sidx = j * W + warp;  // step index within the chunk
@@ -241,7 +254,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
                   }
               }
           }
-          prefetch(slot, step_k(c + 2, j));
+          prefetch(slot, step_k(c + kUnroll, j));
         }
       }
     }
@@ -298,44 +311,61 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   }
 }
 
-template <int MT>
-constexpr int warps_for() {
-  return MT == 1 ? 8 : 4;
-}
+// Kernel shapes.  cfg 0: 16 columns per CTA, cfg 1: 32 columns (both 8 warps for M <= 8, ring of 4);
+// cfg 2: 64 columns, 4 warps, ring of 2 (wide layers).  M in 9..16 always uses 4 warps.
+template <int MT, int CFG>
+struct Shape {
+  static constexpr int R = CFG == 0 ? 1 : CFG == 1 ? 2 : 4;
+  static constexpr int RING = CFG == 2 ? 2 : 4;
+  static constexpr int W = (MT == 1 && CFG != 2) ? 8 : 4;
+};
 
-template <int MT, int R>
+template <int MT, int CFG>
 size_t stream_smem_bytes(int M) {
-  constexpr int W = warps_for<MT>();
-  constexpr int kChunkK = W * kSPC * kStepK;
+  using S = Shape<MT, CFG>;
+  constexpr int kChunkK = S::W * kSPC * kStepK;
   const size_t mrows = (size_t)(M < MT * 8 ? M : MT * 8);
   const size_t stage = 2 * mrows * (kChunkK / 8 + 4) * 16;
-  const size_t red = (size_t)W * MT * 8 * (16 * R + 1) * sizeof(float);
+  const size_t red = (size_t)S::W * MT * 8 * (16 * S::R + 1) * sizeof(float);
   return stage > red ? stage : red;
 }
 
-template <int MT, int R, bool ASYM>
+template <int MT, int CFG, bool ASYM, bool SF32>
 int launch(const StreamParams &p, dim3 grid, cudaStream_t st) {
-  constexpr int W = warps_for<MT>();
-  auto kern = woq_stream_kernel<MT, R, W, ASYM>;
+  using S = Shape<MT, CFG>;
+  auto kern = woq_stream_kernel<MT, S::R, S::RING, S::W, ASYM, SF32>;
   static bool configured = false;
   if (!configured) {
     ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
     configured = true;
   }
-  kern<<<grid, W * 32, stream_smem_bytes<MT, R>(p.M), st>>>(p);
+  kern<<<grid, S::W * 32, stream_smem_bytes<MT, CFG>(p.M), st>>>(p);
   return launch_status("woq_stream_kernel");
+}
+
+template <int MT, int CFG>
+int launch_q(const StreamParams &p, dim3 grid, cudaStream_t st) {
+  const bool asym = p.zeros != nullptr, sf32 = p.scale_dtype == ZT_F32;
+  if (asym) return sf32 ? launch<MT, CFG, true, true>(p, grid, st) : launch<MT, CFG, true, false>(p, grid, st);
+  return sf32 ? launch<MT, CFG, false, true>(p, grid, st) : launch<MT, CFG, false, false>(p, grid, st);
 }
 
 }  // namespace
 
-// R = 2 (32 columns per CTA) once N alone gives every SM two CTAs; K is split across CTAs only
-// when the column tiles cannot occupy the GPU.
+// Columns per CTA grow with N (64 once that still gives every SM about two CTAs); K is split across
+// CTAs only when the column tiles alone cannot occupy the GPU.
 WoqStreamPlan woq_stream_plan(int64_t M, int64_t N, int64_t K) {
   WoqStreamPlan pl{};
   pl.mt = M <= 8 ? 1 : 2;
   const int64_t sms = sm_count();
-  pl.r = (ceil_div<int64_t>(N, 32) >= 2 * sms) ? 2 : 1;
-  const int64_t ntiles = ceil_div<int64_t>(N, 16 * pl.r);
+  int cfg = 0;
+  if (ceil_div<int64_t>(N, 64) * ceil_div<int64_t>(K, 4096) >= 2 * sms) cfg = 2;
+  else if (ceil_div<int64_t>(N, 32) >= 2 * sms) cfg = 1;
+  const char *force = std::getenv("ZENTORCH_B200_WOQ_STREAM_CFG");
+  if (force && *force) cfg = std::atoi(force) < 0 ? 0 : std::atoi(force) > 2 ? 2 : std::atoi(force);
+  pl.r = cfg;  // kernel shape index (see Shape<>)
+  const int64_t tile_n = cfg == 0 ? 16 : cfg == 1 ? 32 : 64;
+  const int64_t ntiles = ceil_div<int64_t>(N, tile_n);
   int nsplit = 1;
   if (ntiles < (3 * sms) / 2) {
     nsplit = (int)ceil_div<int64_t>(2 * sms, ntiles);
@@ -387,14 +417,16 @@ int woq_stream_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   p.counters = reinterpret_cast<int *>(a.workspace);
   p.partial = reinterpret_cast<float *>(reinterpret_cast<char *>(a.workspace) + ZT_WOQ_COUNTER_BYTES);
   p.post = to_dev(a.post);
-  const dim3 grid((unsigned)ceil_div<int64_t>(a.N, 16 * pl.r), (unsigned)pl.nsplit);
-  const bool asym = a.zeros != nullptr;
+  const int tile_n = pl.r == 0 ? 16 : pl.r == 1 ? 32 : 64;
+  const dim3 grid((unsigned)ceil_div<int64_t>(a.N, tile_n), (unsigned)pl.nsplit);
   if (pl.mt == 1) {
-    if (pl.r == 1) return asym ? launch<1, 1, true>(p, grid, st) : launch<1, 1, false>(p, grid, st);
-    return asym ? launch<1, 2, true>(p, grid, st) : launch<1, 2, false>(p, grid, st);
+    if (pl.r == 0) return launch_q<1, 0>(p, grid, st);
+    if (pl.r == 1) return launch_q<1, 1>(p, grid, st);
+    return launch_q<1, 2>(p, grid, st);
   }
-  if (pl.r == 1) return asym ? launch<2, 1, true>(p, grid, st) : launch<2, 1, false>(p, grid, st);
-  return asym ? launch<2, 2, true>(p, grid, st) : launch<2, 2, false>(p, grid, st);
+  if (pl.r == 0) return launch_q<2, 0>(p, grid, st);
+  if (pl.r == 1) return launch_q<2, 1>(p, grid, st);
+  return launch_q<2, 2>(p, grid, st);
 }
 
 }  // namespace zt

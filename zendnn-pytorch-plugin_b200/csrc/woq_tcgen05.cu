@@ -10,7 +10,7 @@
 //   warp 0        TMA producer for the activation tile (2-D tile load, 128-byte swizzle, no multicast)
 //   warp 1        TMEM allocation, tcgen05.mma.kind::f16 issue (bf16 x bf16 -> fp32), TMEM release
 //   warps 2..9    dequantisation: 128-bit loads of packed nibbles straight from global memory
-//                 (prefetched one k-block ahead, with the group's scale / zero point), nibble -> bf16
+//                 (prefetched four k-blocks ahead, with the group's scale / zero point), nibble -> bf16
 //                 with lop3, exact subtraction of the encoding bias, multiplication by the scale in
 //                 bf16x2 arithmetic, byte-permute into k order, 16-byte stores into the canonical
 //                 K-major 128-byte-swizzled operand layout, fence.proxy.async, mbarrier arrive
@@ -23,7 +23,7 @@
 // Rounding.  q (an integer in [-8, 7]) is exact in bf16.  With bf16 scales q*s is one bf16x2
 // multiplication, i.e. exactly bf16(q*s).  With fp32 scales s is split into s_hi + s_lo (both bf16) and
 // dq = fma(q, s_hi, q*s_lo), which equals bf16(q*s) except for rare double-rounding cases one bf16 ulp
-// apart.  The zero-point form adds z the same way.
+// apart.  The zero-point form is evaluated in fp32, (q - 8) * s + z, and rounded once.
 #include <algorithm>
 #include <mutex>
 #include <unordered_map>
@@ -96,11 +96,6 @@ __device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
 __device__ __forceinline__ uint32_t bf2_fma(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t r;
   asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-  return r;
-}
-__device__ __forceinline__ uint32_t bf2_add(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
 // value -> (hi, lo) bf16 parts replicated into both halves of a register each
@@ -227,62 +222,86 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
       r.s = load_as_float(p.scales, gi, p.scale_dtype);
       r.z = ASYM ? load_as_float(p.zeros, gi, p.scale_dtype) : 0.f;
     };
+    // The packed words and scales are fetched kPrefetch k-blocks ahead into a register ring, so that
+    // several global loads per thread are in flight while one k-block is converted.
+    constexpr int kPrefetch = 4;
+    DqRegs ring[kPrefetch];
+    int ftile = blockIdx.x, fkb = 0;  // next (tile, k-block) to fetch
+    auto fetch_next = [&](DqRegs &slot) {
+      if (ftile < total_tiles) {
+        fetch(ftile, fkb, slot);
+        if (++fkb == num_kb) {
+          fkb = 0;
+          ftile += gridDim.x;
+        }
+      }
+    };
+#pragma unroll
+    for (int i = 0; i < kPrefetch; ++i) fetch_next(ring[i]);
     uint32_t it = 0;
     bool ok = true;
-    int tile = blockIdx.x, kb = 0;
-    DqRegs cur, nxt;
-    if (tile < total_tiles) fetch(tile, 0, cur);
-    while (tile < total_tiles) {
-      int ntile = tile, nkb = kb + 1;
-      if (nkb == num_kb) {
-        nkb = 0;
-        ntile = tile + gridDim.x;
-      }
-      if (ntile < total_tiles) fetch(ntile, nkb, nxt);
-      const uint32_t s = it % STAGES;
-      const uint32_t ph = (it / STAGES) & 1;
-      if (ok && !tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
-        tc::report_timeout(p.status, kStatusConvertTimeout);
-        ok = false;
-      }
-      if (ok) {
-        uint32_t s_hi, s_lo, z_hi = 0, z_lo = 0;
-        split_bf16x2(cur.s, s_hi, s_lo);
-        if (ASYM) split_bf16x2(cur.z, z_hi, z_lo);
-        const bool exact_scale = (p.scale_dtype == ZT_BF16);
-        unsigned char *wrow = smem + s * L::kStageBytes + row * 128;
-        const uint32_t words[4] = {cur.w.x, cur.w.y, cur.w.z, cur.w.w};
+    const bool exact_scale = (p.scale_dtype == ZT_BF16);
+    const int my_tiles = blockIdx.x < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t total_it = (uint32_t)my_tiles * (uint32_t)num_kb;
+    while (it < total_it) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t r[4];
-#pragma unroll
-          for (int pp = 0; pp < 4; ++pp) {
-            uint32_t v = nib_pair_to_bf16x2<!ASYM>(words[i] >> (4 * pp));
-            v = bf2_sub(v, 0x43084308u);  // exact: (128 + u) - 136 = q (signed) or q - 8 (zero-point form)
-            uint32_t dq;
-            if (ASYM) {
-              dq = exact_scale ? bf2_fma(v, s_hi, z_hi) : bf2_add(bf2_fma(v, s_hi, z_hi), bf2_fma(v, s_lo, z_lo));
-            } else {
-              dq = exact_scale ? bf2_mul(v, s_hi) : bf2_fma(v, s_hi, bf2_mul(v, s_lo));
-            }
-            r[pp] = dq;  // (k = p, k = p + 4) of this word
+      for (int slot_i = 0; slot_i < kPrefetch; ++slot_i) {
+        if (it < total_it) {
+          const DqRegs cur = ring[slot_i];
+          fetch_next(ring[slot_i]);
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (ok && !tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
+            tc::report_timeout(p.status, kStatusConvertTimeout);
+            ok = false;
           }
-          uint4 o;
-          o.x = prmt(r[0], r[1], 0x5410);  // (k0, k1)
-          o.y = prmt(r[2], r[3], 0x5410);  // (k2, k3)
-          o.z = prmt(r[0], r[1], 0x7632);  // (k4, k5)
-          o.w = prmt(r[2], r[3], 0x7632);  // (k6, k7)
-          const int chunk = 4 * half + i;  // 16-byte chunk of the 128-byte row
-          *reinterpret_cast<uint4 *>(wrow + ((chunk ^ (row & 7)) << 4)) = o;
+          if (ok) {
+            unsigned char *wrow = smem + s * L::kStageBytes + row * 128;
+            const uint32_t words[4] = {cur.w.x, cur.w.y, cur.w.z, cur.w.w};
+            uint32_t s_hi = 0, s_lo = 0;
+            if (!ASYM) split_bf16x2(cur.s, s_hi, s_lo);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 o;
+              if (ASYM) {
+                // zero-point form in fp32, one rounding: bf16((q - 8) * s + z), pairs come out in k order
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const uint32_t bits = ((words[i] >> (4 * e)) & 0xFu) | 0x4B000000u;  // 2^23 + q
+                  f[e] = fmaf(__uint_as_float(bits) - 8388616.0f, cur.s, cur.z);     // (q - 8) * s + z
+                }
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(f[0], f[1]);
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(f[2], f[3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(f[4], f[5]);
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(f[6], f[7]);
+                o.x = *reinterpret_cast<uint32_t *>(&p0);
+                o.y = *reinterpret_cast<uint32_t *>(&p1);
+                o.z = *reinterpret_cast<uint32_t *>(&p2);
+                o.w = *reinterpret_cast<uint32_t *>(&p3);
+              } else {
+                uint32_t r[4];
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp) {
+                  uint32_t v = nib_pair_to_bf16x2<true>(words[i] >> (4 * pp));
+                  v = bf2_sub(v, 0x43084308u);  // exact: (128 + u) - 136 = q
+                  r[pp] = exact_scale ? bf2_mul(v, s_hi) : bf2_fma(v, s_hi, bf2_mul(v, s_lo));  // (k = p, k = p + 4)
+                }
+                o.x = prmt(r[0], r[1], 0x5410);  // (k0, k1)
+                o.y = prmt(r[2], r[3], 0x5410);  // (k2, k3)
+                o.z = prmt(r[0], r[1], 0x7632);  // (k4, k5)
+                o.w = prmt(r[2], r[3], 0x7632);  // (k6, k7)
+              }
+              const int chunk = 4 * half + i;  // 16-byte chunk of the 128-byte row
+              *reinterpret_cast<uint4 *>(wrow + ((chunk ^ (row & 7)) << 4)) = o;
+            }
+            tc::fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+          }
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&full_w[s]);
+          ++it;
         }
-        tc::fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
       }
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&full_w[s]);
-      cur = nxt;
-      tile = ntile;
-      kb = nkb;
-      ++it;
     }
   } else {
     // ---------------- epilogue warps ----------------
