@@ -33,7 +33,7 @@ def test_dynamic_quantize_bit_exact(capi, dtype, m, k):
     assert torch.equal(su.cpu(), su_ref) and torch.equal(zpu.cpu(), zp_ref) and torch.equal(qu.cpu(), qu_ref)
 
 
-TILES = [0, 64, 96, 128, 160, 192, 224, 256]
+TILES = [0, 64, 96, 128, 160, 192, 224, 256, 1128, 1160, 1192, 1256]  # +1000: 256-row CTA tiles
 
 
 @pytest.mark.parametrize("tile", TILES)

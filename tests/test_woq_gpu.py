@@ -129,10 +129,27 @@ def test_stream_kernel_shapes(capi, cfg, m, monkeypatch):
     for (k, n, gs, asym, sdt) in ((4096, 200, 128, False, torch.float32), (1152, 1000, 128, True, torch.bfloat16),
                                   (8192, 72, 256, False, torch.bfloat16), (2048, 4100, 128, True, torch.float32)):
         x, q, s, z, b = make_woq_case(m, k, n, gs, seed=cfg * 100 + m, asym=asym, scale_dtype=sdt)
-        y, packed = _run(capi, x, q, s, z, b, capi.ZT_ALGO_SKINNY)
+        y, packed = _run(capi, x, q, s, z, b, capi.ZT_ALGO_SKINNY | (1 << 8))   # hint 1: register-ring kernel
         assert_close_bf16(y, O.woq_linear(x, packed.t(), s, z, b), what=f"cfg {cfg} M={m} K={k} N={n}")
         exact = O.woq_linear(x, packed.t(), s, z, b, dq_round=None)
         assert_close_bf16(y, exact, rtol=8e-3, atol=4e-3, what=f"cfg {cfg} M={m} K={k} N={n} vs exact")
+
+
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 9, 16])
+def test_streamk_kernel(capi, m):
+    """The work-balanced decode kernel: column tiles shared between CTAs (small N, long K), ragged N,
+    both quantisation forms and scale dtypes; run twice to check that the arrival counters reset."""
+    cases = ((4096, 64, 128, False, torch.float32), (28672, 192, 128, False, torch.float32),
+             (8192, 1000, 256, True, torch.float32), (1024, 4104, 128, True, torch.bfloat16),
+             (4096, 4096, 4096, False, torch.bfloat16), (14336, 136, 128, False, torch.float32))
+    for (k, n, gs, asym, sdt) in cases:
+        x, q, s, z, b = make_woq_case(m, k, n, gs, seed=m * 7 + n, asym=asym, scale_dtype=sdt)
+        ref = O.woq_linear(x, O.woq_repack_weight(q).t(), s, z, b)
+        exact = O.woq_linear(x, O.woq_repack_weight(q).t(), s, z, b, dq_round=None)
+        for rep in range(2):
+            y, _ = _run(capi, x, q, s, z, b, capi.ZT_ALGO_SKINNY | (2 << 8))
+            assert_close_bf16(y, ref, what=f"stream-K M={m} K={k} N={n} rep {rep}")
+            assert_close_bf16(y, exact, rtol=8e-3, atol=4e-3, what=f"stream-K M={m} K={k} N={n} vs exact")
 
 
 def test_generic_odd_shapes(capi):

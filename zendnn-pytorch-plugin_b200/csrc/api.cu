@@ -69,32 +69,53 @@ int validate_post_ops(const zt_post_ops_t &p) {
   return ZT_SUCCESS;
 }
 
-int make_tensor_map_2d(CUtensorMap *out, const void *base, CUtensorMapDataType dtype, uint32_t elem_bytes,
-                       uint64_t inner, uint64_t rows, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows) {
+namespace {
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
   static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
   if (!encode) {
     void *fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
     cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
-    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
-      set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
-      return ZT_CUDA_ERROR;
-    }
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return nullptr;
     encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
   }
-  const cuuint64_t dims[2] = {inner, rows};
-  const cuuint64_t strides[1] = {pitch_bytes};
-  const cuuint32_t box[2] = {box_inner, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  (void)elem_bytes;
-  CUresult r = encode(out, dtype, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return encode;
+}
+}  // namespace
+
+int make_tensor_map(CUtensorMap *out, const void *base, CUtensorMapDataType dtype, int rank, const uint64_t *dims,
+                    const uint64_t *strides_bytes, const uint32_t *box, bool swizzle128) {
+  PFN_cuTensorMapEncodeTiled_v12000 encode = tensor_map_encoder();
+  if (!encode) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return ZT_CUDA_ERROR;
+  }
+  cuuint64_t d[5], st[4];
+  cuuint32_t b[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) st[i] = strides_bytes[i];
+  }
+  CUresult r = encode(out, dtype, (cuuint32_t)rank, const_cast<void *>(base), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner %llu, rows %llu, pitch %llu, box %u x %u)", (int)r,
-              (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)pitch_bytes, box_inner, box_rows);
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu, box %u x %u)", (int)r, rank,
+              (unsigned long long)dims[0], (unsigned long long)dims[1], box[0], box[1]);
     return ZT_CUDA_ERROR;
   }
   return ZT_SUCCESS;
+}
+
+int make_tensor_map_2d(CUtensorMap *out, const void *base, CUtensorMapDataType dtype, uint32_t elem_bytes,
+                       uint64_t inner, uint64_t rows, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows) {
+  (void)elem_bytes;
+  const uint64_t dims[2] = {inner, rows};
+  const uint64_t strides[1] = {pitch_bytes};
+  const uint32_t box[2] = {box_inner, box_rows};
+  return make_tensor_map(out, base, dtype, 2, dims, strides, box, true);
 }
 
 namespace {
@@ -109,9 +130,11 @@ int env_int(const char *name, int dflt) {
 // Read-once 0/1 style switches, in the manner of the reference's EnvReader
 // (src/cpu/cpp/EnvReader.hpp:41-60).
 struct Env {
+  int woq_streamk;     // ZENTORCH_B200_WOQ_STREAMK: 0 = use the register-ring decode kernel instead of stream-K
   int woq_skinny_max;  // ZENTORCH_B200_WOQ_SKINNY_MAX_M: largest M given to the streaming kernel
   int int8_bn;         // ZENTORCH_B200_INT8_BN: force the int8 tensor-core tile width
   Env() {
+    woq_streamk = env_int("ZENTORCH_B200_WOQ_STREAMK", 1);
     woq_skinny_max = env_int("ZENTORCH_B200_WOQ_SKINNY_MAX_M", 256);
     int8_bn = env_int("ZENTORCH_B200_INT8_BN", 0);
   }
@@ -151,7 +174,9 @@ extern "C" size_t zt_woq_linear_workspace_bytes(int64_t M, int64_t N, int64_t K)
   if (M <= 0 || N <= 0 || K <= 0) return ZT_WOQ_COUNTER_BYTES;
   const size_t a = woq_skinny_plan(M, N, K).partial_bytes;
   const size_t b = woq_stream_plan(M < 16 ? M : 16, N, K).partial_bytes;
-  return ZT_WOQ_COUNTER_BYTES + (a > b ? a : b);
+  const size_t c = woq_streamk_workspace_bytes();
+  const size_t m = a > b ? a : b;
+  return ZT_WOQ_COUNTER_BYTES + (m > c ? m : c);
 }
 
 extern "C" int zt_woq_linear(const zt_woq_linear_args_t *a, void *stream) {
@@ -188,6 +213,11 @@ extern "C" int zt_woq_linear(const zt_woq_linear_args_t *a, void *stream) {
   switch (algo) {
     case ZT_ALGO_GENERIC: return woq_generic_launch(*a, st);
     case ZT_ALGO_SKINNY:
+      // tile hint 1 forces the register-ring decode kernel, 2 the stream-K kernel (tests, benchmarks)
+      if (((a->algo >> 8) & 0xffff) != 1 && (env().woq_streamk || ((a->algo >> 8) & 0xffff) == 2) &&
+          woq_streamk_supported(*a) &&
+          a->workspace_bytes >= ZT_WOQ_COUNTER_BYTES + woq_streamk_workspace_bytes())
+        return woq_streamk_launch(*a, st);
       if (stream_ok) return woq_stream_launch(*a, st);
       ZT_REQUIRE(woq_skinny_supported(*a), ZT_UNSUPPORTED,
                  "zt_woq_linear: the streaming kernels need K and the group size to be multiples of 128 and 16-byte "

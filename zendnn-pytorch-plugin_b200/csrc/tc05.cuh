@@ -75,6 +75,14 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
 
+// 3-D tile load global -> shared (c0 innermost).
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *m, uint64_t *bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
 // 2-D tile load global -> shared, completion counted in bytes on `bar`.  c0 is the innermost
 // coordinate (must be a multiple of 16 bytes worth of elements), c1 the row.
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *m, uint64_t *bar, int c0, int c1) {
@@ -167,6 +175,11 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // Encodes a 2-D row-major tensor map (inner extent `inner` elements of `elem_bytes`, `rows` rows,
 // row pitch `pitch_bytes`) with a box of box_inner x box_rows and the 128-byte swizzle.  Returns
 // ZT_SUCCESS or an error (message set).
+// General form: `rank` dimensions (innermost first), `strides_bytes` for dimensions 1..rank-1 (multiples
+// of 16), a box per dimension, with or without the 128-byte swizzle.  Out-of-bounds elements read as zero.
+int make_tensor_map(CUtensorMap *out, const void *base, CUtensorMapDataType dtype, int rank, const uint64_t *dims,
+                    const uint64_t *strides_bytes, const uint32_t *box, bool swizzle128);
+
 int make_tensor_map_2d(CUtensorMap *out, const void *base, CUtensorMapDataType dtype, uint32_t elem_bytes,
                        uint64_t inner, uint64_t rows, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows);
 

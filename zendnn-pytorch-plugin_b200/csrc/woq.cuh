@@ -25,6 +25,11 @@ WoqStreamPlan woq_stream_plan(int64_t M, int64_t N, int64_t K);
 bool woq_stream_supported(const zt_woq_linear_args_t &a);
 int woq_stream_launch(const zt_woq_linear_args_t &a, cudaStream_t st);
 
+// Decode kernel (M <= 16), bulk-copy staged and work-balanced; needs the fixed scratch below.
+size_t woq_streamk_workspace_bytes();
+bool woq_streamk_supported(const zt_woq_linear_args_t &a);
+int woq_streamk_launch(const zt_woq_linear_args_t &a, cudaStream_t st);
+
 // Mid-size M (17..64 per launch) on mma.sync, weights re-read once per 64 rows.
 WoqSkinnyPlan woq_skinny_plan(int64_t M, int64_t N, int64_t K);
 bool woq_skinny_supported(const zt_woq_linear_args_t &a);
