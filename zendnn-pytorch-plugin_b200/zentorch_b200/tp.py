@@ -1,0 +1,146 @@
+"""Tensor-parallel sharding of the quantized linears across the GPUs of one box.
+
+The reference has no communication code; it only makes its int4 tensors sliceable so that vLLM's
+tensor-parallel loader can ``narrow()`` them (slicing rules:
+src/cpu/python/zentorch/vllm/_torchao_int4_opaque_patch.py:93-163).  This module is the B200-side
+equivalent for 70B-class layers: Megatron-style column-parallel (shard N) and row-parallel (shard K on
+quantisation-group boundaries) linears, one process per GPU, with NCCL collectives only at the shard
+boundaries -- an all-reduce after a row-parallel linear, an all-gather when a column-parallel output
+is needed whole.
+
+The compute is ``torch.ops.zentorch.*`` (the CUDA kernels); ``linear_fn`` can be replaced, which is
+how the CPU test-suite checks the sharding and collective logic with gloo ranks.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+# ---- slicing ------------------------------------------------------------------------------------------
+def shard_woq(weight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor],
+              bias: Optional[torch.Tensor], mode: str, rank: int, world: int):
+    """Slice a packed WOQ linear for one rank.  ``weight`` is the op's argument: shape [K/8, N], strides
+    (1, K/8).  'column' keeps columns [rank*N/world, (rank+1)*N/world); 'row' keeps the K range of the
+    same fraction, which must fall on quantisation-group boundaries.  Slices keep the layout contract."""
+    k8, n = weight.shape
+    groups = scales.shape[0]
+    if mode == "column":
+        if n % world != 0:
+            raise ValueError(f"N ({n}) must be divisible by the tensor-parallel size ({world})")
+        n0, n1 = rank * n // world, (rank + 1) * n // world
+        w = weight.t()[n0:n1].contiguous().t()
+        return (w, scales[:, n0:n1].contiguous(), None if zeros is None else zeros[:, n0:n1].contiguous(),
+                None if bias is None else bias[n0:n1].contiguous())
+    if mode == "row":
+        if groups % world != 0:
+            raise ValueError("row-parallel shards must fall on quantization-group boundaries: "
+                             f"{groups} groups over {world} ranks")
+        gs = k8 * 8 // groups
+        g0, g1 = rank * groups // world, (rank + 1) * groups // world
+        w = weight.t()[:, g0 * gs // 8: g1 * gs // 8].contiguous().t()
+        return (w, scales[g0:g1].contiguous(), None if zeros is None else zeros[g0:g1].contiguous(),
+                bias if rank == 0 else None)
+    raise ValueError(f"unknown shard mode {mode!r}")
+
+
+def shard_int8(weight: torch.Tensor, w_scales: torch.Tensor, bias: Optional[torch.Tensor], mode: str, rank: int,
+               world: int):
+    """Slice a dynamic-int8 linear ([N, K] int8, per-channel scales [N]).  Row-parallel ranks quantise
+    their own K-slice of the activations with their own per-token scale."""
+    n, k = weight.shape
+    if mode == "column":
+        n0, n1 = rank * n // world, (rank + 1) * n // world
+        return weight[n0:n1].contiguous(), w_scales.reshape(-1)[n0:n1].contiguous(), \
+            None if bias is None else bias[n0:n1].contiguous()
+    if mode == "row":
+        if k % (16 * world) != 0:
+            raise ValueError(f"K ({k}) must split into multiples of 16 over {world} ranks")
+        k0, k1 = rank * k // world, (rank + 1) * k // world
+        return weight[:, k0:k1].contiguous(), w_scales.reshape(-1).contiguous(), bias if rank == 0 else None
+    raise ValueError(f"unknown shard mode {mode!r}")
+
+
+# ---- layers -------------------------------------------------------------------------------------------
+def _woq_op(x, w, s, z, b):
+    return torch.ops.zentorch.zentorch_woq_linear(x, w, s, z, b)
+
+
+def _int8_op(x, w, s, b):
+    return torch.ops.zentorch.zentorch_dynamic_qlinear(x, w, s, b)
+
+
+@dataclass
+class ParallelLinear:
+    """One shard of a column- or row-parallel quantized linear.
+
+    kind 'woq':  params = (weight [K/8, N_shard] view, scales, zeros, bias)
+    kind 'int8': params = (weight [N_shard, K_shard], w_scales, bias)
+    """
+    kind: str
+    mode: str
+    params: tuple
+    group: Optional[dist.ProcessGroup] = None
+    linear_fn: Optional[Callable] = None
+    reduce_dtype: Optional[torch.dtype] = None   # e.g. torch.float32 for a tighter row-parallel sum
+
+    def local(self, x: torch.Tensor) -> torch.Tensor:
+        fn = self.linear_fn or (_woq_op if self.kind == "woq" else _int8_op)
+        return fn(x, *self.params)
+
+    def __call__(self, x: torch.Tensor, gather_output: bool = False) -> torch.Tensor:
+        """column: x is replicated, the result is this rank's columns (all-gathered when asked).
+        row: x is this rank's K-slice, the result is the all-reduced full output."""
+        y = self.local(x)
+        world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        if world == 1:
+            return y
+        if self.mode == "row":
+            if self.reduce_dtype is not None and y.dtype != self.reduce_dtype:
+                yr = y.to(self.reduce_dtype)
+                dist.all_reduce(yr, group=self.group)
+                return yr.to(y.dtype)
+            dist.all_reduce(y, group=self.group)
+            return y
+        if gather_output:
+            parts = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(parts, y.contiguous(), group=self.group)
+            return torch.cat(parts, dim=-1)
+        return y
+
+
+def make_parallel_woq(weight, scales, zeros, bias, mode, group=None, linear_fn=None, reduce_dtype=None):
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    return ParallelLinear("woq", mode, shard_woq(weight, scales, zeros, bias, mode, rank, world), group, linear_fn,
+                          reduce_dtype)
+
+
+def make_parallel_int8(weight, w_scales, bias, mode, group=None, linear_fn=None, reduce_dtype=None):
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    return ParallelLinear("int8", mode, shard_int8(weight, w_scales, bias, mode, rank, world), group, linear_fn,
+                          reduce_dtype)
+
+
+class ParallelMLP:
+    """gate/up column-parallel -> silu(gate) * up -> down row-parallel: one collective per call (the
+    all-reduce of the down projection), activations between the two stay sharded."""
+
+    def __init__(self, gate: ParallelLinear, up: ParallelLinear, down: ParallelLinear):
+        self.gate, self.up, self.down = gate, up, down
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        h = torch.nn.functional.silu(self.gate(x).float()) * self.up(x).float()
+        return self.down(h.to(x.dtype))
+
+
+def slice_activation_for_row_parallel(x: torch.Tensor, group=None) -> torch.Tensor:
+    """The K-slice of a replicated activation that a row-parallel shard consumes."""
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    k = x.shape[-1]
+    return x[..., rank * k // world:(rank + 1) * k // world].contiguous()
