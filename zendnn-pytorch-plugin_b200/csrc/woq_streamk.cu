@@ -396,24 +396,29 @@ struct Maps {
 
 struct MapKey {
   const void *ptr;
-  uint64_t d0, d1, d2;
+  uint64_t d0, d1, d2, s0, s1;
   uint32_t b0, b1, b2;
+  int dtype;
   bool operator==(const MapKey &o) const {
-    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && b0 == o.b0 && b1 == o.b1 && b2 == o.b2;
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && s0 == o.s0 && s1 == o.s1 && b0 == o.b0 &&
+           b1 == o.b1 && b2 == o.b2 && dtype == o.dtype;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey &k) const {
-    return std::hash<const void *>()(k.ptr) ^ (k.d0 * 1315423911u) ^ (k.d1 << 17) ^ (k.d2 << 29) ^ k.b1 ^ (k.b2 << 9);
+    return std::hash<const void *>()(k.ptr) ^ (k.d0 * 1315423911u) ^ (k.d1 << 17) ^ (k.d2 << 29) ^ k.b1 ^ (k.b2 << 9) ^
+           (k.s0 << 3) ^ (size_t)k.dtype;
   }
 };
 
-// Tensor maps depend only on (pointer, shape, box); they are memoised per process.
+// Tensor maps depend only on (pointer, element type, shape, strides, box); they are memoised per
+// process.  The element type and strides are part of the key: the allocator reuses addresses.
 int cached_map(CUtensorMap *out, const void *ptr, CUtensorMapDataType dt, int rank, const uint64_t *dims,
                const uint64_t *strides, const uint32_t *box) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  const MapKey key{ptr, dims[0], dims[1], rank > 2 ? dims[2] : 0, box[0], box[1], rank > 2 ? box[2] : 0};
+  const MapKey key{ptr,    dims[0], dims[1], rank > 2 ? dims[2] : 0, strides[0], rank > 2 ? strides[1] : 0,
+                   box[0], box[1],  rank > 2 ? box[2] : 0, (int)dt};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
