@@ -147,7 +147,7 @@ def test_streamk_kernel(capi, m):
         ref = O.woq_linear(x, O.woq_repack_weight(q).t(), s, z, b)
         exact = O.woq_linear(x, O.woq_repack_weight(q).t(), s, z, b, dq_round=None)
         for rep in range(2):
-            y, _ = _run(capi, x, q, s, z, b, capi.ZT_ALGO_SKINNY | (2 << 8))
+            y, _ = _run(capi, x, q, s, z, b, capi.ZT_ALGO_SKINNY | (2 << 8))   # hint 2: stream-K kernel
             assert_close_bf16(y, ref, what=f"stream-K M={m} K={k} N={n} rep {rep}")
             assert_close_bf16(y, exact, rtol=8e-3, atol=4e-3, what=f"stream-K M={m} K={k} N={n} vs exact")
 

@@ -58,7 +58,7 @@ struct SKParams {
   int *counters;   // one per column tile, zero on entry and on exit
   int *status;
   int M, N, K;
-  int gs;
+  int gs, spg;  // group size in k and in cells
   int ksteps, ntiles;
   long long total_cells;
   int scale_dtype, bias_dtype;
@@ -103,24 +103,32 @@ struct Chunk {
   bool last_of_segment;
 };
 
-// Walks the chunks of this CTA's cell range in order.
+// Walks the chunks of this CTA's cell range in order.  The only division is in the constructor; the
+// per-chunk step is additions and compares (the loop runs once per chunk in every warp).
 struct ChunkIter {
-  long long c, c_end;
-  int ksteps;
-  __device__ ChunkIter(long long c0, long long c1, int ks) : c(c0), c_end(c1), ksteps(ks) {}
+  int tile, step, ksteps;
+  long long remaining;
+  __device__ ChunkIter(long long c0, long long c1, int ks) : ksteps(ks), remaining(c1 - c0) {
+    tile = (int)(c0 / ks);
+    step = (int)(c0 - (long long)tile * ks);
+  }
   __device__ bool next(Chunk &ch) {
-    if (c >= c_end) return false;
-    const int tile = (int)(c / ksteps);
-    const int step0 = (int)(c - (long long)tile * ksteps);
-    long long seg_end = (long long)(tile + 1) * ksteps;
-    if (seg_end > c_end) seg_end = c_end;
-    int n = (int)(seg_end - c);
+    if (remaining <= 0) return false;
+    int n = ksteps - step;                      // cells left in this column tile
+    const bool tile_ends = (long long)n <= remaining && n <= kChunkSteps;
+    if ((long long)n > remaining) n = (int)remaining;
+    const bool range_ends = (long long)n == remaining && n <= kChunkSteps;
     if (n > kChunkSteps) n = kChunkSteps;
     ch.tile = tile;
-    ch.step0 = step0;
+    ch.step0 = step;
     ch.nsteps = n;
-    ch.last_of_segment = (c + n == seg_end);
-    c += n;
+    ch.last_of_segment = tile_ends || range_ends;
+    remaining -= n;
+    step += n;
+    if (step == ksteps) {
+      step = 0;
+      ++tile;
+    }
     return true;
   }
 };
@@ -165,11 +173,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ---------------- producer warp ----------------
     ChunkIter iter(c_begin, c_end, p.ksteps);
     Chunk ch;
-    uint32_t it = 0;
+    uint32_t s = 0, ph = 0;  // ring position and its phase bit
     bool ok = true;
     while (ok && iter.next(ch)) {
-      const uint32_t s = it % p.stages;
-      const uint32_t ph = (it / p.stages) & 1;
       if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
         tc::report_timeout(p.status, kStatusProducerTimeout);
         ok = false;
@@ -177,7 +183,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       unsigned char *stage = smem + (size_t)s * p.stage_bytes;
       const int n0 = ch.tile * kTileN;
-      const int g0 = ch.step0 * kStepK / p.gs;
+      const int g0 = p.spg == 1 ? ch.step0 : ch.step0 / p.spg;
       if (lane == 0) {
         tc::mbar_expect_tx(&full_bar[s], (uint32_t)kWBytes + (uint32_t)mrows * kXRowBytes +
                                              (uint32_t)kSBytes * (ASYM ? 2u : 1u));
@@ -187,7 +193,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (ASYM) tc::tma_load_2d(stage + kZOff, &map_z, &full_bar[s], n0, g0);
       }
       __syncwarp();
-      ++it;
+      if (++s == (uint32_t)p.stages) {
+        s = 0;
+        ph ^= 1;
+      }
     }
   } else {
     // ---------------- compute warps ----------------
@@ -204,19 +213,17 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     ChunkIter iter(c_begin, c_end, p.ksteps);
     Chunk ch;
-    uint32_t it = 0;
+    uint32_t s = 0, ph = 0;
     bool ok = true;
     while (iter.next(ch)) {
-      const uint32_t s = it % p.stages;
-      const uint32_t ph = (it / p.stages) & 1;
       if (ok && !tc::mbar_wait(&full_bar[s], ph)) {
         tc::report_timeout(p.status, kStatusConvertTimeout);
         ok = false;
       }
       const unsigned char *stage = smem + (size_t)s * p.stage_bytes;
       if (ok && my_step < ch.nsteps) {
-        const int k_start = ch.step0 * kStepK;
-        const int gl = (k_start + my_step * kStepK) / p.gs - k_start / p.gs;  // group within the chunk
+        // group of this warp's cell, relative to the chunk's first group (spg = cells per group)
+        const int gl = p.spg == 1 ? my_step : (ch.step0 + my_step) / p.spg - ch.step0 / p.spg;
         uint4 wv[2][2];
         float sc[2][2], zp[2][2];
 #pragma unroll
@@ -294,7 +301,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&empty_bar[s]);
-      ++it;
+      if (++s == (uint32_t)p.stages) {
+        s = 0;
+        ph ^= 1;
+      }
 
       if (ch.last_of_segment) {
         // ---- the segment of tile ch.tile is complete: combine the warps, then finish or hand over ----
@@ -521,6 +531,7 @@ int woq_streamk_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   p.scale_dtype = a.scale_dtype;
   p.bias_dtype = a.bias_dtype;
   p.gs = (int)(a.K / a.n_groups);
+  p.spg = p.gs / kStepK;
   p.ksteps = (int)(a.K / kStepK);
   p.ntiles = (int)ceil_div<int64_t>(a.N, kTileN);
   p.total_cells = (long long)p.ntiles * p.ksteps;
