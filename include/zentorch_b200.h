@@ -213,6 +213,41 @@ ZT_API int zt_int8_gemm_s32(const void *q, int32_t q_is_u8, const int8_t *w, int
 /* rowsum[n] = sum_k W[n,k]; a one-off weight-prepack by-product used by ZT_ACT_U8_ASYM. */
 ZT_API int zt_int8_weight_rowsum(const int8_t *w, int64_t N, int64_t K, int32_t *rowsum, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Mixture-of-experts FFN with int4 weight-only experts (Mixtral style, symmetric group-wise scales).
+ * The reference's zentorch_fused_moe (src/cpu/cpp/FusedMoE.cpp:470-744) takes bf16 / fp32 / int8 expert
+ * weights only (src/cpu/cpp/GroupMatmul.cpp:104-108); this is the int4 form with the same structure:
+ * per-expert token groups (FusedMoE.cpp:289-436), h = x_e . W13_e with [gate | up] columns, gate first
+ * (src/cpu/python/zentorch/vllm/_int8_moe_patch.py:48-50), a = silu(gate) * up, o = a . W2_e,
+ * y[t] = sum_j topk_weights[t,j] * o_j[t].
+ *
+ * x            [T, H] bf16                      y  [T, H] bf16
+ * topk_ids     [T, top_k] int32; ids outside [0, num_experts) are skipped (expert-parallel ranks)
+ * topk_weights [T, top_k] fp32
+ * w13          [E, 2I, H/8] int32, every expert in the zentorch_woq_linear weight layout (N-major)
+ * s13          [E, H/group_size, 2I]            w2 [E, H, I/8]        s2 [E, I/group_size, H]
+ * workspace    zt_moe_woq_workspace_bytes() bytes, 256-byte aligned
+ * No host synchronisation: group sizes stay on the device. */
+typedef struct {
+  const void *x;
+  int64_t T, H, I;
+  int32_t num_experts, top_k;
+  const int32_t *topk_ids;
+  const float *topk_weights;
+  const int32_t *w13;
+  const void *s13;
+  const int32_t *w2;
+  const void *s2;
+  int32_t scale_dtype;
+  int64_t group_size;
+  void *y;
+  void *workspace;
+  size_t workspace_bytes;
+} zt_moe_woq_args_t;
+
+ZT_API size_t zt_moe_woq_workspace_bytes(int64_t T, int64_t H, int64_t I, int32_t num_experts, int32_t top_k);
+ZT_API int zt_moe_woq(const zt_moe_woq_args_t *args, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

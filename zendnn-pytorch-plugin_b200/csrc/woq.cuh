@@ -39,5 +39,8 @@ int woq_generic_launch(const zt_woq_linear_args_t &a, cudaStream_t st);
 
 bool woq_tcgen05_supported(const zt_woq_linear_args_t &a);
 int woq_tcgen05_launch(const zt_woq_linear_args_t &a, cudaStream_t st);
+int woq_tcgen05_grouped_launch(const void *x, int64_t total_rows, int64_t N, int64_t K, const int32_t *wq,
+                               const void *scales, int scale_dtype, int64_t n_groups, int num_experts, void *y,
+                               const int *tile_count, const int4 *tiles, int max_row_tiles, int bt, cudaStream_t st);
 
 }  // namespace zt

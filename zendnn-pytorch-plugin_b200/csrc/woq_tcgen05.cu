@@ -7,15 +7,22 @@
 // per k-block and reuses it for up to 256 tokens.  One persistent CTA per SM walks over
 // (128 columns) x (BT tokens) tiles; tiles that share a weight block are adjacent in the order.
 //
-//   warp 0        TMA producer for the activation tile (2-D tile load, 128-byte swizzle, no multicast)
+//   warp 0        TMA producer (no multicast): the activation tile of every k-block, and the packed
+//                 weights in chunks of four k-blocks (128 rows x 128 B, 128-byte swizzle) into a ring
+//                 of their own, several chunks ahead, so that enough weight bytes are in flight
 //   warp 1        TMEM allocation, tcgen05.mma.kind::f16 issue (bf16 x bf16 -> fp32), TMEM release
-//   warps 2..9    dequantisation: 128-bit loads of packed nibbles straight from global memory
-//                 (prefetched four k-blocks ahead, with the group's scale / zero point), nibble -> bf16
+//   warps 2..9    dequantisation: 128-bit shared-memory loads of packed nibbles from the chunk ring
+//                 (the group's scale / zero point is prefetched from global memory), nibble -> bf16
 //                 with lop3, exact subtraction of the encoding bias, multiplication by the scale in
 //                 bf16x2 arithmetic, byte-permute into k order, 16-byte stores into the canonical
 //                 K-major 128-byte-swizzled operand layout, fence.proxy.async, mbarrier arrive
 //   warps 10..13  epilogue: tcgen05.ld (lane = output column n, register j = token), transpose
 //                 through shared memory so that stores run along n, bias + post-ops, bf16 stores
+//
+// Grouped mode (mixture-of-experts): the rows of X are sorted by expert, a device-side table lists the
+// row tiles {expert, first row, valid rows}, and each tile uses its expert's slice of the stacked
+// weight and scale tensors; the number of tiles is read from device memory, so no host
+// synchronisation is needed between routing and the GEMM.
 //
 // Accumulators are double buffered in tensor memory: the epilogue of a tile overlaps the next tile's
 // main loop.  All waits are bounded (see tc05.cuh).
@@ -41,6 +48,8 @@ constexpr int kDqWarps = 8;
 constexpr int kEpiWarps = 4;
 constexpr int kThreads = 64 + 32 * (kDqWarps + kEpiWarps);
 constexpr int kEpiRowStride = 36;  // floats; 144 bytes keeps 16-byte alignment and spreads banks
+constexpr int kChunkKB = 4;        // k-blocks per packed-weight chunk: 4 x 32 B = one 128-byte row
+constexpr int kChunkBytes = kBN * 128;
 
 struct TcParams {
   int M, N, K;
@@ -55,17 +64,43 @@ struct TcParams {
   __nv_bfloat16 *y;
   PostOpsDev post;
   int *status;
+  // grouped mode (g_count != nullptr)
+  const int *g_count;     // number of row tiles
+  const int4 *g_tiles;    // per row tile: {expert, first row, valid rows, 0}
+  long long s_estride;    // elements between two experts' scale tables
 };
 
-template <int BT, int STAGES>
+struct TileInfo {
+  int m0, rows, n0, expert;
+};
+
+__device__ __forceinline__ TileInfo decode_tile(const TcParams &p, int tile, int n_mt, int bt) {
+  TileInfo t;
+  const int mt = tile % n_mt;
+  t.n0 = (tile / n_mt) * kBN;
+  if (p.g_count) {
+    const int4 g = p.g_tiles[mt];
+    t.expert = g.x;
+    t.m0 = g.y;
+    t.rows = g.z;
+  } else {
+    t.expert = 0;
+    t.m0 = mt * bt;
+    t.rows = min(bt, p.M - t.m0);
+  }
+  return t;
+}
+
+template <int BT, int STAGES, int PSTAGES>
 struct SmemLayout {
   static constexpr int kWBytes = kBN * 128;
   static constexpr int kXBytes = BT * 128;
   static constexpr int kStageBytes = kWBytes + kXBytes;
   static constexpr int kTileBytes = STAGES * kStageBytes;
+  static constexpr int kPackedBytes = PSTAGES * kChunkBytes;
   static constexpr int kEpiBytes = kEpiWarps * 32 * kEpiRowStride * 4;
-  static constexpr int kBarBytes = (3 * STAGES + 4) * 8 + 8;
-  static constexpr int kTotal = kTileBytes + kEpiBytes + kBarBytes + 1024;
+  static constexpr int kBarBytes = (3 * STAGES + 2 * PSTAGES + 4) * 8 + 8;
+  static constexpr int kTotal = kTileBytes + kPackedBytes + kEpiBytes + kBarBytes + 1024;
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -108,35 +143,45 @@ __device__ __forceinline__ void split_bf16x2(float v, uint32_t &hi2, uint32_t &l
 }
 
 struct DqRegs {
-  uint4 w;
   float s, z;
 };
 
-template <int BT, int STAGES, bool ASYM>
+template <int BT, int STAGES, int PSTAGES, bool ASYM>
 __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                                                                  const __grid_constant__ CUtensorMap tmap_w,
                                                                   const TcParams p) {
-  using L = SmemLayout<BT, STAGES>;
+  using L = SmemLayout<BT, STAGES, PSTAGES>;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char *smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
-  float *epi_scratch = reinterpret_cast<float *>(smem + L::kTileBytes);
-  uint64_t *full_x = reinterpret_cast<uint64_t *>(smem + L::kTileBytes + L::kEpiBytes);
+  unsigned char *packed = smem + L::kTileBytes;  // ring of packed-weight chunks (1024-byte aligned)
+  float *epi_scratch = reinterpret_cast<float *>(smem + L::kTileBytes + L::kPackedBytes);
+  uint64_t *full_x = reinterpret_cast<uint64_t *>(smem + L::kTileBytes + L::kPackedBytes + L::kEpiBytes);
   uint64_t *full_w = full_x + STAGES;
   uint64_t *empty_bar = full_w + STAGES;
-  uint64_t *tmem_full = empty_bar + STAGES;  // [2]
+  uint64_t *full_p = empty_bar + STAGES;     // packed chunk landed
+  uint64_t *empty_p = full_p + PSTAGES;      // packed chunk consumed by all dequantisation warps
+  uint64_t *tmem_full = empty_p + PSTAGES;   // [2]
   uint64_t *tmem_empty = tmem_full + 2;      // [2]
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
 
   constexpr uint32_t kTmemCols = 2 * BT <= 32 ? 32 : 2 * BT <= 64 ? 64 : 2 * BT <= 128 ? 128 : 2 * BT <= 256 ? 256 : 512;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = p.K / kBK;
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int num_chunks = (num_kb + kChunkKB - 1) / kChunkKB;
+  const int n_mt = p.g_count ? *p.g_count : p.m_tiles;
+  const int total_tiles = n_mt * p.n_tiles;
 
   if (threadIdx.x == 0) {
     tc::prefetch_tensormap(&tmap_x);
+    tc::prefetch_tensormap(&tmap_w);
     for (int s = 0; s < STAGES; ++s) {
       tc::mbar_init(&full_x[s], 1);
       tc::mbar_init(&full_w[s], kDqWarps);
       tc::mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < PSTAGES; ++s) {
+      tc::mbar_init(&full_p[s], 1);
+      tc::mbar_init(&empty_p[s], kDqWarps);
     }
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(&tmem_full[b], 1);
@@ -151,13 +196,51 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---------------- TMA producer: activation tiles ----------------
+    // ---------------- TMA producer: packed-weight chunks (running ahead) and activation tiles ----------------
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0;   // activation stage ring position
+      uint32_t pit = 0;  // packed chunk ring position
       bool ok = true;
+      // Issues the next packed chunk if its ring slot is free (or, when `must`, waits for the slot).
+      int ptile = blockIdx.x, pchunk = 0;  // next chunk to issue
+      auto issue_packed = [&](bool must) -> bool {
+        if (ptile >= total_tiles) return false;
+        const uint32_t ps = pit % PSTAGES;
+        const uint32_t pph = (pit / PSTAGES) & 1;
+        if (must) {
+          if (!tc::mbar_wait(&empty_p[ps], pph ^ 1)) {
+            tc::report_timeout(p.status, kStatusProducerTimeout);
+            ok = false;
+            return false;
+          }
+        } else {
+          uint32_t done;
+          asm volatile(
+              "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+              : "=r"(done)
+              : "r"(smem_u32(&empty_p[ps])), "r"(pph ^ 1)
+              : "memory");
+          if (!done) return false;
+        }
+        const TileInfo t = decode_tile(p, ptile, n_mt, BT);
+        tc::mbar_expect_tx(&full_p[ps], kChunkBytes);
+        // rows of the stacked weight: expert * N + n0 ; 32 words (four k-blocks) per row
+        tc::tma_load_2d(packed + ps * kChunkBytes, &tmap_w, &full_p[ps], pchunk * (kChunkKB * 8), t.expert * p.N + t.n0);
+        ++pit;
+        if (++pchunk == num_chunks) {
+          pchunk = 0;
+          ptile += gridDim.x;
+        }
+        return true;
+      };
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.m_tiles) * BT;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const TileInfo t = decode_tile(p, tile, n_mt, BT);
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+          // keep the packed ring full without blocking; the chunk this k-block needs must be issued
+          while (issue_packed(false)) {
+          }
+          const long long need = (long long)((tile - blockIdx.x) / gridDim.x) * num_chunks + kb / kChunkKB;
+          while (ok && (long long)pit <= need) issue_packed(true);
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
@@ -166,7 +249,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
             break;
           }
           tc::mbar_expect_tx(&full_x[s], L::kXBytes);
-          tc::tma_load_2d(smem + s * L::kStageBytes + L::kWBytes, &tmap_x, &full_x[s], kb * kBK, m0);
+          tc::tma_load_2d(smem + s * L::kStageBytes + L::kWBytes, &tmap_x, &full_x[s], kb * kBK, t.m0);
         }
       }
     }
@@ -213,17 +296,15 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
     const int d = threadIdx.x - 64;   // 0..255
     const int row = d >> 1;           // weight row (output column) within the tile
     const int half = d & 1;           // which 32 k of the 64-wide k-block
-    const int k8 = p.K >> 3;
+    // scales (and zero points) come from global memory, fetched kPrefetch k-blocks ahead
     auto fetch = [&](int tile, int kb, DqRegs &r) {
-      const int n = min((tile / p.m_tiles) * kBN + row, p.N - 1);
+      const TileInfo t = decode_tile(p, tile, n_mt, BT);
+      const int n = min(t.n0 + row, p.N - 1);
       const int k = kb * kBK + 32 * half;
-      r.w = ldg_nc_v4(p.wq + (size_t)n * k8 + (k >> 3));
-      const int64_t gi = (int64_t)(k / p.gs) * p.N + n;
+      const int64_t gi = (int64_t)t.expert * p.s_estride + (int64_t)(k / p.gs) * p.N + n;
       r.s = load_as_float(p.scales, gi, p.scale_dtype);
       r.z = ASYM ? load_as_float(p.zeros, gi, p.scale_dtype) : 0.f;
     };
-    // The packed words and scales are fetched kPrefetch k-blocks ahead into a register ring, so that
-    // several global loads per thread are in flight while one k-block is converted.
     constexpr int kPrefetch = 4;
     DqRegs ring[kPrefetch];
     int ftile = blockIdx.x, fkb = 0;  // next (tile, k-block) to fetch
@@ -238,7 +319,9 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
     };
 #pragma unroll
     for (int i = 0; i < kPrefetch; ++i) fetch_next(ring[i]);
-    uint32_t it = 0;
+    uint32_t it = 0;    // k-blocks converted so far (bf16 stage ring position)
+    uint32_t pit = 0;   // packed chunks consumed so far
+    int kb = 0;         // k-block within the current tile
     bool ok = true;
     const bool exact_scale = (p.scale_dtype == ZT_BF16);
     const int my_tiles = blockIdx.x < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
@@ -249,6 +332,12 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
         if (it < total_it) {
           const DqRegs cur = ring[slot_i];
           fetch_next(ring[slot_i]);
+          const int j = kb % kChunkKB;  // k-block within the packed chunk
+          const uint32_t ps = pit % PSTAGES;
+          if (j == 0 && ok && !tc::mbar_wait(&full_p[ps], (pit / PSTAGES) & 1)) {
+            tc::report_timeout(p.status, kStatusConvertTimeout);
+            ok = false;
+          }
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (ok && !tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
@@ -256,8 +345,11 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
             ok = false;
           }
           if (ok) {
+            // this thread's 32 nibbles of the k-block: 16-byte chunk (2j + half) of the swizzled 128-byte row
+            const uint4 wv = *reinterpret_cast<const uint4 *>(packed + ps * kChunkBytes + row * 128 +
+                                                              (((2 * j + half) ^ (row & 7)) << 4));
             unsigned char *wrow = smem + s * L::kStageBytes + row * 128;
-            const uint32_t words[4] = {cur.w.x, cur.w.y, cur.w.z, cur.w.w};
+            const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
             uint32_t s_hi = 0, s_lo = 0;
             if (!ASYM) split_bf16x2(cur.s, s_hi, s_lo);
 #pragma unroll
@@ -300,6 +392,13 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(&full_w[s]);
           ++it;
+          ++kb;
+          const bool tile_done = (kb == num_kb);
+          if (j == kChunkKB - 1 || tile_done) {  // the packed chunk is used up
+            if (lane == 0) tc::mbar_arrive(&empty_p[ps]);
+            ++pit;
+          }
+          if (tile_done) kb = 0;
         }
       }
     }
@@ -311,8 +410,9 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
     int local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
-      const int m0 = (tile % p.m_tiles) * BT;
-      const int n0 = (tile / p.m_tiles) * kBN;
+      const TileInfo ti = decode_tile(p, tile, n_mt, BT);
+      const int m0 = ti.m0, n0 = ti.n0;
+      const int m_end = ti.m0 + ti.rows;  // rows past the tile's valid rows belong to nobody (or to the next expert)
       const uint32_t buf = local & 1;
       const uint32_t use = (uint32_t)local >> 1;
       if (ok && !tc::mbar_wait(&tmem_full[buf], use & 1)) {
@@ -346,7 +446,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
           const int j = pass * 4 + sub_row;
           const int m = m0 + c + j;
           const float4 v4 = *reinterpret_cast<const float4 *>(&scratch[j * kEpiRowStride + col4]);
-          if (m < p.M && nq + col4 < p.N) {
+          if (m < m_end && nq + col4 < p.N) {
             float v[4] = {v4.x + bias4[0], v4.y + bias4[1], v4.z + bias4[2], v4.w + bias4[3]};
             const int64_t base = (int64_t)m * p.N + nq + col4;
             if (p.post.n_ops > 0) {
@@ -400,53 +500,74 @@ struct MapKeyHash {
   }
 };
 
-int cached_x_map(CUtensorMap *out, const void *ptr, uint64_t k, uint64_t rows, uint32_t box_rows) {
+// Tensor maps: activations [rows, K] bf16 with a (64 x BT) box; packed weights [rows, K/8] u32 with a
+// (32 words x 128 rows) box; both 128-byte swizzled.  Memoised per process.
+int cached_map(CUtensorMap *out, const void *ptr, CUtensorMapDataType dt, uint64_t inner, uint64_t rows,
+               uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  const MapKey key{ptr, k, rows, box_rows};
+  const MapKey key{ptr, inner * 4 + (uint64_t)dt % 4, rows, box_rows * 1024 + box_inner};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
     *out = it->second;
     return ZT_SUCCESS;
   }
-  int rc = make_tensor_map_2d(out, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, rows, k * 2, kBK, box_rows);
+  int rc = make_tensor_map_2d(out, ptr, dt, 0, inner, rows, pitch_bytes, box_inner, box_rows);
   if (rc != ZT_SUCCESS) return rc;
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, *out);
   return ZT_SUCCESS;
 }
 
-template <int BT, int STAGES>
-int launch_bt(const TcParams &p0, const void *x, bool asym, cudaStream_t st) {
-  using L = SmemLayout<BT, STAGES>;
+template <int BT, int STAGES, int PSTAGES>
+int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows, int max_row_tiles, bool asym,
+              cudaStream_t st) {
+  using L = SmemLayout<BT, STAGES, PSTAGES>;
+  static_assert(L::kTotal <= 227 * 1024, "rings exceed shared memory");
   TcParams p = p0;
   p.m_tiles = ceil_div(p.M, BT);
   p.n_tiles = ceil_div(p.N, kBN);
-  CUtensorMap tx;
-  int rc = cached_x_map(&tx, x, (uint64_t)p.K, (uint64_t)p.M, BT);
+  CUtensorMap tx, tw;
+  int rc = cached_map(&tx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)p.K, (uint64_t)x_rows, (uint64_t)p.K * 2, kBK, BT);
   if (rc != ZT_SUCCESS) return rc;
-  const int tiles = p.m_tiles * p.n_tiles;
+  rc = cached_map(&tw, p.wq, CU_TENSOR_MAP_DATA_TYPE_UINT32, (uint64_t)p.K / 8, (uint64_t)w_rows, (uint64_t)p.K / 2,
+                  kChunkKB * 8, kBN);
+  if (rc != ZT_SUCCESS) return rc;
+  const long long tiles = (long long)(p.g_count ? max_row_tiles : p.m_tiles) * p.n_tiles;
   const int sms = sm_count();
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   if (asym) {
-    auto kern = woq_tcgen05_kernel<BT, STAGES, true>;
+    auto kern = woq_tcgen05_kernel<BT, STAGES, PSTAGES, true>;
     static bool configured = false;
     if (!configured) {
       ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
       configured = true;
     }
-    kern<<<grid, kThreads, L::kTotal, st>>>(tx, p);
+    kern<<<grid, kThreads, L::kTotal, st>>>(tx, tw, p);
   } else {
-    auto kern = woq_tcgen05_kernel<BT, STAGES, false>;
+    auto kern = woq_tcgen05_kernel<BT, STAGES, PSTAGES, false>;
     static bool configured = false;
     if (!configured) {
       ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
       configured = true;
     }
-    kern<<<grid, kThreads, L::kTotal, st>>>(tx, p);
+    kern<<<grid, kThreads, L::kTotal, st>>>(tx, tw, p);
   }
   return launch_status("woq_tcgen05_kernel");
+}
+
+int launch_any(int bt, const TcParams &p, const void *x, int64_t x_rows, int64_t w_rows, int max_row_tiles, bool asym,
+               cudaStream_t st) {
+  switch (bt) {
+    case 32: return launch_bt<32, 6, 5>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+    case 64: return launch_bt<64, 5, 5>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+    case 128: return launch_bt<128, 4, 4>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+    case 256: return launch_bt<256, 3, 3>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+    default: break;
+  }
+  set_error("zt_woq_linear: unsupported token-tile width %d for the tcgen05 kernel", bt);
+  return ZT_UNSUPPORTED;
 }
 
 }  // namespace
@@ -456,6 +577,7 @@ bool woq_tcgen05_supported(const zt_woq_linear_args_t &a) {
   if (a.n_groups <= 0 || a.K % a.n_groups != 0) return false;
   const int64_t gs = a.K / a.n_groups;
   if (gs % 32 != 0) return false;
+  if (a.K % 32 != 0) return false;  // packed rows are fetched by TMA: pitch K/2 bytes must be a multiple of 16
   if ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.wq)) & 15) return false;
   return a.M <= (1 << 30) && a.N <= (1 << 30) && a.K <= (1 << 30);
 }
@@ -478,15 +600,31 @@ int woq_tcgen05_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   const bool asym = a.zeros != nullptr;
   int bt = (a.algo >> 8) & 0xffff;
   if (bt == 0) bt = a.M <= 32 ? 32 : a.M <= 64 ? 64 : a.M <= 128 ? 128 : 256;
-  switch (bt) {
-    case 32: return launch_bt<32, 8>(p, a.x, asym, st);
-    case 64: return launch_bt<64, 7>(p, a.x, asym, st);
-    case 128: return launch_bt<128, 5>(p, a.x, asym, st);
-    case 256: return launch_bt<256, 4>(p, a.x, asym, st);
-    default: break;
-  }
-  set_error("zt_woq_linear: unsupported token-tile width %d for the tcgen05 kernel", bt);
-  return ZT_UNSUPPORTED;
+  return launch_any(bt, p, a.x, a.M, a.N, 0, asym, st);
+}
+
+// Grouped form for mixture-of-experts: `x` holds `total_rows` rows sorted by expert; `tiles` / `tile_count`
+// (device memory) list the row tiles; weights and scales are stacked per expert.
+int woq_tcgen05_grouped_launch(const void *x, int64_t total_rows, int64_t N, int64_t K, const int32_t *wq,
+                               const void *scales, int scale_dtype, int64_t n_groups, int num_experts, void *y,
+                               const int *tile_count, const int4 *tiles, int max_row_tiles, int bt, cudaStream_t st) {
+  TcParams p{};
+  p.M = (int)total_rows;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.gs = (int)(K / n_groups);
+  p.wq = wq;
+  p.scales = scales;
+  p.zeros = nullptr;
+  p.scale_dtype = scale_dtype;
+  p.bias = nullptr;
+  p.bias_dtype = ZT_BF16;
+  p.y = reinterpret_cast<__nv_bfloat16 *>(y);
+  p.status = device_status_ptr();
+  p.g_count = tile_count;
+  p.g_tiles = tiles;
+  p.s_estride = n_groups * N;
+  return launch_any(bt, p, x, total_rows, (int64_t)num_experts * N, max_row_tiles, false, st);
 }
 
 }  // namespace zt

@@ -27,6 +27,7 @@ EXPORTED_SYMBOLS = (
     "zt_woq_linear_workspace_bytes", "zt_woq_linear", "zt_woq_repack_weight", "zt_woq_repack_from_int4pack",
     "zt_dynamic_qlinear_workspace_bytes", "zt_dynamic_qlinear", "zt_dynamic_quantize", "zt_int8_gemm_s32",
     "zt_int8_weight_rowsum", "zt_qlinear_prequantized", "zt_dynamic_qlinear_static",
+    "zt_moe_woq_workspace_bytes", "zt_moe_woq",
 )
 
 
@@ -49,6 +50,15 @@ class DynamicQLinearArgs(C.Structure):
         ("w", C.c_void_p), ("w_scales", C.c_void_p), ("w_scale_dtype", C.c_int32), ("bias", C.c_void_p),
         ("bias_dtype", C.c_int32), ("act_quant", C.c_int32), ("w_rowsum", C.c_void_p), ("post", PostOps),
         ("y", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("algo", C.c_int32),
+    ]
+
+
+class MoeWoqArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("T", C.c_int64), ("H", C.c_int64), ("I", C.c_int64), ("num_experts", C.c_int32),
+        ("top_k", C.c_int32), ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p), ("w13", C.c_void_p),
+        ("s13", C.c_void_p), ("w2", C.c_void_p), ("s2", C.c_void_p), ("scale_dtype", C.c_int32),
+        ("group_size", C.c_int64), ("y", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -91,6 +101,9 @@ def lib() -> C.CDLL:
     L.zt_int8_gemm_s32.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                    C.c_int32, C.c_void_p]
     L.zt_qlinear_prequantized.argtypes = [C.POINTER(DynamicQLinearArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.zt_moe_woq_workspace_bytes.restype = C.c_size_t
+    L.zt_moe_woq_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32]
+    L.zt_moe_woq.argtypes = [C.POINTER(MoeWoqArgs), C.c_void_p]
     L.zt_int8_weight_rowsum.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
     _lib = L
     return L
@@ -267,4 +280,24 @@ def dynamic_qlinear_static(x, w, w_scales, bias=None, act_quant=ZT_ACT_S8_SYM, p
     y = torch.empty(m, n, dtype=x.dtype, device=x.device)
     a = dynamic_qlinear_args(x, w, w_scales, bias, act_quant, post_ops, buffers, w_rowsum, y, None, algo)
     check(lib().zt_dynamic_qlinear_static(C.byref(a), _stream_ptr()))
+    return y
+
+
+def moe_woq(x, topk_weights, topk_ids, w13, s13, w2, s2):
+    """x [T,H] bf16; w13 [E, 2I, H/8] int32; s13 [E, H/gs, 2I]; w2 [E, H, I/8]; s2 [E, I/gs, H]."""
+    import torch
+    t, h = x.shape
+    e, two_i, _ = w13.shape
+    i = two_i // 2
+    k = topk_ids.shape[1]
+    y = torch.empty(t, h, dtype=x.dtype, device=x.device)
+    nbytes = lib().zt_moe_woq_workspace_bytes(t, h, i, e, k)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    a = MoeWoqArgs()
+    a.x, a.T, a.H, a.I, a.num_experts, a.top_k = x.data_ptr(), t, h, i, e, k
+    a.topk_ids, a.topk_weights = topk_ids.data_ptr(), topk_weights.data_ptr()
+    a.w13, a.s13, a.w2, a.s2 = w13.data_ptr(), s13.data_ptr(), w2.data_ptr(), s2.data_ptr()
+    a.scale_dtype, a.group_size = _dtype_code(s13), h // s13.shape[1]
+    a.y, a.workspace, a.workspace_bytes = y.data_ptr(), ws.data_ptr(), nbytes
+    check(lib().zt_moe_woq(C.byref(a), _stream_ptr()))
     return y
