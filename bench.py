@@ -388,6 +388,15 @@ def run_profile_case(name):
         for i in range(6):
             wq, sc = copies[i % 2]
             _capi.woq_linear(x, wq, sc, None, bias)
+    elif name == "woq_prefill":
+        m, k, n, gs = 2048, 4096, 14336, 128
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        bias = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        copies = [(torch.randint(-2**31, 2**31 - 1, (n, k // 8), dtype=torch.int32, device=dev),
+                   torch.rand(k // gs, n, device=dev) * 0.01) for _ in range(2)]
+        for i in range(4):
+            wq, sc = copies[i % 2]
+            _capi.woq_linear(x, wq, sc, None, bias)
     else:
         raise SystemExit(f"unknown profile case {name}")
     torch.cuda.synchronize()
@@ -463,7 +472,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile", default=None, help="run a few plain launches of one kernel (for ncu): "
-                                                    "int8_gemm | woq_decode | dynquant")
+                                                    "int8_gemm | woq_decode | woq_prefill | dynquant")
     args = ap.parse_args()
     if args.profile:
         run_profile_case(args.profile)

@@ -296,29 +296,42 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
     const int d = threadIdx.x - 64;   // 0..255
     const int row = d >> 1;           // weight row (output column) within the tile
     const int half = d & 1;           // which 32 k of the 64-wide k-block
-    // scales (and zero points) come from global memory, fetched kPrefetch k-blocks ahead
-    auto fetch = [&](int tile, int kb, DqRegs &r) {
-      const TileInfo t = decode_tile(p, tile, n_mt, BT);
-      const int n = min(t.n0 + row, p.N - 1);
-      const int k = kb * kBK + 32 * half;
-      const int64_t gi = (int64_t)t.expert * p.s_estride + (int64_t)(k / p.gs) * p.N + n;
-      r.s = load_as_float(p.scales, gi, p.scale_dtype);
-      r.z = ASYM ? load_as_float(p.zeros, gi, p.scale_dtype) : 0.f;
-    };
+    // scales (and zero points) come from global memory, fetched kPrefetch k-blocks ahead.  The fetch
+    // cursor keeps its tile's column and expert offset; they change only when it moves to a new tile.
+    const int gs_shift = (p.gs & (p.gs - 1)) == 0 ? __ffs(p.gs) - 1 : -1;
     constexpr int kPrefetch = 4;
     DqRegs ring[kPrefetch];
     int ftile = blockIdx.x, fkb = 0;  // next (tile, k-block) to fetch
+    int64_t fbase = 0;                // expert offset + column of the fetch cursor's tile
+    auto set_fetch_tile = [&]() {
+      if (ftile < total_tiles) {
+        const TileInfo t = decode_tile(p, ftile, n_mt, BT);
+        fbase = (int64_t)t.expert * p.s_estride + min(t.n0 + row, p.N - 1);
+      }
+    };
+    set_fetch_tile();
     auto fetch_next = [&](DqRegs &slot) {
       if (ftile < total_tiles) {
-        fetch(ftile, fkb, slot);
+        const int k = fkb * kBK + 32 * half;
+        const int g = gs_shift >= 0 ? (k >> gs_shift) : (k / p.gs);
+        const int64_t gi = fbase + (int64_t)g * p.N;
+        slot.s = load_as_float(p.scales, gi, p.scale_dtype);
+        slot.z = ASYM ? load_as_float(p.zeros, gi, p.scale_dtype) : 0.f;
         if (++fkb == num_kb) {
           fkb = 0;
           ftile += gridDim.x;
+          set_fetch_tile();
         }
       }
     };
 #pragma unroll
     for (int i = 0; i < kPrefetch; ++i) fetch_next(ring[i]);
+    // loop-invariant shared-memory offsets of this thread: where it reads its 16 packed bytes of
+    // k-block j of a chunk, and where it writes its four 16-byte bf16 chunks of a stage row
+    uint32_t st_off[4];
+    const uint32_t row_off = row * 128, row_x = row & 7;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) st_off[i] = row * 128 + (((4 * half + i) ^ (row & 7)) << 4);
     uint32_t it = 0;    // k-blocks converted so far (bf16 stage ring position)
     uint32_t pit = 0;   // packed chunks consumed so far
     int kb = 0;         // k-block within the current tile
@@ -346,9 +359,9 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
           }
           if (ok) {
             // this thread's 32 nibbles of the k-block: 16-byte chunk (2j + half) of the swizzled 128-byte row
-            const uint4 wv = *reinterpret_cast<const uint4 *>(packed + ps * kChunkBytes + row * 128 +
-                                                              (((2 * j + half) ^ (row & 7)) << 4));
-            unsigned char *wrow = smem + s * L::kStageBytes + row * 128;
+            const uint4 wv = *reinterpret_cast<const uint4 *>(packed + ps * kChunkBytes + row_off +
+                                                              ((((uint32_t)(2 * j + half)) ^ row_x) << 4));
+            unsigned char *wstage = smem + s * L::kStageBytes;
             const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
             uint32_t s_hi = 0, s_lo = 0;
             if (!ASYM) split_bf16x2(cur.s, s_hi, s_lo);
@@ -384,8 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
                 o.z = prmt(r[0], r[1], 0x7632);  // (k4, k5)
                 o.w = prmt(r[2], r[3], 0x7632);  // (k6, k7)
               }
-              const int chunk = 4 * half + i;  // 16-byte chunk of the 128-byte row
-              *reinterpret_cast<uint4 *>(wrow + ((chunk ^ (row & 7)) << 4)) = o;
+              *reinterpret_cast<uint4 *>(wstage + st_off[i]) = o;
             }
             tc::fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
           }

@@ -47,4 +47,12 @@ def is_supported_device() -> bool:
     return torch.cuda.is_available() and bool(_capi.lib().zt_device_supported())
 
 
+def register_backend() -> None:
+    """Register ``torch.compile(..., backend="zentorch_b200")``: Inductor with the WOQ replacement and
+    fusion passes as its joint-graph post pass.  Kept out of ``import`` because it pulls in Dynamo."""
+    from . import _compile
+
+    _compile.register_backend()
+
+
 load()
