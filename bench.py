@@ -222,10 +222,11 @@ def run_ours(args):
         ms_quant = time_region(torch, graph_quant.replay, args.steps) / (args.steps * CALLS_PER_STEP)
 
         # ---- weight-only int4 decode GEMV (config 1, M = 1), HBM-bound ---------------------------------
-        woq = bench_woq_decode(torch, _capi, lib, dev, stream, sptr, args.steps, pk) if rank == 0 else None
+        woq = bench_woq(torch, _capi, lib, dev, stream, sptr, args.steps, pk) if rank == 0 else {}
 
     # ---- end to end through torch.ops with host buffers ---------------------------------------------------
     e2e = bench_e2e(torch, dev, sets, args.steps, world)
+    tp_mlp = bench_tp_mlp(torch, dist, dev, args.steps, world)
     clocks = sampler.stop() if rank == 0 else None
     torch.cuda.synchronize()
     status = _capi.poll_device_status()
@@ -267,7 +268,8 @@ def run_ours(args):
                              "twice the kind::f16 rate",
                 "traffic": None,
             },
-            "woq_decode": woq,
+            "woq_decode": woq.get("woq_decode"), "woq_decode_large_layer": woq.get("woq_decode_large_layer"),
+            "woq_prefill": woq.get("woq_prefill"), "tp_mlp": tp_mlp,
             "cpu_baseline": cpu,
             "e2e": {"value": round(e2e_value, 3), "unit": "TOP/s", "h2d_bytes_per_step": e2e["h2d"],
                     "d2h_bytes_per_step": e2e["d2h"], "calls_per_step": 1,
@@ -281,22 +283,34 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def bench_woq_decode(torch, _capi, lib, dev, stream, sptr, steps, pk):
-    """Config 1 at M = 1: y = x[1,4096] . dq(W)[4096,4096] + bias, int4 weights with fp32 scales per
-    group of 128.  Rotates over enough weight copies to exceed L2; reports algorithmic GB/s."""
+def device_woq_weights(torch, _capi, dev, k, n, seed, gs=128):
+    """Synthetic int4 weights made on the device: uniform nibbles in [-8, 7], fp32 group scales around
+    0.01 (the magnitude max|w|/7 of N(0, 0.02) weights gives), packed by the repack kernel."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    q = torch.randint(-8, 8, (n, k), generator=g, device=dev, dtype=torch.int8)
+    scales = (torch.rand(k // gs, n, generator=g, device=dev) * 0.006 + 0.007).contiguous()
+    packed = _capi.woq_repack_weight(q)
+    del q
+    return packed, scales
+
+
+def bench_woq_case(torch, _capi, lib, dev, stream, sptr, steps, pk, m, k, n, label):
+    """One weight-only int4 linear y = x[m,k] . dq(W)[k,n] + bias (fp32 scales per group of 128, bf16
+    bias), rotating over enough weight copies to exceed L2.  Small m is HBM-bound (reported as algorithmic
+    GB/s of the HBM roofline), large m tensor-bound (TFLOP/s of the bf16 roofline)."""
     import ctypes as C
-    from _util import make_woq_case
-    m, k, n, gs = 1, 4096, 4096, 128
-    x, q, s, _, b = make_woq_case(m, k, n, gs, seed=0)
-    alg_bytes = n * k // 2 + (k // gs) * n * 4 + m * k * 2 + m * n * 2 + n * 2
-    copies = -(-int(2.0 * L2_BYTES) // (n * k // 2 + (k // gs) * n * 4))
-    packed0 = _capi.woq_repack_weight(q.to(dev))
-    xs, bs = x.to(dev), b.to(dev)
+    gs = 128
+    w_bytes = n * k // 2 + (k // gs) * n * 4
+    alg_bytes = w_bytes + m * k * 2 + m * n * 2 + n * 2
+    copies = max(2, -(-int(2.0 * L2_BYTES) // w_bytes))
+    packed0, scales0 = device_woq_weights(torch, _capi, dev, k, n, seed=0)
+    xs = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    bs = (torch.randn(n, device=dev) * 0.01).to(torch.bfloat16)
     ws = _capi.woq_workspace(lib.zt_woq_linear_workspace_bytes(m, n, k), dev)
     arglist, keep = [], []
     for i in range(copies):
         wq = packed0.clone()
-        sc = s.to(dev).clone()
+        sc = scales0.clone()
         y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
         a = _capi.WoqLinearArgs()
         a.x, a.M, a.K, a.N = xs.data_ptr(), m, k, n
@@ -320,12 +334,73 @@ def bench_woq_decode(torch, _capi, lib, dev, stream, sptr, steps, pk):
         g.replay()
     reps = max(steps, 10)
     ms = time_region(torch, g.replay, reps) / (reps * copies)
-    gbs = alg_bytes / (ms * 1e-3) / 1e9
-    return {"workload": "BASELINE config 1: WOQ int4 (group 128, fp32 scales) M=1 K=4096 N=4096, bf16 bias",
-            "kernel": "woq_stream_kernel", "bound": "hbm", "us_per_call": round(ms * 1e3, 3),
-            "algorithmic_bytes": alg_bytes, "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-            "frac": round(gbs / pk["hbm_gbs"], 4), "peak_note": f"STREAM-style copy, {pk['source']}",
-            "l2": f"rotating over {copies} weight copies", "launch": "CUDA graph, back-to-back"}
+    out = {"workload": f"{label}: WOQ int4 (group 128, fp32 scales) M={m} K={k} N={n}, bf16 bias",
+           "us_per_call": round(ms * 1e3, 3), "l2": f"rotating over {copies} weight copies",
+           "launch": "CUDA graph, back-to-back"}
+    if m <= 16:
+        gbs = alg_bytes / (ms * 1e-3) / 1e9
+        # the dispatcher's rule: TMA-staged stream-K kernel from 24 MB of packed weights, register ring below
+        kernel = "woq_streamk_kernel" if n * k // 2 >= (24 << 20) else "woq_stream_kernel"
+        out.update({"kernel": kernel, "bound": "hbm", "algorithmic_bytes": alg_bytes, "achieved": round(gbs, 1),
+                    "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / pk["hbm_gbs"], 4),
+                    "peak_note": f"STREAM-style copy, {pk['source']}"})
+    else:
+        tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        out.update({"kernel": "woq_tcgen05_kernel", "bound": "tensor", "achieved": round(tf, 1),
+                    "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": round(tf / pk["bf16_tflops"], 4),
+                    "peak_note": f"cuBLAS bf16 burst, {pk['source']}"})
+    del keep
+    return out
+
+
+def bench_woq(torch, _capi, lib, dev, stream, sptr, steps, pk):
+    cases = {"woq_decode": (1, 4096, 4096, "BASELINE config 1 at M=1"),
+             "woq_decode_large_layer": (1, 8192, 28672, "BASELINE config 3 layer (70B-class up-projection) at M=1"),
+             "woq_prefill": (2048, 4096, 4096, "BASELINE config 1 at M=2048")}
+    return {name: bench_woq_case(torch, _capi, lib, dev, stream, sptr, steps, pk, m, k, n, label)
+            for name, (m, k, n, label) in cases.items()}
+
+
+def bench_tp_mlp(torch, dist, dev, steps, world):
+    """Tensor-parallel WOQ MLP at decode size (M=16): up-projection column-parallel [8192 -> 28672/world],
+    SiLU-gated product, down-projection row-parallel [28672/world -> 8192] followed by the NCCL all-reduce.
+    Device-timed per call, max over ranks.  Shards are generated directly (weights are synthetic)."""
+    from zentorch_b200 import _capi, tp
+    m, hidden, inter = 16, 8192, 28672
+    shard = inter // world
+    ops = torch.ops.zentorch
+
+    def shard_params(k, n, seed):
+        packed, scales = device_woq_weights(torch, _capi, dev, k, n, seed)
+        return packed.t(), scales, None, None
+
+    rank = dist.get_rank() if world > 1 else 0
+    gate = tp.ParallelLinear("woq", "column", shard_params(hidden, shard, 10 + rank))
+    up = tp.ParallelLinear("woq", "column", shard_params(hidden, shard, 20 + rank))
+    down = tp.ParallelLinear("woq", "row", shard_params(shard, hidden, 30 + rank))
+    mlp = tp.ParallelMLP(gate, up, down)
+    x = torch.randn(m, hidden, device=dev).to(torch.bfloat16)
+    for _ in range(3):
+        mlp(x)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    reps = max(steps, 10)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        mlp(x)
+    end.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([start.elapsed_time(end) / reps], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    w_bytes = 3 * (hidden * shard // 2 + (hidden // 128) * shard * 4)
+    us = float(t.item()) * 1e3
+    return {"workload": f"WOQ int4 SiLU-gated MLP {hidden}->{inter}->{hidden}, M={m}, tensor-parallel over {world} GPU(s)",
+            "us_per_call": round(us, 2), "weight_bytes_per_gpu": w_bytes,
+            "weight_stream_gbs_per_gpu": round(w_bytes / (us * 1e-6) / 1e9, 1),
+            "collective": "one NCCL all-reduce of [16, 8192] bf16 per call" if world > 1 else "none"}
 
 
 def bench_e2e(torch, dev, sets, steps, world):
