@@ -135,13 +135,14 @@ def test_stream_kernel_shapes(capi, cfg, m, monkeypatch):
         assert_close_bf16(y, exact, rtol=8e-3, atol=4e-3, what=f"cfg {cfg} M={m} K={k} N={n} vs exact")
 
 
-@pytest.mark.parametrize("m", [1, 2, 5, 8, 9, 16])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 9, 12, 16])
 def test_streamk_kernel(capi, m):
     """The work-balanced decode kernel: column tiles shared between CTAs (small N, long K), ragged N,
     both quantisation forms and scale dtypes; run twice to check that the arrival counters reset."""
     cases = ((4096, 64, 128, False, torch.float32), (28672, 192, 128, False, torch.float32),
              (8192, 1000, 256, True, torch.float32), (1024, 4104, 128, True, torch.bfloat16),
-             (4096, 4096, 4096, False, torch.bfloat16), (14336, 136, 128, False, torch.float32))
+             (4096, 4096, 4096, False, torch.bfloat16), (14336, 136, 128, False, torch.float32),
+             (7168, 4096, 256, True, torch.float32))   # many chunks per CTA: the stage ring wraps several times
     for (k, n, gs, asym, sdt) in cases:
         x, q, s, z, b = make_woq_case(m, k, n, gs, seed=m * 7 + n, asym=asym, scale_dtype=sdt)
         ref = O.woq_linear(x, O.woq_repack_weight(q).t(), s, z, b)

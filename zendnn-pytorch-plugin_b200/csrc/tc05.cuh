@@ -70,6 +70,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   return false;
 }
 
+// Same, for waits that are expected to last: each poll may suspend the warp for up to `hint_ns`
+// (it wakes when the phase completes), so a waiting warp takes almost no issue slots.
+__device__ __forceinline__ bool mbar_wait_suspend(uint64_t *bar, uint32_t parity, uint32_t hint_ns = 2000) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < (kSpinLimit >> 3); ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity), "r"(hint_ns)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
 // ---- TMA ----------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

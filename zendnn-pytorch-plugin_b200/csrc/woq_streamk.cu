@@ -13,18 +13,30 @@
 // described to TMA as a 3-D tensor (16 words of one cell's row, K/128 cells along K, N rows), so one
 // instruction brings 64 rows x 8 cells = 32 KB laid out [row][cell][64 B]; the activations likewise
 // ([row][cell][256 B]) and the scales / zero points of the chunk's groups ([group][64 columns]).  A
-// chunk always loads the full 8-cell box (cells past the CTA's range are simply not used; rows and
-// cells beyond N and K read as zero).  Nothing is
-// staged through registers, so the bytes in flight per SM are bounded by shared memory (> 100 KB), not
-// by occupancy.  No multicast is used.
+// chunk always loads the full box (cells past the CTA's range are simply not used; rows and cells
+// beyond N and K read as zero).  Nothing is staged through registers, so the bytes in flight per SM
+// are bounded by shared memory (> 100 KB), not by occupancy.  No multicast is used.
 //
-// Arithmetic (16 compute warps; warp w takes cell w/2 of the chunk and 32 of its 64 columns).  Nibbles
-// become bf16 pairs with one lop3 each ((w >> 4p) & 0x000f000f picks nibbles p and p+4; or-ing 0x4300
-// into both halves gives 128 + u, signed nibbles are xor-ed with 8 in the same lop3 so that u = q + 8 in
-// both formats) and feed mma.sync.m16n8k16 as the A operand; the activations are the B operand,
-// permuted to the same (k, k+4) pairing with byte-permutes; an all-ones A operand yields sum_k x per
-// cell, with which the bias of 136 is removed on the cell's partial sum and the zero point applied:
-// acc += s * (part - 136 * sum) + z * sum, in fp32.  Dequantised weights are never rounded to bf16.
+// Arithmetic: integer tensor-core MMAs on exact operands.  A packed word holds eight nibbles;
+// (w & 0x0f0f0f0f) is four of them as bytes and ((w >> 4) & 0x0f0f0f0f) the other four (signed nibbles
+// are xor-ed with 8 in the same lop3, so u = q + 8 in both formats): three ALU operations per eight
+// weights, and the bytes are the A operand of mma.sync.m16n8k32 (u8 x s8 -> s32) as they stand.  The
+// activations are made integer once per staged cell by converter warps: the 128 bf16 values of one
+// token's cell are scaled by the power of two that puts the largest below 2^21 (tokens <= 2) or 2^14
+// (more tokens), rounded to an integer X and split into signed base-256 digits X = d2 2^16 + d1 2^8 + d0.
+// bf16 values carry 8 significant bits, so every value within 2^-13 (2^-6) of the cell's largest is
+// represented exactly and the rest to 2^-22 (2^-15) of the largest.  Each (token, digit) is one column
+// of the B operand (n = 8 per MMA), stored in the fragment order the MMA wants, next to the column's
+// power of two and its digit sum.  The accumulators start at -8 * (digit sum), which removes the +8 of u
+// exactly; a cell's integer result is converted once and scaled in fp32:
+// acc[col] += s * 2^e(col) * float(part[col]) (+ z * sum_k x), and a token's columns are added at the
+// end.  Dequantised weights are never rounded and products are exact integers.
+//
+// Launch overlap.  The kernel is launched with programmatic stream serialisation: it lets its successor
+// start as soon as every CTA is running, and itself stages the first weight chunks before waiting for
+// its predecessor (only the activations, the scratch and the output depend on earlier work; weights,
+// scales and zero points must not be written by the kernel launched directly before this one on the
+// same stream unless that kernel completes normally, which every kernel except this one does).
 #include <cstdlib>
 #include <mutex>
 #include <type_traits>
@@ -39,13 +51,23 @@ namespace {
 
 constexpr int kTileN = 64;        // output columns per cell
 constexpr int kStepK = 128;       // k per cell
-constexpr int kChunkSteps = 8;    // cells per stage
 constexpr int kComputeWarps = 16;
-constexpr int kThreads = 32 * (kComputeWarps + 1);
-constexpr int kWRowBytes = kChunkSteps * 64;      // one weight row of a stage: [8 cells][64 B]
-constexpr int kWBytes = kTileN * kWRowBytes;
-constexpr int kXRowBytes = kChunkSteps * 256;     // one activation row of a stage: [8 cells][256 B]
+// Converter warps: seven when the B operand is one 8-column block (the compute warps then fit in 80
+// registers, 24 warps in all), three otherwise (96 registers, 20 warps).
+__host__ __device__ constexpr int conv_warps(int nb) { return nb == 1 ? 7 : 3; }
+__host__ __device__ constexpr int sk_threads(int nb) { return 32 * (kComputeWarps + 1 + conv_warps(nb)); }
 constexpr int kMaxStages = 6;
+constexpr int kRedStride = 33;
+
+// NB = 8-column blocks of the B operand: columns = tokens x digits (3 digits up to 2 tokens, else 2).
+__host__ __device__ constexpr int digits_for(int m) { return m <= 2 ? 3 : 2; }
+__host__ __device__ constexpr int col_blocks(int m) { return (m * digits_for(m) + 7) / 8; }
+// Cells per stage and 16-row blocks per compute warp: one cell x 32 columns per warp with 8-cell chunks,
+// one cell x 16 columns with 4-cell chunks (more than 8 tokens: twice the activation bytes per cell).
+__host__ __device__ constexpr int chunk_steps(int nb) { return nb <= 2 ? 8 : 4; }
+__host__ __device__ constexpr int row_blocks(int nb) { return nb <= 2 ? 2 : 1; }
+// Rows of the cross-warp reduction buffer: columns as they are (3 digits), else one row per token.
+__host__ __device__ constexpr int red_rows(int nb) { return nb <= 2 ? 8 : 4 * nb; }
 
 struct SKParams {
   const __nv_bfloat16 *x;
@@ -59,6 +81,7 @@ struct SKParams {
   int *status;
   int M, N, K;
   int gs, spg;  // group size in k and in cells
+  uint32_t spg_mul;  // 0 when spg == 1, else floor(2^32 / spg) + 1: n / spg == umulhi(n, spg_mul) for n * spg < 2^32
   int ksteps, ntiles;
   long long total_cells;
   int scale_dtype, bias_dtype;
@@ -66,66 +89,71 @@ struct SKParams {
   PostOpsDev post;
 };
 
+// Four nibbles of w as bytes: u = q + 8 for signed nibbles (and-then-xor), u itself for unsigned ones.
+template <bool SIGNED>
+__device__ __forceinline__ uint32_t nib_bytes(uint32_t w) {
+  uint32_t r;
+  if (SIGNED) {
+    asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(r) : "r"(w), "n"(0x0f0f0f0f), "n"(0x08080808));
+  } else {
+    r = w & 0x0f0f0f0fu;
+  }
+  return r;
+}
+__device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t r;
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
   return r;
 }
-template <bool SIGNED>
-__device__ __forceinline__ uint32_t nib_pair_to_bf16x2(uint32_t w) {
-  uint32_t r;
-  if (SIGNED) {
-    asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(r) : "r"(w), "n"(0x000f000f), "n"(0x43084308));
-  } else {
-    asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(w), "n"(0x000f000f), "n"(0x43004300));
-  }
+__device__ __forceinline__ int byte_sum(uint32_t v, int acc) {  // acc + the four signed bytes of v
+  int r;
+  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(v), "r"(0x01010101), "r"(acc));
   return r;
-}
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void compute_barrier() {
   asm volatile("bar.sync 1, %0;" ::"n"(kComputeWarps * 32) : "memory");
 }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // The CTA whose cell range contains cell c, for ranges [b*total/G, (b+1)*total/G).
 __device__ __forceinline__ int cta_of_cell(long long c, long long total, int G) {
   return (int)(((c + 1) * G + total - 1) / total - 1);
 }
 
-// One chunk = up to kChunkSteps consecutive cells of one column tile.
+// One chunk = up to CS consecutive cells of one column tile.
 struct Chunk {
   int tile, step0, nsteps;
   bool last_of_segment;
 };
 
 // Walks the chunks of this CTA's cell range in order.  The only division is in the constructor; the
-// per-chunk step is additions and compares (the loop runs once per chunk in every warp).
+// per-chunk step is a handful of 32-bit additions and compares (it runs once per chunk in every warp).
+template <int CS>
 struct ChunkIter {
-  int tile, step, ksteps;
-  long long remaining;
-  __device__ ChunkIter(long long c0, long long c1, int ks) : ksteps(ks), remaining(c1 - c0) {
+  int tile, step, ksteps, remaining;
+  __device__ ChunkIter(long long c0, long long c1, int ks) : ksteps(ks), remaining((int)(c1 - c0)) {
     tile = (int)(c0 / ks);
     step = (int)(c0 - (long long)tile * ks);
   }
   __device__ bool next(Chunk &ch) {
     if (remaining <= 0) return false;
-    int n = ksteps - step;                      // cells left in this column tile
-    const bool tile_ends = (long long)n <= remaining && n <= kChunkSteps;
-    if ((long long)n > remaining) n = (int)remaining;
-    const bool range_ends = (long long)n == remaining && n <= kChunkSteps;
-    if (n > kChunkSteps) n = kChunkSteps;
+    int n = min(min(ksteps - step, remaining), CS);
     ch.tile = tile;
     ch.step0 = step;
     ch.nsteps = n;
-    ch.last_of_segment = tile_ends || range_ends;
     remaining -= n;
     step += n;
-    if (step == ksteps) {
+    const bool tile_ends = step == ksteps;
+    ch.last_of_segment = tile_ends || remaining == 0;
+    if (tile_ends) {
       step = 0;
       ++tile;
     }
@@ -133,25 +161,46 @@ struct ChunkIter {
   }
 };
 
-template <int MT, bool ASYM, bool SF32>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int NB, bool ASYM, bool SF32>
+__global__ void __launch_bounds__(sk_threads(NB), 1)
     woq_streamk_kernel(const __grid_constant__ CUtensorMap map_w8, const __grid_constant__ CUtensorMap map_x8,
                        const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_z,
                        const SKParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int kCols = MT * 8;
+  constexpr int NC = 8 * NB;                  // B-operand columns held (tokens x digits, padded)
+  constexpr int CS = chunk_steps(NB);         // cells per chunk
+  constexpr int R = row_blocks(NB);           // 16-row blocks per compute warp
+  constexpr int kRows = red_rows(NB);
+  constexpr int kWarpsPerCell = kComputeWarps / CS;
+  constexpr int kConvWarps = conv_warps(NB);
+  constexpr int kThreads = sk_threads(NB);
+  constexpr int kWRowBytes = CS * 64;         // one weight row of a stage: [CS cells][64 B]
+  constexpr int kWBytes = kTileN * kWRowBytes;
+  constexpr int kXRowBytes = CS * 256;        // one activation row of a stage: [CS cells][256 B]
   constexpr int kScaleBytes = SF32 ? 4 : 2;
-  constexpr int kSBytes = kChunkSteps * kTileN * kScaleBytes;  // scales of the chunk: [8 groups][64]
+  constexpr int kSBytes = CS * kTileN * kScaleBytes;  // scales of the chunk: [CS groups][64]
   constexpr int kSOff = kWBytes;
-  constexpr int kZOff = kSOff + 2048;                          // zero points (same shape)
-  constexpr int kXOff = kZOff + (ASYM ? 2048 : 0);             // activations: [mrows][cell][256 B]
-  constexpr int kRedStride = 33;
+  constexpr int kZOff = kSOff + CS * 256;                      // zero points (same shape)
+  constexpr int kEOff = kZOff + (ASYM ? CS * 256 : 0);         // per (cell, column): 2^e, -8 * digit sum, sum of x
+  constexpr int kEBytes = CS * NC * 4;
+  constexpr int kXOff = kEOff + (ASYM ? 3 : 2) * kEBytes;      // staged activations: [M][cell][256 B] bf16
+  using Iter = ChunkIter<CS>;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = gridDim.x;
-  const int mrows = min(p.M, kCols);
-  float *red = reinterpret_cast<float *>(smem + (size_t)p.stages * p.stage_bytes);  // [16][kCols][33]
-  uint64_t *full_bar = reinterpret_cast<uint64_t *>(red + kComputeWarps * kCols * kRedStride);
+  const int nd = digits_for(p.M);
+  const int ncols = p.M * nd;
+  const int kDOff = kXOff + p.M * kXRowBytes;                  // digit fragments: [cell][word pair][column][t][16 B]
+  // A chunk's CS * M (token, cell) conversions take four lanes each; conv_group warps share one chunk and
+  // the groups take chunks in turn, so that a small chunk's conversion latency is spread over several chunks.
+  const int conv_group = min(kConvWarps, (CS * p.M + 7) / 8);
+  // A group must see every phase of the barriers it waits on, so it owns fixed stages: the number of
+  // groups divides the number of stages.
+  int conv_ngroups = kConvWarps / conv_group;
+  while (p.stages % conv_ngroups != 0) --conv_ngroups;
+  float *red = reinterpret_cast<float *>(smem + (size_t)p.stages * p.stage_bytes);  // [16][kRows][33]
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(red + kComputeWarps * kRows * kRedStride);
   uint64_t *empty_bar = full_bar + kMaxStages;
+  uint64_t *frag_bar = empty_bar + kMaxStages;
   __shared__ int s_ticket;
 
   const long long c_begin = (long long)blockIdx.x * p.total_cells / G;
@@ -164,19 +213,54 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int s = 0; s < p.stages; ++s) {
       tc::mbar_init(&full_bar[s], 1);
       tc::mbar_init(&empty_bar[s], kComputeWarps);
+      tc::mbar_init(&frag_bar[s], conv_group);
     }
     tc::mbar_fence_init();
   }
+  // table entries of columns that do not exist are read (and meet zero sums): keep them zero
+  {
+    constexpr int kWords = (ASYM ? 3 : 2) * CS * NC;
+    for (int i = tid; i < p.stages * kWords; i += kThreads) {
+      const int s = i / kWords, r = i - s * kWords;
+      reinterpret_cast<float *>(smem + (size_t)s * p.stage_bytes + kEOff)[r] = 0.f;
+    }
+  }
   __syncthreads();
+  grid_launch_dependents();
 
   if (warp == kComputeWarps) {
     // ---------------- producer warp ----------------
-    ChunkIter iter(c_begin, c_end, p.ksteps);
+    Iter iter(c_begin, c_end, p.ksteps);
     Chunk ch;
-    uint32_t s = 0, ph = 0;  // ring position and its phase bit
+    const uint32_t tx_bytes = (uint32_t)kWBytes + (uint32_t)p.M * kXRowBytes + (uint32_t)kSBytes * (ASYM ? 2u : 1u);
+    // Weights, scales and zero points of the first chunks do not depend on the preceding kernel: stage
+    // them, then wait for it, then bring those chunks' activations.
+    int pre = 0;
+    {
+      Iter head = iter;
+      while (pre < p.stages && iter.next(ch)) {
+        if (lane == 0) {
+          unsigned char *stage = smem + (size_t)pre * p.stage_bytes;
+          const int n0 = ch.tile * kTileN;
+          const int g0 = p.spg == 1 ? ch.step0 : ch.step0 / p.spg;
+          tc::mbar_expect_tx(&full_bar[pre], tx_bytes);
+          tc::tma_load_3d(stage, &map_w8, &full_bar[pre], 0, ch.step0, n0);
+          tc::tma_load_2d(stage + kSOff, &map_s, &full_bar[pre], n0, g0);
+          if (ASYM) tc::tma_load_2d(stage + kZOff, &map_z, &full_bar[pre], n0, g0);
+        }
+        ++pre;
+      }
+      grid_dependency_wait();
+      for (int i = 0; i < pre; ++i) {
+        head.next(ch);
+        if (lane == 0)
+          tc::tma_load_3d(smem + (size_t)i * p.stage_bytes + kXOff, &map_x8, &full_bar[i], 0, ch.step0, 0);
+      }
+    }
+    uint32_t s = 0, ph = 1;  // the ring has been filled once (or the range is exhausted)
     bool ok = true;
     while (ok && iter.next(ch)) {
-      if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
+      if (!tc::mbar_wait_suspend(&empty_bar[s], ph ^ 1)) {
         tc::report_timeout(p.status, kStatusProducerTimeout);
         ok = false;
         break;
@@ -185,8 +269,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int n0 = ch.tile * kTileN;
       const int g0 = p.spg == 1 ? ch.step0 : ch.step0 / p.spg;
       if (lane == 0) {
-        tc::mbar_expect_tx(&full_bar[s], (uint32_t)kWBytes + (uint32_t)mrows * kXRowBytes +
-                                             (uint32_t)kSBytes * (ASYM ? 2u : 1u));
+        tc::mbar_expect_tx(&full_bar[s], tx_bytes);
         tc::tma_load_3d(stage, &map_w8, &full_bar[s], 0, ch.step0, n0);
         tc::tma_load_3d(stage + kXOff, &map_x8, &full_bar[s], 0, ch.step0, 0);
         tc::tma_load_2d(stage + kSOff, &map_s, &full_bar[s], n0, g0);
@@ -198,40 +281,159 @@ __global__ void __launch_bounds__(kThreads, 1)
         ph ^= 1;
       }
     }
-  } else {
-    // ---------------- compute warps ----------------
-    const int g = lane >> 2, t = lane & 3;
-    const int my_step = warp >> 1;
-    const int rb = 32 * (warp & 1);  // first of this warp's 32 columns within the tile
-    float acc[2][MT][4];
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-#pragma unroll
-      for (int m = 0; m < MT; ++m)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[r][m][e] = 0.f;
-
-    ChunkIter iter(c_begin, c_end, p.ksteps);
+  } else if (warp > kComputeWarps) {
+    // ---------------- converter warps: bf16 activations -> integer digit fragments ----------------
+    // Four lanes per (token, cell); a lane converts four of the cell's sixteen 8-value pieces.
+    grid_dependency_wait();
+    const int cw = warp - kComputeWarps - 1;
+    const int my_group = cw / conv_group, my_slot = cw - my_group * conv_group;   // warps past the last group idle
+    int turn = 0;                                                                   // group whose chunk this is
+    const int q = lane >> 2, sub = lane & 3;
+    const uint32_t qmask = 0xfu << (lane & 28);
+    const int sh = nd == 3 ? 20 : 13;                       // |X| < 2^(sh + 1)
+    // 1.5 * 2^23 + 0x8080: after the add, bytes 0 and 1 of the float hold digits 0 and 1 in excess 128 and
+    // bits 16..22 hold 0x40 + digit 2
+    const float magic = 12582912.f + 32896.f;
+    Iter iter(c_begin, c_end, p.ksteps);
     Chunk ch;
     uint32_t s = 0, ph = 0;
     bool ok = true;
     while (iter.next(ch)) {
-      if (ok && !tc::mbar_wait(&full_bar[s], ph)) {
+      const bool mine = turn == my_group;
+      if (++turn == conv_ngroups) turn = 0;
+      if (mine && ok && !tc::mbar_wait_suspend(&full_bar[s], ph)) {
+        tc::report_timeout(p.status, kStatusConvertTimeout);
+        ok = false;
+      }
+      unsigned char *stage = smem + (size_t)s * p.stage_bytes;
+      if (mine && ok) {
+        for (int base = my_slot * 8; base < CS * p.M; base += 8 * conv_group) {
+          const int idx = base + q;
+          if (idx < CS * p.M) {   // uniform within a quad
+            const int m = idx / CS, cell = idx % CS;
+            const unsigned char *src = stage + kXOff + m * kXRowBytes + cell * 256;
+            uint4 v[4];
+            uint32_t amax = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int kk = (4 * i + sub + 4 * (q & 1)) & 15;   // rotated so that a quarter-warp covers all banks
+              v[i] = *reinterpret_cast<const uint4 *>(src + kk * 16);
+              const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) amax = max(amax, max(w[j] & 0x7fffu, (w[j] >> 16) & 0x7fffu));
+            }
+            amax = max(amax, __shfl_xor_sync(qmask, amax, 1));
+            amax = max(amax, __shfl_xor_sync(qmask, amax, 2));
+            const int e_raw = (int)(amax >> 7);                       // biased exponent of the largest magnitude
+            const int e = min(max(e_raw, sh + 1), 253);
+            const float scale = __uint_as_float((uint32_t)(254 + sh - e) << 23);   // 2^(127 + sh - e)
+            int dsum[3] = {0, 0, 0};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int kk = (4 * i + sub + 4 * (q & 1)) & 15;
+              const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+              uint32_t yb[8];   // float bit patterns whose low bytes are the excess-coded digits
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                yb[2 * j] = __float_as_uint(fmaf(__uint_as_float(w[j] << 16), scale, magic));
+                yb[2 * j + 1] = __float_as_uint(fmaf(__uint_as_float(w[j] & 0xffff0000u), scale, magic));
+              }
+              // even elements feed b0 (k slots of nibbles 0,2,4,6), odd elements b1 (nibbles 1,3,5,7)
+              const uint32_t pe = prmt(yb[0], yb[2], 0x5140), qe = prmt(yb[4], yb[6], 0x5140);
+              const uint32_t po = prmt(yb[1], yb[3], 0x5140), qo = prmt(yb[5], yb[7], 0x5140);
+              uint32_t b0[3], b1[3];
+              b0[0] = prmt(pe, qe, 0x5410) ^ 0x80808080u;
+              b1[0] = prmt(po, qo, 0x5410) ^ 0x80808080u;
+              b0[1] = prmt(pe, qe, 0x7632) ^ 0x80808080u;
+              b1[1] = prmt(po, qo, 0x7632) ^ 0x80808080u;
+              if (nd == 3) {
+                const uint32_t te = prmt(prmt(yb[0], yb[2], 0x0062), prmt(yb[4], yb[6], 0x0062), 0x5410) ^ 0x40404040u;
+                const uint32_t to = prmt(prmt(yb[1], yb[3], 0x0062), prmt(yb[5], yb[7], 0x0062), 0x5410) ^ 0x40404040u;
+                b0[2] = te | ((te & 0x40404040u) << 1);   // excess 64 -> two's complement
+                b1[2] = to | ((to & 0x40404040u) << 1);
+              }
+              const int t = kk >> 2, c = kk & 3;
+              unsigned char *dst = stage + kDOff + (((cell * 2 + (c >> 1)) * ncols + m * nd) * 4 + t) * 16 + (c & 1) * 8;
+#pragma unroll
+              for (int d = 0; d < 3; ++d)
+                if (d < nd) {
+                  *reinterpret_cast<uint2 *>(dst + d * 64) = make_uint2(b0[d], b1[d]);
+                  dsum[d] = byte_sum(b1[d], byte_sum(b0[d], dsum[d]));
+                }
+            }
+#pragma unroll
+            for (int d = 0; d < 3; ++d) {
+              dsum[d] += __shfl_xor_sync(qmask, dsum[d], 1);
+              dsum[d] += __shfl_xor_sync(qmask, dsum[d], 2);
+            }
+            if (sub == 0) {
+              float *ftab = reinterpret_cast<float *>(stage + kEOff) + cell * NC + m * nd;
+              int *ntab = reinterpret_cast<int *>(stage + kEOff + kEBytes) + cell * NC + m * nd;
+              const float f0 = e_raw == 255 ? __uint_as_float(0x7fc00000u)             // inf / NaN in the cell
+                                            : __uint_as_float((uint32_t)(e - sh) << 23);  // 2^(e - 127 - sh)
+#pragma unroll
+              for (int d = 0; d < 3; ++d)
+                if (d < nd) {
+                  ftab[d] = f0 * (d == 0 ? 1.f : d == 1 ? 256.f : 65536.f);
+                  ntab[d] = -8 * dsum[d];
+                }
+              if (ASYM) {
+                float *xtab = reinterpret_cast<float *>(stage + kEOff + 2 * kEBytes) + cell * NC + m * nd;
+                xtab[0] = f0 * (float)(dsum[0] + 256 * dsum[1] + 65536 * dsum[2]);   // sum_k x of the cell
+              }
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (mine && lane == 0) tc::mbar_arrive(&frag_bar[s]);
+      if (++s == (uint32_t)p.stages) {
+        s = 0;
+        ph ^= 1;
+      }
+    }
+  } else {
+    // ---------------- compute warps ----------------
+    grid_dependency_wait();
+    const int g = lane >> 2, t = lane & 3;
+    const int my_step = warp / kWarpsPerCell;
+    const int rb = 16 * R * (warp % kWarpsPerCell);  // first of this warp's 16 R columns within the tile
+    float acc[R][NB][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < NB; ++m)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[r][m][e] = 0.f;
+    // byte offsets inside a stage that do not change from chunk to chunk
+    const int w_off = (rb + g) * kWRowBytes + my_step * 64 + 16 * t;
+    const int d_off = kDOff + ((my_step * 2 * ncols + g) * 4 + t) * 16;   // + (pair * ncols + 8 m) * 64
+    const int d_pstride = ncols * 64;
+    const int e_off = kEOff + (my_step * NC + 2 * t) * 4;                  // + 8 m * 4
+
+    Iter iter(c_begin, c_end, p.ksteps);
+    Chunk ch;
+    uint32_t s = 0, ph = 0;
+    bool ok = true;
+    while (iter.next(ch)) {
+      if (ok && !(tc::mbar_wait_suspend(&full_bar[s], ph) && tc::mbar_wait_suspend(&frag_bar[s], ph))) {
         tc::report_timeout(p.status, kStatusConvertTimeout);
         ok = false;
       }
       const unsigned char *stage = smem + (size_t)s * p.stage_bytes;
       if (ok && my_step < ch.nsteps) {
         // group of this warp's cell, relative to the chunk's first group (spg = cells per group)
-        const int gl = p.spg == 1 ? my_step : (ch.step0 + my_step) / p.spg - ch.step0 / p.spg;
-        uint4 wv[2][2];
-        float sc[2][2], zp[2][2];
+        const int gl = p.spg_mul == 0 ? my_step
+                                      : (int)(__umulhi((uint32_t)(ch.step0 + my_step), p.spg_mul) -
+                                              __umulhi((uint32_t)ch.step0, p.spg_mul));
+        uint4 wv[R][2];
+        float sc[R][2], zp[R][2];
 #pragma unroll
-        for (int r = 0; r < 2; ++r)
+        for (int r = 0; r < R; ++r)
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int row = rb + 16 * r + 8 * h + g;
-            wv[r][h] = *reinterpret_cast<const uint4 *>(stage + row * kWRowBytes + my_step * 64 + 16 * t);
+            wv[r][h] = *reinterpret_cast<const uint4 *>(stage + w_off + (16 * r + 8 * h) * kWRowBytes);
             const unsigned char *sp = stage + kSOff + gl * kTileN * kScaleBytes;
             sc[r][h] = SF32 ? reinterpret_cast<const float *>(sp)[row]
                             : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(sp)[row]);
@@ -241,63 +443,60 @@ __global__ void __launch_bounds__(kThreads, 1)
                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(zq)[row]);
             }
           }
-        float part[2][MT][4], xsum[MT][4];
+        // integer accumulators start at -8 * (digit sum of the column): sum_k (q + 8) d - 8 sum_k d
+        int part[R][NB][4];
 #pragma unroll
-        for (int m = 0; m < MT; ++m)
+        for (int m = 0; m < NB; ++m) {
+          const int2 nb = *reinterpret_cast<const int2 *>(stage + e_off + kEBytes + m * 32);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            xsum[m][e] = 0.f;
-            part[0][m][e] = 0.f;
-            part[1][m][e] = 0.f;
+          for (int r = 0; r < R; ++r) {
+            part[r][m][0] = nb.x;
+            part[r][m][1] = nb.y;
+            part[r][m][2] = nb.x;
+            part[r][m][3] = nb.y;
+          }
+        }
+#pragma unroll
+        for (int pr = 0; pr < 2; ++pr) {   // pairs of packed words (c = 2 pr, 2 pr + 1)
+          uint4 xb[NB];
+#pragma unroll
+          for (int m = 0; m < NB; ++m) {
+            xb[m] = make_uint4(0u, 0u, 0u, 0u);
+            if (m * 8 + g < ncols)
+              xb[m] = *reinterpret_cast<const uint4 *>(stage + d_off + pr * d_pstride + m * 8 * 64);
           }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t bf[MT][4];
+          for (int ci = 0; ci < 2; ++ci) {
 #pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            const int col = m * 8 + g;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (col < mrows)
-              v = *reinterpret_cast<const uint4 *>(stage + kXOff + col * kXRowBytes + my_step * 256 + 64 * t + 16 * i);
-            bf[m][0] = prmt(v.x, v.z, 0x5410);  // (x0, x4)
-            bf[m][1] = prmt(v.x, v.z, 0x7632);  // (x1, x5)
-            bf[m][2] = prmt(v.y, v.w, 0x5410);  // (x2, x6)
-            bf[m][3] = prmt(v.y, v.w, 0x7632);  // (x3, x7)
-            constexpr uint32_t kOnes = 0x3f803f80u;
-            mma_bf16_16816(xsum[m], kOnes, kOnes, kOnes, kOnes, bf[m][0], bf[m][1]);
-            mma_bf16_16816(xsum[m], kOnes, kOnes, kOnes, kOnes, bf[m][2], bf[m][3]);
-          }
+            for (int r = 0; r < R; ++r) {
+              const uint32_t wa = pr == 0 ? (ci == 0 ? wv[r][0].x : wv[r][0].y) : (ci == 0 ? wv[r][0].z : wv[r][0].w);
+              const uint32_t wb = pr == 0 ? (ci == 0 ? wv[r][1].x : wv[r][1].y) : (ci == 0 ? wv[r][1].z : wv[r][1].w);
+              const uint32_t a0 = nib_bytes<!ASYM>(wa), a1 = nib_bytes<!ASYM>(wb);             // nibbles 0,2,4,6
+              const uint32_t a2 = nib_bytes<!ASYM>(wa >> 4), a3 = nib_bytes<!ASYM>(wb >> 4);   // nibbles 1,3,5,7
 #pragma unroll
-          for (int r = 0; r < 2; ++r) {
-            const uint32_t wa = (i == 0) ? wv[r][0].x : (i == 1) ? wv[r][0].y : (i == 2) ? wv[r][0].z : wv[r][0].w;
-            const uint32_t wb = (i == 0) ? wv[r][1].x : (i == 1) ? wv[r][1].y : (i == 2) ? wv[r][1].z : wv[r][1].w;
-            uint32_t ra[4], rbv[4];
-#pragma unroll
-            for (int pp = 0; pp < 4; ++pp) {
-              ra[pp] = nib_pair_to_bf16x2<!ASYM>(wa >> (4 * pp));
-              rbv[pp] = nib_pair_to_bf16x2<!ASYM>(wb >> (4 * pp));
-            }
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-              mma_bf16_16816(part[r][m], ra[0], rbv[0], ra[1], rbv[1], bf[m][0], bf[m][1]);
-              mma_bf16_16816(part[r][m], ra[2], rbv[2], ra[3], rbv[3], bf[m][2], bf[m][3]);
+              for (int m = 0; m < NB; ++m)
+                mma_u8s8_16832(part[r][m], a0, a1, a2, a3, ci == 0 ? xb[m].x : xb[m].z, ci == 0 ? xb[m].y : xb[m].w);
             }
           }
         }
 #pragma unroll
-        for (int m = 0; m < MT; ++m)
+        for (int m = 0; m < NB; ++m) {
+          const float2 f = *reinterpret_cast<const float2 *>(stage + e_off + m * 32);
+          float2 xs = make_float2(0.f, 0.f);
+          if (ASYM) xs = *reinterpret_cast<const float2 *>(stage + e_off + 2 * kEBytes + m * 32);
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const float sxv = xsum[m][e];
+            const float fv = e ? f.y : f.x, xsv = e ? xs.y : xs.x;
 #pragma unroll
-            for (int r = 0; r < 2; ++r)
+            for (int r = 0; r < R; ++r)
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
-                float v = sc[r][h] * fmaf(-136.f, sxv, part[r][m][2 * h + e]);
-                if (ASYM) v = fmaf(zp[r][h], sxv, v);
+                float v = (sc[r][h] * fv) * __int2float_rn(part[r][m][2 * h + e]);
+                if (ASYM) v = fmaf(zp[r][h], xsv, v);
                 acc[r][m][2 * h + e] += v;
               }
           }
+        }
       }
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&empty_bar[s]);
@@ -308,16 +507,23 @@ __global__ void __launch_bounds__(kThreads, 1)
 
       if (ch.last_of_segment) {
         // ---- the segment of tile ch.tile is complete: combine the warps, then finish or hand over ----
+        // With two digits a lane's column pair (2t, 2t+1) is one token: add the pair.  With three digits the
+        // columns go out as they are and are added when the rows are read back.
 #pragma unroll
-        for (int r = 0; r < 2; ++r)
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-          for (int m = 0; m < MT; ++m)
+          for (int m = 0; m < NB; ++m)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int nl = 16 * r + 8 * (e >> 1) + g;  // within this warp's 32 columns
-              const int ml = m * 8 + 2 * t + (e & 1);
-              red[(warp * kCols + ml) * kRedStride + nl] = acc[r][m][e];
-              acc[r][m][e] = 0.f;
+            for (int h = 0; h < 2; ++h) {
+              const int nl = 16 * r + 8 * h + g;  // within this warp's 16 R columns
+              if (nd == 2) {
+                red[(warp * kRows + 4 * m + t) * kRedStride + nl] = acc[r][m][2 * h] + acc[r][m][2 * h + 1];
+              } else if (m == 0) {
+                red[(warp * kRows + 2 * t) * kRedStride + nl] = acc[r][m][2 * h];
+                red[(warp * kRows + 2 * t + 1) * kRedStride + nl] = acc[r][m][2 * h + 1];
+              }
+              acc[r][m][2 * h] = 0.f;
+              acc[r][m][2 * h + 1] = 0.f;
             }
         compute_barrier();
         const int n0 = ch.tile * kTileN;
@@ -325,18 +531,20 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int b_first = cta_of_cell(t_first, p.total_cells, G);
         const int b_last = cta_of_cell(t_first + p.ksteps - 1, p.total_cells, G);
         const bool shared_tile = b_first != b_last;
-        const int nl = tid & 63;       // column within the tile
-        const int half = nl >> 5;      // which row-half's warps hold it
+        const int nl = tid & 63;        // column within the tile
+        const int sub = nl / (16 * R);  // which of a cell's warps holds this column
         const int n = n0 + nl;
-        float mine[2] = {0.f, 0.f};    // up to two output rows per thread (M <= 16, 8 rows per pass)
+        float mine[2] = {0.f, 0.f};     // up to two output rows per thread (M <= 16, 8 rows per pass)
 #pragma unroll
         for (int pass = 0; pass < 2; ++pass) {
           const int ml = (tid >> 6) + 8 * pass;
           if (ml < p.M) {
             float v = 0.f;
+            const int row0 = nd == 2 ? ml : 3 * ml, nrow = nd == 2 ? 1 : 3;
+            for (int rr = 0; rr < nrow; ++rr)
 #pragma unroll
-            for (int w8 = 0; w8 < kComputeWarps / 2; ++w8)
-              v += red[((2 * w8 + half) * kCols + ml) * kRedStride + (nl & 31)];
+              for (int cell = 0; cell < CS; ++cell)
+                v += red[((cell * kWarpsPerCell + sub) * kRows + row0 + rr) * kRedStride + (nl % (16 * R))];
             mine[pass] = v;
           }
         }
@@ -391,13 +599,15 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
-size_t streamk_stage_bytes(int mt, int M, bool asym) {
-  const int mrows = M < mt * 8 ? M : mt * 8;
-  size_t b = (size_t)kWBytes + 2048 * (asym ? 2 : 1) + (size_t)mrows * kXRowBytes;
+size_t streamk_stage_bytes(int M, bool asym) {
+  const size_t nb = col_blocks(M), cs = chunk_steps((int)nb), ncols = (size_t)M * digits_for(M);
+  // weights, scales (+ zero points), per-column tables, staged bf16 activations, digit fragments
+  size_t b = kTileN * cs * 64 + cs * 256 * (asym ? 2 : 1) + (asym ? 3 : 2) * cs * nb * 8 * 4 + (size_t)M * cs * 256 +
+             cs * 128 * ncols;
   return (b + 127) / 128 * 128;
 }
-size_t streamk_tail_bytes(int mt) {
-  return (size_t)kComputeWarps * mt * 8 * 33 * sizeof(float) + 2 * kMaxStages * sizeof(uint64_t) + 64;
+size_t streamk_tail_bytes(int nb) {
+  return (size_t)kComputeWarps * red_rows(nb) * kRedStride * sizeof(float) + 3 * kMaxStages * sizeof(uint64_t) + 64;
 }
 
 struct Maps {
@@ -442,19 +652,19 @@ int cached_map(CUtensorMap *out, const void *ptr, CUtensorMapDataType dt, int ra
   return ZT_SUCCESS;
 }
 
-int build_maps(const zt_woq_linear_args_t &a, int mrows, Maps &m) {
+int build_maps(const zt_woq_linear_args_t &a, int mrows, uint32_t cs, Maps &m) {
   const uint64_t ksteps = (uint64_t)a.K / kStepK;
   {  // packed weight: [N rows][K/128 cells][16 words]
     const uint64_t dims[3] = {16, ksteps, (uint64_t)a.N};
     const uint64_t strides[2] = {64, (uint64_t)a.K / 2};
-    const uint32_t box[3] = {16, kChunkSteps, kTileN};
+    const uint32_t box[3] = {16, cs, kTileN};
     int rc = cached_map(&m.w8, a.wq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, dims, strides, box);
     if (rc != ZT_SUCCESS) return rc;
   }
   {  // activations: [M rows][K/128 cells][128 bf16]
     const uint64_t dims[3] = {128, ksteps, (uint64_t)a.M};
     const uint64_t strides[2] = {256, (uint64_t)a.K * 2};
-    const uint32_t box[3] = {128, kChunkSteps, (uint32_t)mrows};
+    const uint32_t box[3] = {128, cs, (uint32_t)mrows};
     int rc = cached_map(&m.x8, a.x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box);
     if (rc != ZT_SUCCESS) return rc;
   }
@@ -463,7 +673,7 @@ int build_maps(const zt_woq_linear_args_t &a, int mrows, Maps &m) {
     const CUtensorMapDataType dt = f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     const uint64_t dims[2] = {(uint64_t)a.N, (uint64_t)a.n_groups};
     const uint64_t strides[1] = {(uint64_t)a.N * (f32 ? 4 : 2)};
-    const uint32_t box[2] = {kTileN, kChunkSteps};
+    const uint32_t box[2] = {kTileN, cs};
     int rc = cached_map(&m.s, a.scales, dt, 2, dims, strides, box);
     if (rc != ZT_SUCCESS) return rc;
     if (a.zeros) {
@@ -476,24 +686,43 @@ int build_maps(const zt_woq_linear_args_t &a, int mrows, Maps &m) {
   return ZT_SUCCESS;
 }
 
-template <int MT, bool ASYM, bool SF32>
+// ZENTORCH_B200_WOQ_PDL=0 launches the kernel with ordinary stream ordering.
+bool overlap_launches() {
+  static const bool on = [] {
+    const char *e = std::getenv("ZENTORCH_B200_WOQ_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+template <int NB, bool ASYM, bool SF32>
 int launch(const Maps &m, const SKParams &p, int grid, size_t smem_bytes, cudaStream_t st) {
-  auto kern = woq_streamk_kernel<MT, ASYM, SF32>;
+  auto kern = woq_streamk_kernel<NB, ASYM, SF32>;
   static bool configured = false;
   if (!configured) {
-    ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+    ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     configured = true;
   }
-  kern<<<grid, kThreads, smem_bytes, st>>>(m.w8, m.x8, m.s, m.z, p);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)sk_threads(NB));
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_launches() ? 1 : 0;
+  ZT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, m.w8, m.x8, m.s, m.z, p));
   return launch_status("woq_streamk_kernel");
 }
 
-template <int MT>
+template <int NB>
 int launch_q(const Maps &m, const SKParams &p, int grid, size_t smem_bytes, cudaStream_t st) {
   const bool asym = p.zeros != nullptr, sf32 = p.scale_dtype == ZT_F32;
   if (asym)
-    return sf32 ? launch<MT, true, true>(m, p, grid, smem_bytes, st) : launch<MT, true, false>(m, p, grid, smem_bytes, st);
-  return sf32 ? launch<MT, false, true>(m, p, grid, smem_bytes, st) : launch<MT, false, false>(m, p, grid, smem_bytes, st);
+    return sf32 ? launch<NB, true, true>(m, p, grid, smem_bytes, st) : launch<NB, true, false>(m, p, grid, smem_bytes, st);
+  return sf32 ? launch<NB, false, true>(m, p, grid, smem_bytes, st) : launch<NB, false, false>(m, p, grid, smem_bytes, st);
 }
 
 }  // namespace
@@ -511,7 +740,7 @@ bool woq_streamk_supported(const zt_woq_linear_args_t &a) {
                          reinterpret_cast<uintptr_t>(a.scales) | reinterpret_cast<uintptr_t>(a.zeros);
   if (ptrs & 15) return false;
   if (ceil_div<int64_t>(a.N, kTileN) * (int64_t)sizeof(int) > ZT_WOQ_COUNTER_BYTES) return false;
-  return a.K <= (1 << 30) && a.N <= (1 << 30);
+  return a.K <= (1 << 22) && a.N <= (1 << 30);  // group lookups divide by multiplication: (K/128)^2 < 2^32
 }
 
 int woq_streamk_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
@@ -532,6 +761,7 @@ int woq_streamk_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   p.bias_dtype = a.bias_dtype;
   p.gs = (int)(a.K / a.n_groups);
   p.spg = p.gs / kStepK;
+  p.spg_mul = p.spg == 1 ? 0u : (uint32_t)((1ull << 32) / (uint64_t)p.spg + 1);
   p.ksteps = (int)(a.K / kStepK);
   p.ntiles = (int)ceil_div<int64_t>(a.N, kTileN);
   p.total_cells = (long long)p.ntiles * p.ksteps;
@@ -539,10 +769,10 @@ int woq_streamk_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   p.partial = reinterpret_cast<float *>(reinterpret_cast<char *>(a.workspace) + ZT_WOQ_COUNTER_BYTES);
   p.status = device_status_ptr();
   p.post = to_dev(a.post);
-  const int mt = a.M <= 8 ? 1 : 2;
-  const size_t stage = streamk_stage_bytes(mt, (int)a.M, a.zeros != nullptr);
-  const size_t tail = streamk_tail_bytes(mt);
-  int stages = (int)((216 * 1024 - tail) / stage);
+  const int nb = col_blocks((int)a.M);
+  const size_t stage = streamk_stage_bytes((int)a.M, a.zeros != nullptr);
+  const size_t tail = streamk_tail_bytes(nb);
+  int stages = (int)((226 * 1024 - tail) / stage);
   if (stages > kMaxStages) stages = kMaxStages;
   ZT_REQUIRE(stages >= 2, ZT_UNSUPPORTED, "zt_woq_linear: stream-K stage of %zu bytes does not fit twice", stage);
   p.stages = stages;
@@ -551,10 +781,14 @@ int woq_streamk_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   if ((long long)grid > p.total_cells) grid = (int)p.total_cells;
   const size_t smem_bytes = (size_t)stages * stage + tail;
   Maps maps;
-  const int mrows = (int)(a.M < mt * 8 ? a.M : mt * 8);
-  int rc = build_maps(a, mrows, maps);
+  int rc = build_maps(a, (int)a.M, (uint32_t)chunk_steps(nb), maps);
   if (rc != ZT_SUCCESS) return rc;
-  return mt == 1 ? launch_q<1>(maps, p, grid, smem_bytes, st) : launch_q<2>(maps, p, grid, smem_bytes, st);
+  switch (nb) {
+    case 1: return launch_q<1>(maps, p, grid, smem_bytes, st);
+    case 2: return launch_q<2>(maps, p, grid, smem_bytes, st);
+    case 3: return launch_q<3>(maps, p, grid, smem_bytes, st);
+    default: return launch_q<4>(maps, p, grid, smem_bytes, st);
+  }
 }
 
 }  // namespace zt
