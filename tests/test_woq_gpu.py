@@ -135,7 +135,7 @@ def test_stream_kernel_shapes(capi, cfg, m, monkeypatch):
         assert_close_bf16(y, exact, rtol=8e-3, atol=4e-3, what=f"cfg {cfg} M={m} K={k} N={n} vs exact")
 
 
-@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 9, 12, 16])
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
 def test_streamk_kernel(capi, m):
     """The work-balanced decode kernel: column tiles shared between CTAs (small N, long K), ragged N,
     both quantisation forms and scale dtypes; run twice to check that the arrival counters reset."""

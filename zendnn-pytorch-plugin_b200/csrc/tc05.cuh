@@ -72,7 +72,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 
 // Same, for waits that are expected to last: each poll may suspend the warp for up to `hint_ns`
 // (it wakes when the phase completes), so a waiting warp takes almost no issue slots.
-__device__ __forceinline__ bool mbar_wait_suspend(uint64_t *bar, uint32_t parity, uint32_t hint_ns = 2000) {
+__device__ __forceinline__ bool mbar_wait_suspend(uint64_t *bar, uint32_t parity, uint32_t sleep_ns = 100,
+                                                  uint32_t hint_ns = 2000) {
   const uint32_t addr = smem_u32(bar);
   for (uint32_t i = 0; i < (kSpinLimit >> 3); ++i) {
     uint32_t done;
@@ -82,6 +83,7 @@ __device__ __forceinline__ bool mbar_wait_suspend(uint64_t *bar, uint32_t parity
         : "r"(addr), "r"(parity), "r"(hint_ns)
         : "memory");
     if (done) return true;
+    if (i >= 2) __nanosleep(sleep_ns);   // a failed poll returns early more often than not: keep pollers off the issue slots
   }
   return false;
 }

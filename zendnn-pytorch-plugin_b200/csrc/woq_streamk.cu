@@ -52,12 +52,13 @@ namespace {
 constexpr int kTileN = 64;        // output columns per cell
 constexpr int kStepK = 128;       // k per cell
 constexpr int kComputeWarps = 16;
-// Converter warps: seven when the B operand is one 8-column block (the compute warps then fit in 80
-// registers, 24 warps in all), three otherwise (96 registers, 20 warps).
-__host__ __device__ constexpr int conv_warps(int nb) { return nb == 1 ? 7 : 3; }
-__host__ __device__ constexpr int sk_threads(int nb) { return 32 * (kComputeWarps + 1 + conv_warps(nb)); }
-constexpr int kMaxStages = 6;
+// Warps: 16 compute, weight producer, activation producer, epilogue, converters -- five converters when the
+// B operand is one 8-column block (24 warps, 80 registers), two otherwise (21 warps, 96 registers).
+__host__ __device__ constexpr int conv_warps(int nb) { return nb == 1 ? 5 : 2; }
+__host__ __device__ constexpr int sk_threads(int nb) { return 32 * (kComputeWarps + 3 + conv_warps(nb)); }
+constexpr int kMaxStages = 8;   // weight stages and activation slots, each
 constexpr int kRedStride = 33;
+constexpr int kMaxTokens = 4;
 
 // NB = 8-column blocks of the B operand: columns = tokens x digits (3 digits up to 2 tokens, else 2).
 __host__ __device__ constexpr int digits_for(int m) { return m <= 2 ? 3 : 2; }
@@ -66,8 +67,6 @@ __host__ __device__ constexpr int col_blocks(int m) { return (m * digits_for(m) 
 // one cell x 16 columns with 4-cell chunks (more than 8 tokens: twice the activation bytes per cell).
 __host__ __device__ constexpr int chunk_steps(int nb) { return nb <= 2 ? 8 : 4; }
 __host__ __device__ constexpr int row_blocks(int nb) { return nb <= 2 ? 2 : 1; }
-// Rows of the cross-warp reduction buffer: columns as they are (3 digits), else one row per token.
-__host__ __device__ constexpr int red_rows(int nb) { return nb <= 2 ? 8 : 4 * nb; }
 
 struct SKParams {
   const __nv_bfloat16 *x;
@@ -77,7 +76,7 @@ struct SKParams {
   const void *bias;
   __nv_bfloat16 *y;
   float *partial;  // [G][2][16][64]
-  int *counters;   // one per column tile, zero on entry and on exit
+  int *counters;   // two per column tile ([2][ntiles]: arrived, published), zero on entry and on exit
   int *status;
   int M, N, K;
   int gs, spg;  // group size in k and in cells
@@ -85,18 +84,21 @@ struct SKParams {
   int ksteps, ntiles;
   long long total_cells;
   int scale_dtype, bias_dtype;
-  int stages, stage_bytes;
+  int stages, stage_bytes;   // ring of weight stages
+  int xslots, xslot_bytes;   // ring of activation slots
   PostOpsDev post;
 };
 
 // Four nibbles of w as bytes: u = q + 8 for signed nibbles (and-then-xor), u itself for unsigned ones.
+// mask = 0x0f0f0f0f and flip = 0x08080808 are passed in registers: lop3 takes one immediate only, and
+// constants known to the compiler get re-materialised next to every use when registers are short.
 template <bool SIGNED>
-__device__ __forceinline__ uint32_t nib_bytes(uint32_t w) {
+__device__ __forceinline__ uint32_t nib_bytes(uint32_t w, uint32_t mask, uint32_t flip) {
   uint32_t r;
   if (SIGNED) {
-    asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(r) : "r"(w), "n"(0x0f0f0f0f), "n"(0x08080808));
+    asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(r) : "r"(w), "r"(mask), "r"(flip));
   } else {
-    r = w & 0x0f0f0f0fu;
+    r = w & mask;
   }
   return r;
 }
@@ -116,9 +118,6 @@ __device__ __forceinline__ int byte_sum(uint32_t v, int acc) {  // acc + the fou
   int r;
   asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(v), "r"(0x01010101), "r"(acc));
   return r;
-}
-__device__ __forceinline__ void compute_barrier() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kComputeWarps * 32) : "memory");
 }
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -170,20 +169,20 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
   constexpr int NC = 8 * NB;                  // B-operand columns held (tokens x digits, padded)
   constexpr int CS = chunk_steps(NB);         // cells per chunk
   constexpr int R = row_blocks(NB);           // 16-row blocks per compute warp
-  constexpr int kRows = red_rows(NB);
   constexpr int kWarpsPerCell = kComputeWarps / CS;
   constexpr int kConvWarps = conv_warps(NB);
   constexpr int kThreads = sk_threads(NB);
   constexpr int kWRowBytes = CS * 64;         // one weight row of a stage: [CS cells][64 B]
   constexpr int kWBytes = kTileN * kWRowBytes;
-  constexpr int kXRowBytes = CS * 256;        // one activation row of a stage: [CS cells][256 B]
+  constexpr int kXRowBytes = CS * 256;        // one activation row of a slot: [CS cells][256 B]
   constexpr int kScaleBytes = SF32 ? 4 : 2;
   constexpr int kSBytes = CS * kTileN * kScaleBytes;  // scales of the chunk: [CS groups][64]
+  // weight stage: packed weights, scales, zero points
   constexpr int kSOff = kWBytes;
-  constexpr int kZOff = kSOff + CS * 256;                      // zero points (same shape)
-  constexpr int kEOff = kZOff + (ASYM ? CS * 256 : 0);         // per (cell, column): 2^e, -8 * digit sum, sum of x
+  constexpr int kZOff = kSOff + CS * 256;
+  // activation slot: per (cell, column) tables (2^e, -8 * digit sum, sum of x), staged bf16, digit fragments
   constexpr int kEBytes = CS * NC * 4;
-  constexpr int kXOff = kEOff + (ASYM ? 3 : 2) * kEBytes;      // staged activations: [M][cell][256 B] bf16
+  constexpr int kXOff = (ASYM ? 3 : 2) * kEBytes;              // [M][cell][256 B] bf16
   using Iter = ChunkIter<CS>;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = gridDim.x;
@@ -192,86 +191,96 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
   const int kDOff = kXOff + p.M * kXRowBytes;                  // digit fragments: [cell][word pair][column][t][16 B]
   // A chunk's CS * M (token, cell) conversions take four lanes each; conv_group warps share one chunk and
   // the groups take chunks in turn, so that a small chunk's conversion latency is spread over several chunks.
+  // A group must see every phase of the barriers it waits on, so it owns fixed slots: the number of groups
+  // divides the number of slots.
   const int conv_group = min(kConvWarps, (CS * p.M + 7) / 8);
-  // A group must see every phase of the barriers it waits on, so it owns fixed stages: the number of
-  // groups divides the number of stages.
   int conv_ngroups = kConvWarps / conv_group;
-  while (p.stages % conv_ngroups != 0) --conv_ngroups;
-  float *red = reinterpret_cast<float *>(smem + (size_t)p.stages * p.stage_bytes);  // [16][kRows][33]
-  uint64_t *full_bar = reinterpret_cast<uint64_t *>(red + kComputeWarps * kRows * kRedStride);
-  uint64_t *empty_bar = full_bar + kMaxStages;
-  uint64_t *frag_bar = empty_bar + kMaxStages;
-  __shared__ int s_ticket;
+  while (p.xslots % conv_ngroups != 0) --conv_ngroups;
+  unsigned char *xring = smem + (size_t)p.stages * p.stage_bytes;
+  // Two reduction buffers [16 warps][rrows][33]: rows are the columns themselves with three digits, tokens else.
+  const int rrows = nd == 3 ? ncols : p.M;
+  const int red_buf_floats = kComputeWarps * rrows * kRedStride;
+  float *red = reinterpret_cast<float *>(xring + (size_t)p.xslots * p.xslot_bytes);
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(red + 2 * red_buf_floats);
+  uint64_t *empty_bar = full_bar + kMaxStages;   // weight stage consumed by all compute warps
+  uint64_t *xfull_bar = empty_bar + kMaxStages;  // staged activations have landed
+  uint64_t *frag_bar = xfull_bar + kMaxStages;   // digit fragments and tables are written
+  uint64_t *xempty_bar = frag_bar + kMaxStages;  // activation slot consumed by all compute warps
+  uint64_t *red_full = xempty_bar + kMaxStages;  // [2] every compute warp has written its sums
+  uint64_t *red_free = red_full + 2;             // [2] the epilogue warp has read them
 
   const long long c_begin = (long long)blockIdx.x * p.total_cells / G;
   const long long c_end = (long long)(blockIdx.x + 1) * p.total_cells / G;
 
+  // The weight producer sets up its own barriers and fills the ring once before anybody else is ready:
+  // weights do not depend on earlier work, and the first bytes take the longest to arrive.
+  Iter w_iter(c_begin, c_end, p.ksteps);
+  constexpr uint32_t kWTxBytes = (uint32_t)kWBytes + (uint32_t)kSBytes * (ASYM ? 2u : 1u);
+  int w_pre = 0;
+  if (warp == kComputeWarps) {
+    if (lane == 0) {
+      tc::prefetch_tensormap(&map_w8);
+      tc::prefetch_tensormap(&map_s);
+      for (int s = 0; s < kMaxStages; ++s) {
+        tc::mbar_init(&full_bar[s], 1);
+        tc::mbar_init(&empty_bar[s], kComputeWarps);
+      }
+      tc::mbar_fence_init();
+    }
+    __syncwarp();
+    Chunk ch;
+    while (w_pre < p.stages && w_iter.next(ch)) {
+      if (lane == 0) {
+        unsigned char *stage = smem + (size_t)w_pre * p.stage_bytes;
+        const int n0 = ch.tile * kTileN;
+        const int g0 = p.spg == 1 ? ch.step0 : ch.step0 / p.spg;
+        tc::mbar_expect_tx(&full_bar[w_pre], kWTxBytes);
+        tc::tma_load_3d(stage, &map_w8, &full_bar[w_pre], 0, ch.step0, n0);
+        tc::tma_load_2d(stage + kSOff, &map_s, &full_bar[w_pre], n0, g0);
+        if (ASYM) tc::tma_load_2d(stage + kZOff, &map_z, &full_bar[w_pre], n0, g0);
+      }
+      ++w_pre;
+    }
+  }
   if (tid == 0) {
-    tc::prefetch_tensormap(&map_w8);
     tc::prefetch_tensormap(&map_x8);
-    tc::prefetch_tensormap(&map_s);
-    for (int s = 0; s < p.stages; ++s) {
-      tc::mbar_init(&full_bar[s], 1);
-      tc::mbar_init(&empty_bar[s], kComputeWarps);
+    for (int s = 0; s < kMaxStages; ++s) {
+      tc::mbar_init(&xfull_bar[s], 1);
       tc::mbar_init(&frag_bar[s], conv_group);
+      tc::mbar_init(&xempty_bar[s], kComputeWarps);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(&red_full[b], kComputeWarps);
+      tc::mbar_init(&red_free[b], 1);
     }
     tc::mbar_fence_init();
   }
   // table entries of columns that do not exist are read (and meet zero sums): keep them zero
   {
     constexpr int kWords = (ASYM ? 3 : 2) * CS * NC;
-    for (int i = tid; i < p.stages * kWords; i += kThreads) {
+    for (int i = tid; i < p.xslots * kWords; i += kThreads) {
       const int s = i / kWords, r = i - s * kWords;
-      reinterpret_cast<float *>(smem + (size_t)s * p.stage_bytes + kEOff)[r] = 0.f;
+      reinterpret_cast<float *>(xring + (size_t)s * p.xslot_bytes)[r] = 0.f;
     }
   }
   __syncthreads();
   grid_launch_dependents();
 
   if (warp == kComputeWarps) {
-    // ---------------- producer warp ----------------
-    Iter iter(c_begin, c_end, p.ksteps);
+    // ---------------- weight producer: never touches anything an earlier kernel writes ----------------
     Chunk ch;
-    const uint32_t tx_bytes = (uint32_t)kWBytes + (uint32_t)p.M * kXRowBytes + (uint32_t)kSBytes * (ASYM ? 2u : 1u);
-    // Weights, scales and zero points of the first chunks do not depend on the preceding kernel: stage
-    // them, then wait for it, then bring those chunks' activations.
-    int pre = 0;
-    {
-      Iter head = iter;
-      while (pre < p.stages && iter.next(ch)) {
-        if (lane == 0) {
-          unsigned char *stage = smem + (size_t)pre * p.stage_bytes;
-          const int n0 = ch.tile * kTileN;
-          const int g0 = p.spg == 1 ? ch.step0 : ch.step0 / p.spg;
-          tc::mbar_expect_tx(&full_bar[pre], tx_bytes);
-          tc::tma_load_3d(stage, &map_w8, &full_bar[pre], 0, ch.step0, n0);
-          tc::tma_load_2d(stage + kSOff, &map_s, &full_bar[pre], n0, g0);
-          if (ASYM) tc::tma_load_2d(stage + kZOff, &map_z, &full_bar[pre], n0, g0);
-        }
-        ++pre;
-      }
-      grid_dependency_wait();
-      for (int i = 0; i < pre; ++i) {
-        head.next(ch);
-        if (lane == 0)
-          tc::tma_load_3d(smem + (size_t)i * p.stage_bytes + kXOff, &map_x8, &full_bar[i], 0, ch.step0, 0);
-      }
-    }
-    uint32_t s = 0, ph = 1;  // the ring has been filled once (or the range is exhausted)
-    bool ok = true;
-    while (ok && iter.next(ch)) {
-      if (!tc::mbar_wait_suspend(&empty_bar[s], ph ^ 1)) {
+    uint32_t s = 0, ph = 1;   // the ring has been filled once (or the range is exhausted)
+    while (w_iter.next(ch)) {
+      if (!tc::mbar_wait_suspend(&empty_bar[s], ph ^ 1, 300)) {
         tc::report_timeout(p.status, kStatusProducerTimeout);
-        ok = false;
         break;
       }
-      unsigned char *stage = smem + (size_t)s * p.stage_bytes;
-      const int n0 = ch.tile * kTileN;
-      const int g0 = p.spg == 1 ? ch.step0 : ch.step0 / p.spg;
       if (lane == 0) {
-        tc::mbar_expect_tx(&full_bar[s], tx_bytes);
+        unsigned char *stage = smem + (size_t)s * p.stage_bytes;
+        const int n0 = ch.tile * kTileN;
+        const int g0 = p.spg == 1 ? ch.step0 : ch.step0 / p.spg;
+        tc::mbar_expect_tx(&full_bar[s], kWTxBytes);
         tc::tma_load_3d(stage, &map_w8, &full_bar[s], 0, ch.step0, n0);
-        tc::tma_load_3d(stage + kXOff, &map_x8, &full_bar[s], 0, ch.step0, 0);
         tc::tma_load_2d(stage + kSOff, &map_s, &full_bar[s], n0, g0);
         if (ASYM) tc::tma_load_2d(stage + kZOff, &map_z, &full_bar[s], n0, g0);
       }
@@ -281,11 +290,174 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
         ph ^= 1;
       }
     }
-  } else if (warp > kComputeWarps) {
+  } else if (warp == kComputeWarps + 1) {
+    // ---------------- activation producer: its own, deeper ring of small slots ----------------
+    grid_dependency_wait();
+    Iter iter(c_begin, c_end, p.ksteps);
+    Chunk ch;
+    uint32_t s = 0, ph = 0;
+    while (iter.next(ch)) {
+      if (!tc::mbar_wait_suspend(&xempty_bar[s], ph ^ 1, 300)) {
+        tc::report_timeout(p.status, kStatusProducerTimeout);
+        break;
+      }
+      if (lane == 0) {
+        tc::mbar_expect_tx(&xfull_bar[s], (uint32_t)p.M * kXRowBytes);
+        tc::tma_load_3d(xring + (size_t)s * p.xslot_bytes + kXOff, &map_x8, &xfull_bar[s], 0, ch.step0, 0);
+      }
+      __syncwarp();
+      if (++s == (uint32_t)p.xslots) {
+        s = 0;
+        ph ^= 1;
+      }
+    }
+  } else if (warp == kComputeWarps + 2) {
+    // ---------------- epilogue warp: finishes the segments while the compute warps go on ----------------
+    // A tile shared by several CTAs is finished by the last of them to reach it.  Roles are drawn from an
+    // arrival counter as soon as the segment's turn comes (the atomic's latency overlaps the compute warps'
+    // last chunk); the others publish their partial sums and bump a second counter, for which the finisher
+    // waits (bounded) before it adds the partial sums in CTA order.
+    grid_dependency_wait();   // scratch, counters and output are shared with earlier work
+    Iter iter(c_begin, c_end, p.ksteps);
+    Chunk ch;
+    uint32_t buf = 0, bph = 0;
+    bool ok = true;
+    int *arrived = p.counters, *published = p.counters + p.ntiles;
+    const int nrow = nd == 2 ? 1 : 3;
+    while (iter.next(ch)) {
+      if (!ch.last_of_segment) continue;
+      const int n0 = ch.tile * kTileN;
+      const long long t_first = (long long)ch.tile * p.ksteps;
+      const int b_first = cta_of_cell(t_first, p.total_cells, G);
+      const int b_last = cta_of_cell(t_first + p.ksteps - 1, p.total_cells, G);
+      const bool shared_tile = b_first != b_last;
+      int ticket = 0;
+      if (shared_tile && lane == 0) ticket = atomicAdd(&arrived[ch.tile], 1);
+      float bias_v[2] = {0.f, 0.f};
+      if (p.bias) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+          if (n0 + lane + 32 * half < p.N) bias_v[half] = load_as_float(p.bias, n0 + lane + 32 * half, p.bias_dtype);
+      }
+      ticket = __shfl_sync(0xffffffffu, ticket, 0);
+      const bool finisher = !shared_tile || ticket == b_last - b_first;
+      // A CTA has two scratch slots: 0 for the tile its range starts in, 1 for the tile it ends in.  Every
+      // CTA of a shared tile but the first starts inside the tile; the first does only if it starts on it.
+      const int slot = (c_begin / p.ksteps == ch.tile) ? 0 : 1;
+      const int first_slot = ((long long)b_first * p.total_cells / G >= t_first) ? 0 : 1;
+      // The usual shared tile has one other CTA, which was there long ago: fetch its partial sums now, while
+      // the compute warps are still on this segment.
+      const bool early = shared_tile && finisher && b_last - b_first == 1 && p.M <= 8;
+      float other[2][8];
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) other[half][j] = 0.f;
+      if (ok && shared_tile && finisher) {
+        // wait until every other CTA of the tile has published
+        bool seen = false;
+        for (uint32_t i = 0; i < tc::kSpinLimit && !seen; ++i) {
+          int v = 0;
+          if (lane == 0) asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(published + ch.tile) : "memory");
+          seen = __shfl_sync(0xffffffffu, v, 0) == b_last - b_first;
+          if (!seen && i > 16) __nanosleep(200);
+        }
+        if (!seen) {
+          tc::report_timeout(p.status, kStatusEpilogueTimeout);
+          ok = false;
+        }
+        if (ok && early) {
+          const int b = b_first == (int)blockIdx.x ? b_last : b_first;
+          const float *src = p.partial + ((size_t)(b * 2 + (b == b_first ? first_slot : 0)) * 16) * kTileN;
+#pragma unroll
+          for (int half = 0; half < 2; ++half)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (j < p.M) other[half][j] = __ldcg(src + j * kTileN + lane + 32 * half);
+        }
+      }
+      if (ok && !tc::mbar_wait_suspend(&red_full[buf], bph, 400)) {
+        tc::report_timeout(p.status, kStatusEpilogueTimeout);
+        ok = false;
+      }
+      if (ok) {
+        const float *rb = red + (size_t)buf * red_buf_floats;
+        float *mine = p.partial + ((size_t)(blockIdx.x * 2 + slot) * 16) * kTileN;
+        // a lane finishes columns lane and lane + 32 of the tile, one token at a time
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int nl = lane + 32 * half;
+          const int sub = nl / (16 * R), nw = nl % (16 * R);   // which of a cell's warps holds the column, and where
+          const int n = n0 + nl;
+#pragma unroll 2
+          for (int ml = 0; ml < p.M; ++ml) {
+            // all the loads first (they are independent), then the sum in a fixed order
+            float part[3][CS];
+#pragma unroll
+            for (int rr = 0; rr < 3; ++rr)
+#pragma unroll
+              for (int cell = 0; cell < CS; ++cell)
+                part[rr][cell] = rr < nrow ? rb[((cell * kWarpsPerCell + sub) * rrows + nrow * ml + rr) * kRedStride + nw]
+                                           : 0.f;
+            float own = 0.f;
+#pragma unroll
+            for (int rr = 0; rr < 3; ++rr)
+#pragma unroll
+              for (int cell = 0; cell < CS; ++cell) own += part[rr][cell];
+            if (!finisher) {
+              mine[ml * kTileN + nl] = own;
+            } else if (n < p.N) {
+              float v = own;
+              if (early) {
+                float o = 0.f;   // ml < 8 here; a select chain keeps other[][] in registers
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  if (j == ml) o = other[half][j];
+                v = b_first == (int)blockIdx.x ? own + o : o + own;   // CTA order
+              } else if (shared_tile) {
+                // partial sums in CTA order, own term in its place; four loads in flight at a time
+                v = 0.f;
+                for (int b0 = b_first; b0 <= b_last; b0 += 4) {
+                  float term[4];
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const int b = b0 + j;
+                    term[j] = 0.f;
+                    if (b <= b_last && b != (int)blockIdx.x)
+                      term[j] = __ldcg(p.partial + ((size_t)(b * 2 + (b == b_first ? first_slot : 0)) * 16 + ml) * kTileN + nl);
+                    if (b == (int)blockIdx.x) term[j] = own;
+                  }
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) v += term[j];
+                }
+              }
+              v += bias_v[half];
+              const int64_t idx = (int64_t)ml * p.N + n;
+              v = apply_post_ops(v, p.post, idx, ZT_BF16);
+              p.y[idx] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+        if (shared_tile) {
+          if (!finisher) {
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(&published[ch.tile], 1);
+          } else if (lane == 0) {   // both counters return to zero for the next launch
+            arrived[ch.tile] = 0;
+            published[ch.tile] = 0;
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&red_free[buf]);
+      buf ^= 1;
+      if (buf == 0) bph ^= 1;
+    }
+  } else if (warp > kComputeWarps + 2) {
     // ---------------- converter warps: bf16 activations -> integer digit fragments ----------------
     // Four lanes per (token, cell); a lane converts four of the cell's sixteen 8-value pieces.
-    grid_dependency_wait();
-    const int cw = warp - kComputeWarps - 1;
+    const int cw = warp - kComputeWarps - 3;
     const int my_group = cw / conv_group, my_slot = cw - my_group * conv_group;   // warps past the last group idle
     int turn = 0;                                                                   // group whose chunk this is
     const int q = lane >> 2, sub = lane & 3;
@@ -301,11 +473,11 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
     while (iter.next(ch)) {
       const bool mine = turn == my_group;
       if (++turn == conv_ngroups) turn = 0;
-      if (mine && ok && !tc::mbar_wait_suspend(&full_bar[s], ph)) {
+      if (mine && ok && !tc::mbar_wait_suspend(&xfull_bar[s], ph, 300)) {
         tc::report_timeout(p.status, kStatusConvertTimeout);
         ok = false;
       }
-      unsigned char *stage = smem + (size_t)s * p.stage_bytes;
+      unsigned char *stage = xring + (size_t)s * p.xslot_bytes;
       if (mine && ok) {
         for (int base = my_slot * 8; base < CS * p.M; base += 8 * conv_group) {
           const int idx = base + q;
@@ -367,8 +539,8 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
               dsum[d] += __shfl_xor_sync(qmask, dsum[d], 2);
             }
             if (sub == 0) {
-              float *ftab = reinterpret_cast<float *>(stage + kEOff) + cell * NC + m * nd;
-              int *ntab = reinterpret_cast<int *>(stage + kEOff + kEBytes) + cell * NC + m * nd;
+              float *ftab = reinterpret_cast<float *>(stage) + cell * NC + m * nd;
+              int *ntab = reinterpret_cast<int *>(stage + kEBytes) + cell * NC + m * nd;
               const float f0 = e_raw == 255 ? __uint_as_float(0x7fc00000u)             // inf / NaN in the cell
                                             : __uint_as_float((uint32_t)(e - sh) << 23);  // 2^(e - 127 - sh)
 #pragma unroll
@@ -378,7 +550,7 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
                   ntab[d] = -8 * dsum[d];
                 }
               if (ASYM) {
-                float *xtab = reinterpret_cast<float *>(stage + kEOff + 2 * kEBytes) + cell * NC + m * nd;
+                float *xtab = reinterpret_cast<float *>(stage + 2 * kEBytes) + cell * NC + m * nd;
                 xtab[0] = f0 * (float)(dsum[0] + 256 * dsum[1] + 65536 * dsum[2]);   // sum_k x of the cell
               }
             }
@@ -387,15 +559,17 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
       }
       __syncwarp();
       if (mine && lane == 0) tc::mbar_arrive(&frag_bar[s]);
-      if (++s == (uint32_t)p.stages) {
+      if (++s == (uint32_t)p.xslots) {
         s = 0;
         ph ^= 1;
       }
     }
   } else {
     // ---------------- compute warps ----------------
-    grid_dependency_wait();
     const int g = lane >> 2, t = lane & 3;
+    uint32_t kmask, kflip;   // opaque to the compiler so that they stay in registers
+    asm volatile("mov.b32 %0, 0x0f0f0f0f;" : "=r"(kmask));
+    asm volatile("mov.b32 %0, 0x08080808;" : "=r"(kflip));
     const int my_step = warp / kWarpsPerCell;
     const int rb = 16 * R * (warp % kWarpsPerCell);  // first of this warp's 16 R columns within the tile
     float acc[R][NB][4];
@@ -409,18 +583,20 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
     const int w_off = (rb + g) * kWRowBytes + my_step * 64 + 16 * t;
     const int d_off = kDOff + ((my_step * 2 * ncols + g) * 4 + t) * 16;   // + (pair * ncols + 8 m) * 64
     const int d_pstride = ncols * 64;
-    const int e_off = kEOff + (my_step * NC + 2 * t) * 4;                  // + 8 m * 4
+    const int e_off = (my_step * NC + 2 * t) * 4;                          // + 8 m * 4
 
     Iter iter(c_begin, c_end, p.ksteps);
     Chunk ch;
-    uint32_t s = 0, ph = 0;
+    uint32_t s = 0, ph = 0, xs_i = 0, xph = 0;   // weight stage / activation slot and their phase bits
+    uint32_t rbuf = 0, rph = 0;                  // reduction buffer and its phase bit
     bool ok = true;
     while (iter.next(ch)) {
-      if (ok && !(tc::mbar_wait_suspend(&full_bar[s], ph) && tc::mbar_wait_suspend(&frag_bar[s], ph))) {
+      if (ok && !(tc::mbar_wait_suspend(&full_bar[s], ph, 60) && tc::mbar_wait_suspend(&frag_bar[xs_i], xph, 60))) {
         tc::report_timeout(p.status, kStatusConvertTimeout);
         ok = false;
       }
       const unsigned char *stage = smem + (size_t)s * p.stage_bytes;
+      const unsigned char *xslot = xring + (size_t)xs_i * p.xslot_bytes;
       if (ok && my_step < ch.nsteps) {
         // group of this warp's cell, relative to the chunk's first group (spg = cells per group)
         const int gl = p.spg_mul == 0 ? my_step
@@ -447,7 +623,7 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
         int part[R][NB][4];
 #pragma unroll
         for (int m = 0; m < NB; ++m) {
-          const int2 nb = *reinterpret_cast<const int2 *>(stage + e_off + kEBytes + m * 32);
+          const int2 nb = *reinterpret_cast<const int2 *>(xslot + e_off + kEBytes + m * 32);
 #pragma unroll
           for (int r = 0; r < R; ++r) {
             part[r][m][0] = nb.x;
@@ -463,7 +639,7 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
           for (int m = 0; m < NB; ++m) {
             xb[m] = make_uint4(0u, 0u, 0u, 0u);
             if (m * 8 + g < ncols)
-              xb[m] = *reinterpret_cast<const uint4 *>(stage + d_off + pr * d_pstride + m * 8 * 64);
+              xb[m] = *reinterpret_cast<const uint4 *>(xslot + d_off + pr * d_pstride + m * 8 * 64);
           }
 #pragma unroll
           for (int ci = 0; ci < 2; ++ci) {
@@ -471,8 +647,9 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
             for (int r = 0; r < R; ++r) {
               const uint32_t wa = pr == 0 ? (ci == 0 ? wv[r][0].x : wv[r][0].y) : (ci == 0 ? wv[r][0].z : wv[r][0].w);
               const uint32_t wb = pr == 0 ? (ci == 0 ? wv[r][1].x : wv[r][1].y) : (ci == 0 ? wv[r][1].z : wv[r][1].w);
-              const uint32_t a0 = nib_bytes<!ASYM>(wa), a1 = nib_bytes<!ASYM>(wb);             // nibbles 0,2,4,6
-              const uint32_t a2 = nib_bytes<!ASYM>(wa >> 4), a3 = nib_bytes<!ASYM>(wb >> 4);   // nibbles 1,3,5,7
+              const uint32_t a0 = nib_bytes<!ASYM>(wa, kmask, kflip), a1 = nib_bytes<!ASYM>(wb, kmask, kflip);  // nibbles 0,2,4,6
+              const uint32_t a2 = nib_bytes<!ASYM>(wa >> 4, kmask, kflip);                                     // nibbles 1,3,5,7
+              const uint32_t a3 = nib_bytes<!ASYM>(wb >> 4, kmask, kflip);
 #pragma unroll
               for (int m = 0; m < NB; ++m)
                 mma_u8s8_16832(part[r][m], a0, a1, a2, a3, ci == 0 ? xb[m].x : xb[m].z, ci == 0 ? xb[m].y : xb[m].w);
@@ -481,9 +658,9 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
         }
 #pragma unroll
         for (int m = 0; m < NB; ++m) {
-          const float2 f = *reinterpret_cast<const float2 *>(stage + e_off + m * 32);
+          const float2 f = *reinterpret_cast<const float2 *>(xslot + e_off + m * 32);
           float2 xs = make_float2(0.f, 0.f);
-          if (ASYM) xs = *reinterpret_cast<const float2 *>(stage + e_off + 2 * kEBytes + m * 32);
+          if (ASYM) xs = *reinterpret_cast<const float2 *>(xslot + e_off + 2 * kEBytes + m * 32);
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const float fv = e ? f.y : f.x, xsv = e ? xs.y : xs.x;
@@ -499,16 +676,28 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
         }
       }
       __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&empty_bar[s]);
+      if (lane == 0) {
+        tc::mbar_arrive(&empty_bar[s]);
+        tc::mbar_arrive(&xempty_bar[xs_i]);
+      }
       if (++s == (uint32_t)p.stages) {
         s = 0;
         ph ^= 1;
       }
+      if (++xs_i == (uint32_t)p.xslots) {
+        xs_i = 0;
+        xph ^= 1;
+      }
 
       if (ch.last_of_segment) {
-        // ---- the segment of tile ch.tile is complete: combine the warps, then finish or hand over ----
+        // ---- the segment of tile ch.tile is complete: hand the warp's sums to the epilogue warp and go on ----
         // With two digits a lane's column pair (2t, 2t+1) is one token: add the pair.  With three digits the
         // columns go out as they are and are added when the rows are read back.
+        if (ok && !tc::mbar_wait_suspend(&red_free[rbuf], rph ^ 1)) {
+          tc::report_timeout(p.status, kStatusEpilogueTimeout);
+          ok = false;
+        }
+        float *rw = red + (size_t)rbuf * red_buf_floats + warp * rrows * kRedStride;
 #pragma unroll
         for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -517,97 +706,37 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
             for (int h = 0; h < 2; ++h) {
               const int nl = 16 * r + 8 * h + g;  // within this warp's 16 R columns
               if (nd == 2) {
-                red[(warp * kRows + 4 * m + t) * kRedStride + nl] = acc[r][m][2 * h] + acc[r][m][2 * h + 1];
+                if (4 * m + t < rrows) rw[(4 * m + t) * kRedStride + nl] = acc[r][m][2 * h] + acc[r][m][2 * h + 1];
               } else if (m == 0) {
-                red[(warp * kRows + 2 * t) * kRedStride + nl] = acc[r][m][2 * h];
-                red[(warp * kRows + 2 * t + 1) * kRedStride + nl] = acc[r][m][2 * h + 1];
+                if (2 * t < rrows) rw[(2 * t) * kRedStride + nl] = acc[r][m][2 * h];
+                if (2 * t + 1 < rrows) rw[(2 * t + 1) * kRedStride + nl] = acc[r][m][2 * h + 1];
               }
               acc[r][m][2 * h] = 0.f;
               acc[r][m][2 * h + 1] = 0.f;
             }
-        compute_barrier();
-        const int n0 = ch.tile * kTileN;
-        const long long t_first = (long long)ch.tile * p.ksteps;
-        const int b_first = cta_of_cell(t_first, p.total_cells, G);
-        const int b_last = cta_of_cell(t_first + p.ksteps - 1, p.total_cells, G);
-        const bool shared_tile = b_first != b_last;
-        const int nl = tid & 63;        // column within the tile
-        const int sub = nl / (16 * R);  // which of a cell's warps holds this column
-        const int n = n0 + nl;
-        float mine[2] = {0.f, 0.f};     // up to two output rows per thread (M <= 16, 8 rows per pass)
-#pragma unroll
-        for (int pass = 0; pass < 2; ++pass) {
-          const int ml = (tid >> 6) + 8 * pass;
-          if (ml < p.M) {
-            float v = 0.f;
-            const int row0 = nd == 2 ? ml : 3 * ml, nrow = nd == 2 ? 1 : 3;
-            for (int rr = 0; rr < nrow; ++rr)
-#pragma unroll
-              for (int cell = 0; cell < CS; ++cell)
-                v += red[((cell * kWarpsPerCell + sub) * kRows + row0 + rr) * kRedStride + (nl % (16 * R))];
-            mine[pass] = v;
-          }
-        }
-        bool finish = true;
-        if (shared_tile) {
-          const int slot = (c_begin / p.ksteps == ch.tile) ? 0 : 1;
-          float *dst = p.partial + ((size_t)(blockIdx.x * 2 + slot) * 16) * kTileN;
-#pragma unroll
-          for (int pass = 0; pass < 2; ++pass) {
-            const int ml = (tid >> 6) + 8 * pass;
-            if (ml < p.M) dst[ml * kTileN + nl] = mine[pass];
-          }
-          __threadfence();
-          compute_barrier();
-          if (tid == 0) s_ticket = atomicAdd(&p.counters[ch.tile], 1);
-          compute_barrier();
-          finish = (s_ticket == b_last - b_first);
-          if (finish) {
-            __threadfence();
-            if (tid == 0) p.counters[ch.tile] = 0;
-#pragma unroll
-            for (int pass = 0; pass < 2; ++pass) {
-              const int ml = (tid >> 6) + 8 * pass;
-              if (ml < p.M) {
-                float v = 0.f;
-                for (int b = b_first; b <= b_last; ++b) {
-                  const long long bs = (long long)b * p.total_cells / G;
-                  const int bslot = (bs / p.ksteps == ch.tile) ? 0 : 1;
-                  v += __ldcg(p.partial + ((size_t)(b * 2 + bslot) * 16 + ml) * kTileN + nl);
-                }
-                mine[pass] = v;
-              }
-            }
-          }
-        }
-        if (finish && n < p.N) {
-#pragma unroll
-          for (int pass = 0; pass < 2; ++pass) {
-            const int ml = (tid >> 6) + 8 * pass;
-            if (ml < p.M) {
-              float v = mine[pass];
-              if (p.bias) v += load_as_float(p.bias, n, p.bias_dtype);
-              const int64_t idx = (int64_t)ml * p.N + n;
-              v = apply_post_ops(v, p.post, idx, ZT_BF16);
-              p.y[idx] = __float2bfloat16_rn(v);
-            }
-          }
-        }
-        compute_barrier();  // red[] and s_ticket are reused by the next segment
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&red_full[rbuf]);
+        rbuf ^= 1;
+        if (rbuf == 0) rph ^= 1;
       }
     }
   }
 }
 
+// Weight stage: packed weights, scales (+ zero points).
 size_t streamk_stage_bytes(int M, bool asym) {
+  const size_t cs = chunk_steps(col_blocks(M));
+  return kTileN * cs * 64 + cs * 256 * (asym ? 2 : 1);
+}
+// Activation slot: per-column tables, staged bf16 activations, digit fragments.
+size_t streamk_xslot_bytes(int M, bool asym) {
   const size_t nb = col_blocks(M), cs = chunk_steps((int)nb), ncols = (size_t)M * digits_for(M);
-  // weights, scales (+ zero points), per-column tables, staged bf16 activations, digit fragments
-  size_t b = kTileN * cs * 64 + cs * 256 * (asym ? 2 : 1) + (asym ? 3 : 2) * cs * nb * 8 * 4 + (size_t)M * cs * 256 +
-             cs * 128 * ncols;
+  const size_t b = (asym ? 3 : 2) * cs * nb * 8 * 4 + (size_t)M * cs * 256 + cs * 128 * ncols;
   return (b + 127) / 128 * 128;
 }
-size_t streamk_tail_bytes(int nb) {
-  return (size_t)kComputeWarps * red_rows(nb) * kRedStride * sizeof(float) + 3 * kMaxStages * sizeof(uint64_t) + 64;
+size_t streamk_tail_bytes(int M) {   // two reduction buffers and the barriers
+  const size_t rrows = digits_for(M) == 3 ? (size_t)M * 3 : (size_t)M;
+  return 2 * kComputeWarps * rrows * kRedStride * sizeof(float) + (5 * kMaxStages + 4) * sizeof(uint64_t) + 64;
 }
 
 struct Maps {
@@ -730,7 +859,9 @@ int launch_q(const Maps &m, const SKParams &p, int grid, size_t smem_bytes, cuda
 size_t woq_streamk_workspace_bytes() { return (size_t)sm_count() * 2 * 16 * kTileN * sizeof(float); }
 
 bool woq_streamk_supported(const zt_woq_linear_args_t &a) {
-  if (a.M < 1 || a.M > 16 || a.N < 1) return false;
+  // Beyond four tokens the conversion of the activations (redone by every CTA) outweighs the cheaper
+  // weight path and the register-ring decode kernel is faster.
+  if (a.M < 1 || a.M > kMaxTokens || a.N < 1) return false;
   if (a.K % kStepK != 0 || a.n_groups <= 0 || a.K % a.n_groups != 0) return false;
   const int64_t gs = a.K / a.n_groups;
   if (gs % kStepK != 0) return false;
@@ -739,7 +870,7 @@ bool woq_streamk_supported(const zt_woq_linear_args_t &a) {
   const uintptr_t ptrs = reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.wq) |
                          reinterpret_cast<uintptr_t>(a.scales) | reinterpret_cast<uintptr_t>(a.zeros);
   if (ptrs & 15) return false;
-  if (ceil_div<int64_t>(a.N, kTileN) * (int64_t)sizeof(int) > ZT_WOQ_COUNTER_BYTES) return false;
+  if (2 * ceil_div<int64_t>(a.N, kTileN) * (int64_t)sizeof(int) > ZT_WOQ_COUNTER_BYTES) return false;  // two counters per tile
   return a.K <= (1 << 22) && a.N <= (1 << 30);  // group lookups divide by multiplication: (K/128)^2 < 2^32
 }
 
@@ -771,24 +902,28 @@ int woq_streamk_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   p.post = to_dev(a.post);
   const int nb = col_blocks((int)a.M);
   const size_t stage = streamk_stage_bytes((int)a.M, a.zeros != nullptr);
-  const size_t tail = streamk_tail_bytes(nb);
-  int stages = (int)((226 * 1024 - tail) / stage);
+  const size_t xslot = streamk_xslot_bytes((int)a.M, a.zeros != nullptr);
+  const size_t tail = streamk_tail_bytes((int)a.M);
+  const size_t budget = 226 * 1024 - tail;
+  // Activation slots are small and let the conversion run ahead of the weights: six of them for up to two
+  // tokens, four up to four, three beyond; fewer when that buys no weight stage less than three.
+  int xslots = a.M <= 2 ? 6 : a.M <= 4 ? 4 : 3;
+  while (xslots > 2 && (budget - xslots * xslot) / stage < 3) --xslots;
+  int stages = (int)((budget - xslots * xslot) / stage);
   if (stages > kMaxStages) stages = kMaxStages;
   ZT_REQUIRE(stages >= 2, ZT_UNSUPPORTED, "zt_woq_linear: stream-K stage of %zu bytes does not fit twice", stage);
   p.stages = stages;
   p.stage_bytes = (int)stage;
+  p.xslots = xslots;
+  p.xslot_bytes = (int)xslot;
   int grid = sm_count();
   if ((long long)grid > p.total_cells) grid = (int)p.total_cells;
-  const size_t smem_bytes = (size_t)stages * stage + tail;
+  const size_t smem_bytes = (size_t)stages * stage + (size_t)xslots * xslot + tail;
   Maps maps;
   int rc = build_maps(a, (int)a.M, (uint32_t)chunk_steps(nb), maps);
   if (rc != ZT_SUCCESS) return rc;
-  switch (nb) {
-    case 1: return launch_q<1>(maps, p, grid, smem_bytes, st);
-    case 2: return launch_q<2>(maps, p, grid, smem_bytes, st);
-    case 3: return launch_q<3>(maps, p, grid, smem_bytes, st);
-    default: return launch_q<4>(maps, p, grid, smem_bytes, st);
-  }
+  ZT_REQUIRE(nb == 1, ZT_UNSUPPORTED, "zt_woq_linear: the stream-K kernel takes at most %d tokens", kMaxTokens);
+  return launch_q<1>(maps, p, grid, smem_bytes, st);
 }
 
 }  // namespace zt
