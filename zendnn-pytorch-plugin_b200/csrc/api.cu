@@ -42,6 +42,14 @@ int cuda_fail(cudaError_t e, const char *what) {
   return ZT_CUDA_ERROR;
 }
 
+bool overlap_launches() {
+  static const bool on = [] {
+    const char *e = std::getenv("ZENTORCH_B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;

@@ -39,6 +39,35 @@ inline int launch_status(const char *kernel) {
 
 int sm_count();
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// Decode kernels are launched with programmatic stream serialisation: a kernel lets its successor start
+// early (grid_launch_dependents) and itself waits for its predecessor (grid_dependency_wait) only before
+// it touches what earlier work may write -- activations, scratch, output.  Weights, scales and zero points
+// are read before that wait: they must not be written by the kernel launched directly before on the same
+// stream unless that kernel completes normally, which every kernel but these does.
+// ZENTORCH_B200_PDL=0 launches with ordinary stream ordering.
+bool overlap_launches();
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename Kernel, typename... Args>
+inline cudaError_t launch_overlapped(Kernel kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_launches() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+#endif
+
 // ---- post-op chain ----------------------------------------------------------------------------
 struct PostOpsDev {
   int n_ops;

@@ -50,6 +50,7 @@ struct StreamParams {
   int kslice;
   int nsplit;
   int scale_dtype, bias_dtype;
+  int early_trigger;  // the grid is resident at once: let the next kernel in at entry rather than after the main loop
   PostOpsDev post;
 };
 
@@ -165,8 +166,14 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
     cp_async_commit();
   };
 
+  // Weights and scales do not depend on the kernel before this one: fill the register ring, and only then
+  // wait for that kernel before touching activations, scratch and output.
+  // The next kernel may come in at once when this grid is resident as a whole; otherwise only after the main
+  // loop, when every CTA of this grid has started (its CTAs would take the places of this grid's later ones).
+  if (p.early_trigger) grid_launch_dependents();
 #pragma unroll
   for (int s = 0; s < RING; ++s) prefetch(ring[s], step_k(s / kSPC, s % kSPC));
+  grid_dependency_wait();
   stage(0, 0);
 
   float acc[R][MT][4];
@@ -261,6 +268,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   }
 
   // ---- reduce the warps (they split K) through shared memory ------------------------------------------
+  if (!p.early_trigger) grid_launch_dependents();
   __syncthreads();
   float *red = reinterpret_cast<float *>(smem_raw);  // [W][kCols][kTileN + 1]
   constexpr int kRedStride = kTileN + 1;
@@ -331,7 +339,7 @@ size_t stream_smem_bytes(int M) {
 }
 
 template <int MT, int CFG, bool ASYM, bool SF32>
-int launch(const StreamParams &p, dim3 grid, cudaStream_t st) {
+int launch(const StreamParams &p_in, dim3 grid, cudaStream_t st) {
   using S = Shape<MT, CFG>;
   auto kern = woq_stream_kernel<MT, S::R, S::RING, S::W, ASYM, SF32>;
   static bool configured = false;
@@ -339,7 +347,14 @@ int launch(const StreamParams &p, dim3 grid, cudaStream_t st) {
     ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
     configured = true;
   }
-  kern<<<grid, S::W * 32, stream_smem_bytes<MT, CFG>(p.M), st>>>(p);
+  const size_t smem = stream_smem_bytes<MT, CFG>(p_in.M);
+  static int per_sm_for_m[17] = {0};   // resident CTAs per SM; the dynamic shared memory depends on M only
+  int &per_sm = per_sm_for_m[p_in.M];
+  if (per_sm == 0) ZT_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, S::W * 32, smem));
+  StreamParams p = p_in;
+  // half the resident capacity at most: the next kernel's CTAs then find room beside this grid's
+  p.early_trigger = (long long)grid.x * grid.y * 2 <= (long long)per_sm * sm_count() ? 1 : 0;
+  ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(S::W * 32), smem, st, p));
   return launch_status("woq_stream_kernel");
 }
 

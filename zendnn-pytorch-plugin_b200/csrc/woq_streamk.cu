@@ -119,8 +119,6 @@ __device__ __forceinline__ int byte_sum(uint32_t v, int acc) {  // acc + the fou
   asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(v), "r"(0x01010101), "r"(acc));
   return r;
 }
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // The CTA whose cell range contains cell c, for ranges [b*total/G, (b+1)*total/G).
 __device__ __forceinline__ int cta_of_cell(long long c, long long total, int G) {
@@ -815,15 +813,6 @@ int build_maps(const zt_woq_linear_args_t &a, int mrows, uint32_t cs, Maps &m) {
   return ZT_SUCCESS;
 }
 
-// ZENTORCH_B200_WOQ_PDL=0 launches the kernel with ordinary stream ordering.
-bool overlap_launches() {
-  static const bool on = [] {
-    const char *e = std::getenv("ZENTORCH_B200_WOQ_PDL");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
-
 template <int NB, bool ASYM, bool SF32>
 int launch(const Maps &m, const SKParams &p, int grid, size_t smem_bytes, cudaStream_t st) {
   auto kern = woq_streamk_kernel<NB, ASYM, SF32>;
@@ -832,17 +821,8 @@ int launch(const Maps &m, const SKParams &p, int grid, size_t smem_bytes, cudaSt
     ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     configured = true;
   }
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3((unsigned)sk_threads(NB));
-  cfg.dynamicSmemBytes = smem_bytes;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = overlap_launches() ? 1 : 0;
-  ZT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, m.w8, m.x8, m.s, m.z, p));
+  ZT_CUDA_OK(launch_overlapped(kern, dim3((unsigned)grid), dim3((unsigned)sk_threads(NB)), smem_bytes, st, m.w8, m.x8, m.s,
+                               m.z, p));
   return launch_status("woq_streamk_kernel");
 }
 
