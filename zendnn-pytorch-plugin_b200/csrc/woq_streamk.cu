@@ -15,7 +15,7 @@
 // ([row][cell][256 B]) and the scales / zero points of the chunk's groups ([group][64 columns]).  A
 // chunk always loads the full box (cells past the CTA's range are simply not used; rows and cells
 // beyond N and K read as zero).  Nothing is staged through registers, so the bytes in flight per SM
-// are bounded by shared memory (> 100 KB), not by occupancy.  No multicast is used.
+// are bounded by shared memory (> 100 KB), not by occupancy.  Loads are plain per-CTA loads.
 //
 // Arithmetic: integer tensor-core MMAs on exact operands.  A packed word holds eight nibbles;
 // (w & 0x0f0f0f0f) is four of them as bytes and ((w >> 4) & 0x0f0f0f0f) the other four (signed nibbles

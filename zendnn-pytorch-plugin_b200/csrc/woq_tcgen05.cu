@@ -7,7 +7,7 @@
 // per k-block and reuses it for up to 256 tokens.  One persistent CTA per SM walks over
 // (128 columns) x (BT tokens) tiles; tiles that share a weight block are adjacent in the order.
 //
-//   warp 0        TMA producer (no multicast): the activation tile of every k-block, and the packed
+//   warp 0        TMA producer (plain per-CTA loads): the activation tile of every k-block, and the packed
 //                 weights in chunks of four k-blocks (128 rows x 128 B, 128-byte swizzle) into a ring
 //                 of their own, several chunks ahead, so that enough weight bytes are in flight
 //   warp 1        TMEM allocation, tcgen05.mma.kind::f16 issue (bf16 x bf16 -> fp32), TMEM release
