@@ -223,6 +223,8 @@ def run_ours(args):
 
         # ---- weight-only int4 decode GEMV (config 1, M = 1), HBM-bound ---------------------------------
         woq = bench_woq(torch, _capi, lib, dev, stream, sptr, args.steps, pk) if rank == 0 else {}
+        layer_cfg = bench_layer_configs(torch, _capi, lib, dev, stream, sptr, pk) if rank == 0 else None
+    moe_cfg = bench_moe_config(torch, _capi, dev, pk) if rank == 0 else None
 
     # ---- end to end through torch.ops with host buffers ---------------------------------------------------
     e2e = bench_e2e(torch, dev, sets, args.steps, world)
@@ -270,6 +272,7 @@ def run_ours(args):
             },
             "woq_decode": woq.get("woq_decode"), "woq_decode_large_layer": woq.get("woq_decode_large_layer"),
             "woq_prefill": woq.get("woq_prefill"), "tp_mlp": tp_mlp,
+            "llama8b_layer": layer_cfg, "moe_int4": moe_cfg,
             "cpu_baseline": cpu,
             "e2e": {"value": round(e2e_value, 3), "unit": "TOP/s", "h2d_bytes_per_step": e2e["h2d"],
                     "d2h_bytes_per_step": e2e["d2h"], "calls_per_step": 1,
@@ -359,6 +362,100 @@ def bench_woq(torch, _capi, lib, dev, stream, sptr, steps, pk):
              "woq_prefill": (2048, 4096, 4096, "BASELINE config 1 at M=2048")}
     return {name: bench_woq_case(torch, _capi, lib, dev, stream, sptr, steps, pk, m, k, n, label)
             for name, (m, k, n, label) in cases.items()}
+
+
+def bench_layer_configs(torch, _capi, lib, dev, stream, sptr, pk):
+    """BASELINE config 2: the seven WOQ int4 projections of a Llama-3-8B decoder layer at decode batch
+    M in {1, 8, 32, 64} and prefill M = 2048.  Per M: the layer's summed time, its algorithmic bytes per
+    second (decode) or flops per second (prefill).  Weights rotate over copies larger than L2 in total."""
+    import ctypes as C
+    shapes = [("q", 4096, 4096), ("k", 4096, 1024), ("v", 4096, 1024), ("o", 4096, 4096), ("gate", 4096, 14336),
+              ("up", 4096, 14336), ("down", 14336, 4096)]
+    gs = 128
+    weights = {}
+    for _, k, n in shapes:
+        if (k, n) not in weights:
+            w_bytes = n * k // 2 + (k // gs) * n * 4
+            copies = max(2, -(-int(1.5 * L2_BYTES) // w_bytes))
+            packed0, scales0 = device_woq_weights(torch, _capi, dev, k, n, seed=k + n)
+            weights[(k, n)] = [(packed0.clone(), scales0.clone()) for _ in range(copies)]
+    out = {}
+    for m in (1, 8, 32, 64, 2048):
+        total_us, total_bytes, total_flops = 0.0, 0, 0.0
+        for _, k, n in shapes:
+            xs = torch.randn(m, k, device=dev).to(torch.bfloat16)
+            bs = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+            ws = _capi.woq_workspace(lib.zt_woq_linear_workspace_bytes(m, n, k), dev)
+            ys = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            arglist = []
+            for wq, sc in weights[(k, n)]:
+                a = _capi.WoqLinearArgs()
+                a.x, a.M, a.K, a.N = xs.data_ptr(), m, k, n
+                a.wq, a.scales, a.zeros = wq.data_ptr(), sc.data_ptr(), None
+                a.scale_dtype, a.n_groups = _capi.ZT_F32, k // gs
+                a.bias, a.bias_dtype = bs.data_ptr(), _capi.ZT_BF16
+                a.y, a.workspace, a.workspace_bytes, a.algo = ys.data_ptr(), ws.data_ptr(), ws.numel(), _capi.ZT_ALGO_AUTO
+                arglist.append(a)
+
+            def one_pass():
+                for a in arglist:
+                    _capi.check(lib.zt_woq_linear(C.byref(a), sptr))
+
+            g = torch.cuda.CUDAGraph()
+            one_pass()
+            stream.synchronize()
+            with torch.cuda.graph(g, stream=stream):
+                one_pass()
+            g.replay()
+            reps = 5
+            us = time_region(torch, g.replay, reps) * 1e3 / (reps * len(arglist))
+            total_us += us
+            total_bytes += n * k // 2 + (k // gs) * n * 4 + m * k * 2 + m * n * 2 + n * 2
+            total_flops += 2.0 * m * n * k
+        entry = {"layer_us": round(total_us, 2)}
+        if m <= 64:
+            gbs = total_bytes / (total_us * 1e-6) / 1e9
+            entry.update({"algorithmic_GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / pk["hbm_gbs"], 4)})
+        else:
+            tf = total_flops / (total_us * 1e-6) / 1e12
+            entry.update({"TFLOPps": round(tf, 1), "frac_of_bf16_peak": round(tf / pk["bf16_tflops"], 4)})
+        out[f"M={m}"] = entry
+    return {"workload": "BASELINE config 2: Llama-3-8B decoder layer, seven WOQ int4 (group 128) projections, "
+                        "one launch each, weights not in L2", "per_batch": out}
+
+
+def bench_moe_config(torch, _capi, dev, pk):
+    """BASELINE config 3: Mixtral-style int4 expert FFN, 8 experts, top-2 over 256 tokens, hidden 4096, ffn 14336."""
+    t, h, inter, e, topk, gs = 256, 4096, 14336, 8, 2, 128
+    g = torch.Generator(device=dev).manual_seed(3)
+    x = torch.randn(t, h, generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn(t, e, generator=g, device=dev)
+    wts, ids = torch.topk(torch.softmax(logits, dim=-1), topk, dim=-1)
+    wts = (wts / wts.sum(dim=-1, keepdim=True)).float().contiguous()
+    ids = ids.to(torch.int32).contiguous()
+    w13 = torch.randint(-2**31, 2**31 - 1, (e, 2 * inter, h // 8), generator=g, device=dev, dtype=torch.int32)
+    s13 = (torch.rand(e, h // gs, 2 * inter, generator=g, device=dev) * 0.006 + 0.007).contiguous()
+    w2 = torch.randint(-2**31, 2**31 - 1, (e, h, inter // 8), generator=g, device=dev, dtype=torch.int32)
+    s2 = (torch.rand(e, inter // gs, h, generator=g, device=dev) * 0.006 + 0.007).contiguous()
+    for _ in range(2):
+        _capi.moe_woq(x, wts, ids, w13, s13, w2, s2)
+    torch.cuda.synchronize()
+    reps = 5
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        _capi.moe_woq(x, wts, ids, w13, s13, w2, s2)
+    end.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(end) * 1e3 / reps
+    w_bytes = w13.numel() * 4 + w2.numel() * 4 + s13.numel() * 4 + s2.numel() * 4
+    flops = 2.0 * t * topk * (h * 2 * inter + inter * h)
+    return {"workload": "BASELINE config 3: int4 MoE FFN, 8 experts, top-2, 256 tokens, hidden 4096, ffn 14336 "
+                        "(routing, grouping, two grouped tcgen05 GEMMs, SiLU-mul, combine)",
+            "us_per_call": round(us, 1), "weight_bytes": w_bytes, "weight_GBps": round(w_bytes / (us * 1e-6) / 1e9, 1),
+            "frac_of_hbm_peak": round(w_bytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 4),
+            "TFLOPps": round(flops / (us * 1e-6) / 1e12, 1),
+            "l2": "705 MB of expert weights per call exceed L2", "launch": "plain launches on the current stream"}
 
 
 def bench_tp_mlp(torch, dist, dev, steps, world):

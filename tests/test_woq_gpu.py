@@ -179,8 +179,9 @@ def test_post_ops(capi, name, algo_name):
 @pytest.mark.parametrize("asym,scale_dtype", [(False, torch.float32), (False, torch.bfloat16), (True, torch.float32),
                                               (True, torch.bfloat16)])
 def test_tcgen05_kernel(capi, tile, asym, scale_dtype):
+    # K = 128, 320, 448: packed-weight chunks of four k-blocks that end in a partial chunk
     for (m, k, n, gs) in ((17, 256, 128, 128), (100, 512, 200, 64), (300, 1024, 136, 128), (64, 128, 8, 32),
-                          (257, 2048, 384, 2048)):
+                          (257, 2048, 384, 2048), (40, 320, 72, 32), (129, 448, 260, 64)):
         x, q, s, z, b = make_woq_case(m, k, n, gs, seed=m + n, asym=asym, scale_dtype=scale_dtype)
         algo = capi.ZT_ALGO_TCGEN05 | (tile << 8)
         y, packed = _run(capi, x, q, s, z, b, algo)

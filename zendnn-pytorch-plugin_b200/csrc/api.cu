@@ -211,6 +211,10 @@ extern "C" int zt_woq_linear(const zt_woq_linear_args_t *a, void *stream) {
     const bool tiny = a->N * a->K < (1 << 18);
     if (stream_ok && !tiny)
       algo = ZT_ALGO_SKINNY;
+    else if (a->M <= 32 && a->N <= 8192 && !tiny && woq_skinny_supported(*a))
+      // 17..32 tokens on a layer with few 128-column tiles: the tensor-core kernel would run its whole K loop
+      // on 8..64 SMs, the mma.sync kernel splits K over all of them (measured 2x..4x faster there)
+      algo = ZT_ALGO_SKINNY;
     else if (woq_tcgen05_supported(*a))
       algo = ZT_ALGO_TCGEN05;
     else if (woq_skinny_supported(*a) && !tiny && a->M <= env().woq_skinny_max)

@@ -24,6 +24,12 @@
 // weight and scale tensors; the number of tiles is read from device memory, so no host
 // synchronisation is needed between routing and the GEMM.
 //
+// All eight dequantisation warps take every k-block together, in order.  Giving different k-blocks to
+// different warp teams (to overlap the conversion latency of several k-blocks) is only sound when the
+// number of stages is a multiple of the number of teams: otherwise consecutive uses of a stage belong to
+// different teams, a team can reach its wait two uses ahead of the stage's barrier, and an mbarrier
+// parity wait that far ahead passes at once.
+//
 // Accumulators are double buffered in tensor memory: the epilogue of a tile overlaps the next tile's
 // main loop.  All waits are bounded (see tc05.cuh).
 //
