@@ -11,12 +11,12 @@
 //                 weights in chunks of four k-blocks (128 rows x 128 B, 128-byte swizzle) into a ring
 //                 of their own, several chunks ahead, so that enough weight bytes are in flight
 //   warp 1        TMEM allocation, tcgen05.mma.kind::f16 issue (bf16 x bf16 -> fp32), TMEM release
-//   warps 2..9    dequantisation: 128-bit shared-memory loads of packed nibbles from the chunk ring
+//   warps 2..17   dequantisation (two packed words per thread and k-block): shared-memory loads of packed nibbles from the chunk ring
 //                 (the group's scale / zero point is prefetched from global memory), nibble -> bf16
 //                 with lop3, exact subtraction of the encoding bias, multiplication by the scale in
 //                 bf16x2 arithmetic, byte-permute into k order, 16-byte stores into the canonical
 //                 K-major 128-byte-swizzled operand layout, fence.proxy.async, mbarrier arrive
-//   warps 10..13  epilogue: tcgen05.ld (lane = output column n, register j = token), transpose
+//   warps 18..21  epilogue: tcgen05.ld (lane = output column n, register j = token), transpose
 //                 through shared memory so that stores run along n, bias + post-ops, bf16 stores
 //
 // Grouped mode (mixture-of-experts): the rows of X are sorted by expert, a device-side table lists the
@@ -50,7 +50,8 @@ namespace {
 
 constexpr int kBN = 128;  // output columns per tile (UMMA M)
 constexpr int kBK = 64;   // k per stage: 128 bytes of bf16
-constexpr int kDqWarps = 8;
+constexpr int kDqWarps = 16;
+constexpr int kWPT = 32 / kDqWarps;   // packed words per dequantisation thread and k-block (4 with 8 warps, 2 with 16)
 constexpr int kEpiWarps = 4;
 constexpr int kThreads = 64 + 32 * (kDqWarps + kEpiWarps);
 constexpr int kEpiRowStride = 36;  // floats; 144 bytes keeps 16-byte alignment and spreads banks
@@ -299,9 +300,12 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
     }
   } else if (warp < 2 + kDqWarps) {
     // ---------------- dequantisation warps ----------------
-    const int d = threadIdx.x - 64;   // 0..255
-    const int row = d >> 1;           // weight row (output column) within the tile
-    const int half = d & 1;           // which 32 k of the 64-wide k-block
+    const int d = threadIdx.x - 64;                 // 0 .. 32 * kDqWarps - 1
+    constexpr int kThreadsPerRow = 8 / kWPT;        // a k-block row is 8 packed words
+    const int row = d / kThreadsPerRow;             // weight row (output column) within the tile
+    const int sub = d % kThreadsPerRow;
+    const int half = sub * kWPT / 4;                // which 32 k of the 64-wide k-block (one scale each)
+    const int word0 = sub * kWPT % 4;               // first of this thread's words within that half
     // scales (and zero points) come from global memory, fetched kPrefetch k-blocks ahead.  The fetch
     // cursor keeps its tile's column and expert offset; they change only when it moves to a new tile.
     const int gs_shift = (p.gs & (p.gs - 1)) == 0 ? __ffs(p.gs) - 1 : -1;
@@ -334,10 +338,10 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
     for (int i = 0; i < kPrefetch; ++i) fetch_next(ring[i]);
     // loop-invariant shared-memory offsets of this thread: where it reads its 16 packed bytes of
     // k-block j of a chunk, and where it writes its four 16-byte bf16 chunks of a stage row
-    uint32_t st_off[4];
+    uint32_t st_off[kWPT];
     const uint32_t row_off = row * 128, row_x = row & 7;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) st_off[i] = row * 128 + (((4 * half + i) ^ (row & 7)) << 4);
+    for (int i = 0; i < kWPT; ++i) st_off[i] = row * 128 + (((4 * half + word0 + i) ^ (row & 7)) << 4);
     uint32_t it = 0;    // k-blocks converted so far (bf16 stage ring position)
     uint32_t pit = 0;   // packed chunks consumed so far
     int kb = 0;         // k-block within the current tile
@@ -365,14 +369,25 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
           }
           if (ok) {
             // this thread's 32 nibbles of the k-block: 16-byte chunk (2j + half) of the swizzled 128-byte row
-            const uint4 wv = *reinterpret_cast<const uint4 *>(packed + ps * kChunkBytes + row_off +
-                                                              ((((uint32_t)(2 * j + half)) ^ row_x) << 4));
+            const unsigned char *src = packed + ps * kChunkBytes + row_off + ((((uint32_t)(2 * j + half)) ^ row_x) << 4) +
+                                       4 * word0;
+            uint32_t words[kWPT];
+            if (kWPT == 4) {
+              const uint4 wv = *reinterpret_cast<const uint4 *>(src);
+              words[0] = wv.x;
+              words[1] = wv.y;
+              words[kWPT - 2] = wv.z;
+              words[kWPT - 1] = wv.w;
+            } else {
+              const uint2 wv = *reinterpret_cast<const uint2 *>(src);
+              words[0] = wv.x;
+              words[1] = wv.y;
+            }
             unsigned char *wstage = smem + s * L::kStageBytes;
-            const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
             uint32_t s_hi = 0, s_lo = 0;
             if (!ASYM) split_bf16x2(cur.s, s_hi, s_lo);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < kWPT; ++i) {
               uint4 o;
               if (ASYM) {
                 // zero-point form in fp32, one rounding: bf16((q - 8) * s + z), pairs come out in k order
