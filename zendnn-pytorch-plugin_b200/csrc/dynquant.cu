@@ -73,6 +73,10 @@ __global__ void __launch_bounds__(kThreads) dynquant_vec_kernel(const void *__re
                                                                 uint8_t *__restrict__ q, float *__restrict__ scales,
                                                                 int32_t *__restrict__ zps) {
   __shared__ float scratch[16];
+  // programmatic dependent launch: let the GEMM that follows start its prologue and weight prefetch now;
+  // wait for the kernel before this one (it may still read the buffers written here) before any access
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t row = blockIdx.x;
   const int64_t base = row * K;
   const int64_t chunks = K / kVec;
@@ -147,6 +151,8 @@ __global__ void __launch_bounds__(kThreads) dynquant_scalar_kernel(const void *_
                                                                    uint8_t *__restrict__ q, float *__restrict__ scales,
                                                                    int32_t *__restrict__ zps) {
   __shared__ float scratch[16];
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t row = blockIdx.x;
   const int64_t base = row * K;
   float hi = 0.f, lo = 0.f;
@@ -190,14 +196,14 @@ int dynamic_quantize_launch(const void *x, int x_dtype, int64_t M, int64_t K, in
   const dim3 grid((unsigned)M);
   if (vec) {
     if (u8)
-      dynquant_vec_kernel<true><<<grid, kThreads, 0, st>>>(x, x_dtype, K, qq, scales, zps);
+      ZT_CUDA_OK(launch_overlapped(dynquant_vec_kernel<true>, dim3(grid), dim3(kThreads), (size_t)0, st, x, x_dtype, K, qq, scales, zps));
     else
-      dynquant_vec_kernel<false><<<grid, kThreads, 0, st>>>(x, x_dtype, K, qq, scales, zps);
+      ZT_CUDA_OK(launch_overlapped(dynquant_vec_kernel<false>, dim3(grid), dim3(kThreads), (size_t)0, st, x, x_dtype, K, qq, scales, zps));
   } else {
     if (u8)
-      dynquant_scalar_kernel<true><<<grid, kThreads, 0, st>>>(x, x_dtype, K, qq, scales, zps);
+      ZT_CUDA_OK(launch_overlapped(dynquant_scalar_kernel<true>, dim3(grid), dim3(kThreads), (size_t)0, st, x, x_dtype, K, qq, scales, zps));
     else
-      dynquant_scalar_kernel<false><<<grid, kThreads, 0, st>>>(x, x_dtype, K, qq, scales, zps);
+      ZT_CUDA_OK(launch_overlapped(dynquant_scalar_kernel<false>, dim3(grid), dim3(kThreads), (size_t)0, st, x, x_dtype, K, qq, scales, zps));
   }
   return launch_status("dynquant_kernel");
 }

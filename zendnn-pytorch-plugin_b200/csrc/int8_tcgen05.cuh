@@ -185,16 +185,35 @@ __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: the next kernel on the stream may start its prologue now; this one waits
+  // for its predecessor (the per-token quantisation) only where it touches what that kernel writes.
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       uint32_t it = 0;  // ring position, runs across tiles
       bool ok = true;
+      // First pass over the ring: the weight tiles do not depend on the preceding kernel, so they are
+      // requested before the dependency wait and the activation tiles of the same stages after it.
+      int pre = 0;
+      if ((int)blockIdx.x < total_tiles) {
+        const int m0 = ((int)blockIdx.x % p.m_tiles) * (MH * kBM);
+        const int n0 = ((int)blockIdx.x / p.m_tiles) * BN;
+        pre = num_kb < STAGES ? num_kb : STAGES;
+        for (int kb = 0; kb < pre; ++kb) {
+          tc::mbar_expect_tx(&full_bar[kb], L::kStageBytes);
+          tc::tma_load_2d(smem + kb * L::kStageBytes + L::kABytes, &tmap_b, &full_bar[kb], kb * kBK, n0);
+        }
+        grid_dependency_wait();
+        for (int kb = 0; kb < pre; ++kb)
+          tc::tma_load_2d(smem + kb * L::kStageBytes, &tmap_a, &full_bar[kb], kb * kBK, m0);
+        it = (uint32_t)pre;
+      }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % p.m_tiles) * (MH * kBM);
         const int n0 = (tile / p.m_tiles) * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = (tile == (int)blockIdx.x ? pre : 0); kb < num_kb; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
@@ -257,6 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_
     }
   } else {
     // ---------------- epilogue warps (2..9) ----------------
+    grid_dependency_wait();                    // activation scales / zero points come from the preceding kernel
     const int et = threadIdx.x - 64;           // 0..255
     const int quarter = warp & 3;              // TMEM lanes this warp may read: 32*quarter ..
     const int parity = (warp - 2) >> 2;        // which 32-column chunks this warp takes
@@ -369,7 +389,7 @@ int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, 
   const int tiles = q.m_tiles * q.n_tiles;
   const int sms = sm_count();
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));
-  kern<<<grid, kThreads, L::kTotal, st>>>(ta, tb, q);
+  ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, ta, tb, q));
   return launch_status("int8_tcgen05_kernel");
 }
 
