@@ -181,7 +181,8 @@ def test_post_ops(capi, name, algo_name):
 def test_tcgen05_kernel(capi, tile, asym, scale_dtype):
     # K = 128, 320, 448: packed-weight chunks of four k-blocks that end in a partial chunk
     for (m, k, n, gs) in ((17, 256, 128, 128), (100, 512, 200, 64), (300, 1024, 136, 128), (64, 128, 8, 32),
-                          (257, 2048, 384, 2048), (40, 320, 72, 32), (129, 448, 260, 64)):
+                          (257, 2048, 384, 2048), (40, 320, 72, 32), (129, 448, 260, 64),
+                          (64, 1024, 256, 128), (200, 2048, 136, 64)):   # few tiles, long K: split over K when tile == 0
         x, q, s, z, b = make_woq_case(m, k, n, gs, seed=m + n, asym=asym, scale_dtype=scale_dtype)
         algo = capi.ZT_ALGO_TCGEN05 | (tile << 8)
         y, packed = _run(capi, x, q, s, z, b, algo)

@@ -183,8 +183,10 @@ extern "C" size_t zt_woq_linear_workspace_bytes(int64_t M, int64_t N, int64_t K)
   const size_t a = woq_skinny_plan(M, N, K).partial_bytes;
   const size_t b = woq_stream_plan(M < 16 ? M : 16, N, K).partial_bytes;
   const size_t c = woq_streamk_workspace_bytes();
-  const size_t m = a > b ? a : b;
-  return ZT_WOQ_COUNTER_BYTES + (m > c ? m : c);
+  const size_t d = woq_tcgen05_workspace_bytes(M, N, K);
+  size_t m = a > b ? a : b;
+  m = m > c ? m : c;
+  return ZT_WOQ_COUNTER_BYTES + (m > d ? m : d);
 }
 
 extern "C" int zt_woq_linear(const zt_woq_linear_args_t *a, void *stream) {
@@ -210,10 +212,6 @@ extern "C" int zt_woq_linear(const zt_woq_linear_args_t *a, void *stream) {
     // per-element dequantisation rounds exactly like the reference's test oracle.
     const bool tiny = a->N * a->K < (1 << 18);
     if (stream_ok && !tiny)
-      algo = ZT_ALGO_SKINNY;
-    else if (a->M <= 32 && a->N <= 8192 && !tiny && woq_skinny_supported(*a))
-      // 17..32 tokens on a layer with few 128-column tiles: the tensor-core kernel would run its whole K loop
-      // on 8..64 SMs, the mma.sync kernel splits K over all of them (measured 2x..4x faster there)
       algo = ZT_ALGO_SKINNY;
     else if (woq_tcgen05_supported(*a))
       algo = ZT_ALGO_TCGEN05;

@@ -37,6 +37,7 @@ int woq_skinny_launch(const zt_woq_linear_args_t &a, bool fold, cudaStream_t st)
 
 int woq_generic_launch(const zt_woq_linear_args_t &a, cudaStream_t st);
 
+size_t woq_tcgen05_workspace_bytes(int64_t M, int64_t N, int64_t K);  // fp32 partial sums of its split-K form
 bool woq_tcgen05_supported(const zt_woq_linear_args_t &a);
 int woq_tcgen05_launch(const zt_woq_linear_args_t &a, cudaStream_t st);
 int woq_tcgen05_grouped_launch(const void *x, int64_t total_rows, int64_t N, int64_t K, const int32_t *wq,

@@ -75,14 +75,23 @@ struct TcParams {
   const int *g_count;     // number of row tiles
   const int4 *g_tiles;    // per row tile: {expert, first row, valid rows, 0}
   long long s_estride;    // elements between two experts' scale tables
+  // split K (dense mode, layers with fewer tiles than SMs): every tile is cut into ksplit work items of kps
+  // k-blocks each (kps a multiple of the packed chunk, ksplit * kps = K / 64); the items write fp32 partial
+  // sums [ksplit][M][N] that a second kernel adds.  ksplit = 1: kps = K / 64, partial unused.
+  int ksplit, kps;
+  float *partial;
 };
 
 struct TileInfo {
   int m0, rows, n0, expert;
+  int kb0, ks;   // first k-block and index of the K slice (0, 0 without split K)
 };
 
 __device__ __forceinline__ TileInfo decode_tile(const TcParams &p, int tile, int n_mt, int bt) {
   TileInfo t;
+  t.ks = p.ksplit > 1 ? tile % p.ksplit : 0;
+  t.kb0 = t.ks * p.kps;
+  if (p.ksplit > 1) tile /= p.ksplit;
   const int mt = tile % n_mt;
   t.n0 = (tile / n_mt) * kBN;
   if (p.g_count) {
@@ -153,6 +162,35 @@ struct DqRegs {
   float s, z;
 };
 
+// Adds the K slices of a split-K run: y = post_ops(sum_s partial[s] + bias), four columns per thread.
+__global__ void __launch_bounds__(256) woq_splitk_reduce_kernel(const float *__restrict__ partial, int ksplit, int M, int N,
+                                                                const void *__restrict__ bias, int bias_dtype,
+                                                                PostOpsDev post, __nv_bfloat16 *__restrict__ y) {
+  const int64_t quad = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // N % 4 == 0 here
+  const int64_t base = quad * 4;
+  if (base >= (int64_t)M * N) return;
+  const int n = (int)(base % N);
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < ksplit; ++s) {
+    const float4 t = __ldcg(reinterpret_cast<const float4 *>(partial + (int64_t)s * M * N + base));
+    v[0] += t.x;
+    v[1] += t.y;
+    v[2] += t.z;
+    v[3] += t.w;
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    if (bias) v[e] += load_as_float(bias, n + e, bias_dtype);
+    v[e] = apply_post_ops(v[e], post, base + e, ZT_BF16);
+  }
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
+  __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 o;
+  o.x = *reinterpret_cast<uint32_t *>(&lo);
+  o.y = *reinterpret_cast<uint32_t *>(&hi);
+  *reinterpret_cast<uint2 *>(y + base) = o;
+}
+
 template <int BT, int STAGES, int PSTAGES, bool ASYM>
 __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                   const __grid_constant__ CUtensorMap tmap_w,
@@ -173,10 +211,10 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
 
   constexpr uint32_t kTmemCols = 2 * BT <= 32 ? 32 : 2 * BT <= 64 ? 64 : 2 * BT <= 128 ? 128 : 2 * BT <= 256 ? 256 : 512;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_kb = p.K / kBK;
+  const int num_kb = p.kps;   // k-blocks per work item (all of K unless the host split it)
   const int num_chunks = (num_kb + kChunkKB - 1) / kChunkKB;
   const int n_mt = p.g_count ? *p.g_count : p.m_tiles;
-  const int total_tiles = n_mt * p.n_tiles;
+  const int total_tiles = n_mt * p.n_tiles * p.ksplit;   // work items
 
   if (threadIdx.x == 0) {
     tc::prefetch_tensormap(&tmap_x);
@@ -232,7 +270,8 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
         const TileInfo t = decode_tile(p, ptile, n_mt, BT);
         tc::mbar_expect_tx(&full_p[ps], kChunkBytes);
         // rows of the stacked weight: expert * N + n0 ; 32 words (four k-blocks) per row
-        tc::tma_load_2d(packed + ps * kChunkBytes, &tmap_w, &full_p[ps], pchunk * (kChunkKB * 8), t.expert * p.N + t.n0);
+        tc::tma_load_2d(packed + ps * kChunkBytes, &tmap_w, &full_p[ps], (t.kb0 / kChunkKB + pchunk) * (kChunkKB * 8),
+                        t.expert * p.N + t.n0);
         ++pit;
         if (++pchunk == num_chunks) {
           pchunk = 0;
@@ -256,7 +295,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
             break;
           }
           tc::mbar_expect_tx(&full_x[s], L::kXBytes);
-          tc::tma_load_2d(smem + s * L::kStageBytes + L::kWBytes, &tmap_x, &full_x[s], kb * kBK, t.m0);
+          tc::tma_load_2d(smem + s * L::kStageBytes + L::kWBytes, &tmap_x, &full_x[s], (t.kb0 + kb) * kBK, t.m0);
         }
       }
     }
@@ -313,16 +352,18 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
     DqRegs ring[kPrefetch];
     int ftile = blockIdx.x, fkb = 0;  // next (tile, k-block) to fetch
     int64_t fbase = 0;                // expert offset + column of the fetch cursor's tile
+    int fkb0 = 0;                     // first k-block of the fetch cursor's work item
     auto set_fetch_tile = [&]() {
       if (ftile < total_tiles) {
         const TileInfo t = decode_tile(p, ftile, n_mt, BT);
         fbase = (int64_t)t.expert * p.s_estride + min(t.n0 + row, p.N - 1);
+        fkb0 = t.kb0;
       }
     };
     set_fetch_tile();
     auto fetch_next = [&](DqRegs &slot) {
       if (ftile < total_tiles) {
-        const int k = fkb * kBK + 32 * half;
+        const int k = (fkb0 + fkb) * kBK + 32 * half;
         const int g = gs_shift >= 0 ? (k >> gs_shift) : (k / p.gs);
         const int64_t gi = fbase + (int64_t)g * p.N;
         slot.s = load_as_float(p.scales, gi, p.scale_dtype);
@@ -479,7 +520,20 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
           const int j = pass * 4 + sub_row;
           const int m = m0 + c + j;
           const float4 v4 = *reinterpret_cast<const float4 *>(&scratch[j * kEpiRowStride + col4]);
-          if (m < m_end && nq + col4 < p.N) {
+          if (p.ksplit > 1) {
+            // split K: raw fp32 sums of this K slice; bias and post-ops belong to the kernel that adds the slices
+            if (m < m_end) {
+              float *dst = p.partial + ((int64_t)ti.ks * p.M + m) * p.N + nq + col4;
+              if (nq + col4 + 4 <= p.N && (p.N & 3) == 0) {
+                *reinterpret_cast<float4 *>(dst) = v4;
+              } else {
+                const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (nq + col4 + e < p.N) dst[e] = v[e];
+              }
+            }
+          } else if (m < m_end && nq + col4 < p.N) {
             float v[4] = {v4.x + bias4[0], v4.y + bias4[1], v4.z + bias4[2], v4.w + bias4[3]};
             const int64_t base = (int64_t)m * p.N + nq + col4;
             if (p.post.n_ops > 0) {
@@ -567,7 +621,7 @@ int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows,
   rc = cached_map(&tw, p.wq, CU_TENSOR_MAP_DATA_TYPE_UINT32, (uint64_t)p.K / 8, (uint64_t)w_rows, (uint64_t)p.K / 2,
                   kChunkKB * 8, kBN);
   if (rc != ZT_SUCCESS) return rc;
-  const long long tiles = (long long)(p.g_count ? max_row_tiles : p.m_tiles) * p.n_tiles;
+  const long long tiles = (long long)(p.g_count ? max_row_tiles : p.m_tiles) * p.n_tiles * p.ksplit;
   const int sms = sm_count();
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   if (asym) {
@@ -605,6 +659,28 @@ int launch_any(int bt, const TcParams &p, const void *x, int64_t x_rows, int64_t
 
 }  // namespace
 
+// Split-K plan of the dense mode: the largest number of equal K slices (each a multiple of the packed chunk) that keeps tiles x slices within one round of the SMs.  1 = no split.
+int woq_tcgen05_ksplit(int64_t M, int64_t N, int64_t K) {
+  if (M > 256 || (N & 3) != 0 || K % kBK != 0) return 1;
+  const int bt = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  const int64_t tiles = ceil_div<int64_t>(M, bt) * ceil_div<int64_t>(N, kBN);
+  const int64_t num_kb = K / kBK;
+  const int sms = sm_count();
+  int best = 1;
+  for (int ks = 2; ks <= 32; ++ks) {
+    if (tiles * ks > sms) break;
+    if (num_kb % ks != 0) continue;
+    const int64_t kps = num_kb / ks;
+    if (kps % kChunkKB != 0) continue;
+    best = ks;
+  }
+  return best;
+}
+size_t woq_tcgen05_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  const int ks = woq_tcgen05_ksplit(M, N, K);
+  return ks > 1 ? (size_t)ks * M * N * sizeof(float) : 0;
+}
+
 bool woq_tcgen05_supported(const zt_woq_linear_args_t &a) {
   if (a.M < 1 || a.N < 1 || a.K < kBK || a.K % kBK != 0) return false;
   if (a.n_groups <= 0 || a.K % a.n_groups != 0) return false;
@@ -632,8 +708,25 @@ int woq_tcgen05_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   p.status = device_status_ptr();
   const bool asym = a.zeros != nullptr;
   int bt = (a.algo >> 8) & 0xffff;
-  if (bt == 0) bt = a.M <= 32 ? 32 : a.M <= 64 ? 64 : a.M <= 128 ? 128 : 256;
-  return launch_any(bt, p, a.x, a.M, a.N, 0, asym, st);
+  p.ksplit = 1;
+  p.kps = (int)(a.K / kBK);
+  if (bt == 0) {
+    bt = a.M <= 32 ? 32 : a.M <= 64 ? 64 : a.M <= 128 ? 128 : 256;
+    // few tiles: split K over the idle SMs when the caller's workspace has room for the partial sums
+    const int ks = woq_tcgen05_ksplit(a.M, a.N, a.K);
+    const size_t need = ZT_WOQ_COUNTER_BYTES + (size_t)ks * a.M * a.N * sizeof(float);
+    if (ks > 1 && a.workspace != nullptr && a.workspace_bytes >= need) {
+      p.ksplit = ks;
+      p.kps = (int)(a.K / kBK / ks);
+      p.partial = reinterpret_cast<float *>(reinterpret_cast<char *>(a.workspace) + ZT_WOQ_COUNTER_BYTES);
+    }
+  }
+  int rc = launch_any(bt, p, a.x, a.M, a.N, 0, asym, st);
+  if (rc != ZT_SUCCESS || p.ksplit == 1) return rc;
+  const int64_t quads = a.M * a.N / 4;
+  woq_splitk_reduce_kernel<<<(unsigned)ceil_div<int64_t>(quads, 256), 256, 0, st>>>(p.partial, p.ksplit, p.M, p.N, p.bias,
+                                                                                      p.bias_dtype, p.post, p.y);
+  return launch_status("woq_splitk_reduce_kernel");
 }
 
 // Grouped form for mixture-of-experts: `x` holds `total_rows` rows sorted by expert; `tiles` / `tile_count`
@@ -654,6 +747,8 @@ int woq_tcgen05_grouped_launch(const void *x, int64_t total_rows, int64_t N, int
   p.bias_dtype = ZT_BF16;
   p.y = reinterpret_cast<__nv_bfloat16 *>(y);
   p.status = device_status_ptr();
+  p.ksplit = 1;
+  p.kps = (int)(K / kBK);
   p.g_count = tile_count;
   p.g_tiles = tiles;
   p.s_estride = n_groups * N;
