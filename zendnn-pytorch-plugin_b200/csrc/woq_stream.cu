@@ -373,9 +373,12 @@ WoqStreamPlan woq_stream_plan(int64_t M, int64_t N, int64_t K) {
   WoqStreamPlan pl{};
   pl.mt = M <= 8 ? 1 : 2;
   const int64_t sms = sm_count();
+  // Wide CTAs (64 columns) re-read the activations least and measured fastest wherever column tiles x K
+  // slices still give every other SM a CTA; narrower ones only for layers too small for that.
+  const int64_t max_split0 = K / 512 > 0 ? K / 512 : 1;
   int cfg = 0;
-  if (ceil_div<int64_t>(N, 64) * ceil_div<int64_t>(K, 4096) >= 2 * sms) cfg = 2;
-  else if (ceil_div<int64_t>(N, 32) >= 2 * sms) cfg = 1;
+  if (ceil_div<int64_t>(N, 64) * max_split0 >= sms / 2) cfg = 2;
+  else if (ceil_div<int64_t>(N, 32) * max_split0 >= sms / 2) cfg = 1;
   const char *force = std::getenv("ZENTORCH_B200_WOQ_STREAM_CFG");
   if (force && *force) cfg = std::atoi(force) < 0 ? 0 : std::atoi(force) > 2 ? 2 : std::atoi(force);
   pl.r = cfg;  // kernel shape index (see Shape<>)
