@@ -342,8 +342,8 @@ def bench_woq_case(torch, _capi, lib, dev, stream, sptr, steps, pk, m, k, n, lab
            "launch": "CUDA graph, back-to-back"}
     if m <= 16:
         gbs = alg_bytes / (ms * 1e-3) / 1e9
-        # the dispatcher's rule: TMA-staged stream-K kernel from 24 MB of packed weights, register ring below
-        kernel = "woq_streamk_kernel" if n * k // 2 >= (24 << 20) else "woq_stream_kernel"
+        # the dispatcher's rule: TMA-staged stream-K kernel from 48 MB of packed weights, register ring below
+        kernel = "woq_streamk_kernel" if n * k // 2 >= (48 << 20) else "woq_stream_kernel"
         out.update({"kernel": kernel, "bound": "hbm", "algorithmic_bytes": alg_bytes, "achieved": round(gbs, 1),
                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / pk["hbm_gbs"], 4),
                     "peak_note": f"STREAM-style copy, {pk['source']}"})

@@ -224,10 +224,10 @@ extern "C" int zt_woq_linear(const zt_woq_linear_args_t *a, void *stream) {
     case ZT_ALGO_GENERIC: return woq_generic_launch(*a, st);
     case ZT_ALGO_SKINNY:
       // Two decode kernels: the work-balanced TMA-staged one streams faster but has a longer fixed
-      // latency (cross-CTA reduction), so it takes the layers with at least 24 MB of packed weights.
+      // latency (cross-CTA reduction), so it takes the layers with at least 48 MB of packed weights (at 30 MB the two measured equal).
       // Tile hint 1 forces the register-ring kernel, 2 the stream-K kernel (tests, benchmarks).
       if (((a->algo >> 8) & 0xffff) != 1 &&
-          ((env().woq_streamk && a->N * a->K / 2 >= (24 << 20)) || ((a->algo >> 8) & 0xffff) == 2) &&
+          ((env().woq_streamk && a->N * a->K / 2 >= (48 << 20)) || ((a->algo >> 8) & 0xffff) == 2) &&
           woq_streamk_supported(*a) &&
           a->workspace_bytes >= ZT_WOQ_COUNTER_BYTES + woq_streamk_workspace_bytes())
         return woq_streamk_launch(*a, st);
