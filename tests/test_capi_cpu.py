@@ -58,6 +58,11 @@ def test_argument_validation_precedes_device_work(zt):
     assert b"input must be bfloat16 or float32" in lib.zt_last_error()
     assert lib.zt_woq_linear_workspace_bytes(1, 4096, 4096) >= _capi.ZT_WOQ_COUNTER_BYTES
     assert lib.zt_dynamic_qlinear_workspace_bytes(512, 4096) >= 512 * 4096 + 2 * 512 * 4
+    # decode batches on a layer with few 128-column tiles are split over K: room for the fp32 partial sums
+    # (32 tiles on a 148-SM part -> 4 slices), none when the tiles already cover the SMs or M is large
+    base = lib.zt_woq_linear_workspace_bytes(1, 4096, 4096)
+    assert lib.zt_woq_linear_workspace_bytes(64, 4096, 4096) >= _capi.ZT_WOQ_COUNTER_BYTES + 2 * 64 * 4096 * 4
+    assert lib.zt_woq_linear_workspace_bytes(2048, 4096, 4096) <= max(base, lib.zt_woq_linear_workspace_bytes(64, 4096, 4096))
 
 
 def test_schemas_match_the_reference(zt):
