@@ -268,6 +268,7 @@ def run_ours(args):
                 "unit": "TOP/s", "frac": round(OPS_PER_CALL / (ms_gemm * 1e-3) / 1e12 / int8_peak, 4),
                 "peak_note": f"2 x cuBLAS bf16 burst ({pk['bf16_tflops']} TF/s, {pk['source']}): kind::i8 issues at "
                              "twice the kind::f16 rate",
+                "frac_of_sustained_peak": round(OPS_PER_CALL / (ms_gemm * 1e-3) / 1e12 / (2.0 * pk["bf16_tflops_sustained"]), 4),
                 "traffic": None,
             },
             "woq_decode": woq.get("woq_decode"), "woq_decode_large_layer": woq.get("woq_decode_large_layer"),
