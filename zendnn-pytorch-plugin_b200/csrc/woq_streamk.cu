@@ -52,10 +52,10 @@ namespace {
 constexpr int kTileN = 64;        // output columns per cell
 constexpr int kStepK = 128;       // k per cell
 constexpr int kComputeWarps = 16;
-// Warps: 16 compute, weight producer, activation producer, epilogue, converters -- five converters when the
-// B operand is one 8-column block (24 warps, 80 registers), two otherwise (21 warps, 96 registers).
-__host__ __device__ constexpr int conv_warps(int nb) { return nb == 1 ? 5 : 2; }
-__host__ __device__ constexpr int sk_threads(int nb) { return 32 * (kComputeWarps + 3 + conv_warps(nb)); }
+// Warps: 16 compute, weight producer, activation producer, epilogue, converters -- five converters up to two
+// tokens (24 warps; a chunk needs one or two of them, so the groups take chunks in turn), eight for three and
+// four tokens (27 warps: still two groups).
+__host__ __device__ constexpr int sk_threads(int conv_warps) { return 32 * (kComputeWarps + 3 + conv_warps); }
 constexpr int kMaxStages = 8;   // weight stages and activation slots, each
 constexpr int kRedStride = 33;
 constexpr int kMaxTokens = 4;
@@ -158,8 +158,8 @@ struct ChunkIter {
   }
 };
 
-template <int NB, bool ASYM, bool SF32>
-__global__ void __launch_bounds__(sk_threads(NB), 1)
+template <int NB, int CW, bool ASYM, bool SF32>
+__global__ void __launch_bounds__(sk_threads(CW), 1)
     woq_streamk_kernel(const __grid_constant__ CUtensorMap map_w8, const __grid_constant__ CUtensorMap map_x8,
                        const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_z,
                        const SKParams p) {
@@ -168,8 +168,8 @@ __global__ void __launch_bounds__(sk_threads(NB), 1)
   constexpr int CS = chunk_steps(NB);         // cells per chunk
   constexpr int R = row_blocks(NB);           // 16-row blocks per compute warp
   constexpr int kWarpsPerCell = kComputeWarps / CS;
-  constexpr int kConvWarps = conv_warps(NB);
-  constexpr int kThreads = sk_threads(NB);
+  constexpr int kConvWarps = CW;
+  constexpr int kThreads = sk_threads(CW);
   constexpr int kWRowBytes = CS * 64;         // one weight row of a stage: [CS cells][64 B]
   constexpr int kWBytes = kTileN * kWRowBytes;
   constexpr int kXRowBytes = CS * 256;        // one activation row of a slot: [CS cells][256 B]
@@ -813,25 +813,25 @@ int build_maps(const zt_woq_linear_args_t &a, int mrows, uint32_t cs, Maps &m) {
   return ZT_SUCCESS;
 }
 
-template <int NB, bool ASYM, bool SF32>
+template <int NB, int CW, bool ASYM, bool SF32>
 int launch(const Maps &m, const SKParams &p, int grid, size_t smem_bytes, cudaStream_t st) {
-  auto kern = woq_streamk_kernel<NB, ASYM, SF32>;
+  auto kern = woq_streamk_kernel<NB, CW, ASYM, SF32>;
   static bool configured = false;
   if (!configured) {
     ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     configured = true;
   }
-  ZT_CUDA_OK(launch_overlapped(kern, dim3((unsigned)grid), dim3((unsigned)sk_threads(NB)), smem_bytes, st, m.w8, m.x8, m.s,
+  ZT_CUDA_OK(launch_overlapped(kern, dim3((unsigned)grid), dim3((unsigned)sk_threads(CW)), smem_bytes, st, m.w8, m.x8, m.s,
                                m.z, p));
   return launch_status("woq_streamk_kernel");
 }
 
-template <int NB>
+template <int NB, int CW>
 int launch_q(const Maps &m, const SKParams &p, int grid, size_t smem_bytes, cudaStream_t st) {
   const bool asym = p.zeros != nullptr, sf32 = p.scale_dtype == ZT_F32;
   if (asym)
-    return sf32 ? launch<NB, true, true>(m, p, grid, smem_bytes, st) : launch<NB, true, false>(m, p, grid, smem_bytes, st);
-  return sf32 ? launch<NB, false, true>(m, p, grid, smem_bytes, st) : launch<NB, false, false>(m, p, grid, smem_bytes, st);
+    return sf32 ? launch<NB, CW, true, true>(m, p, grid, smem_bytes, st) : launch<NB, CW, true, false>(m, p, grid, smem_bytes, st);
+  return sf32 ? launch<NB, CW, false, true>(m, p, grid, smem_bytes, st) : launch<NB, CW, false, false>(m, p, grid, smem_bytes, st);
 }
 
 }  // namespace
@@ -903,7 +903,7 @@ int woq_streamk_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   int rc = build_maps(a, (int)a.M, (uint32_t)chunk_steps(nb), maps);
   if (rc != ZT_SUCCESS) return rc;
   ZT_REQUIRE(nb == 1, ZT_UNSUPPORTED, "zt_woq_linear: the stream-K kernel takes at most %d tokens", kMaxTokens);
-  return launch_q<1>(maps, p, grid, smem_bytes, st);
+  return a.M <= 2 ? launch_q<1, 5>(maps, p, grid, smem_bytes, st) : launch_q<1, 8>(maps, p, grid, smem_bytes, st);
 }
 
 }  // namespace zt
