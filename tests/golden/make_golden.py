@@ -1,8 +1,8 @@
 """Generates tests/golden/zentorch_golden.npz from the reference's own Python test utilities.
 
-Run once in a container that has the reference tree (default /root/reference, override with
-ZENTORCH_REFERENCE_ROOT); the resulting file is committed and is what the test-suite reads -- the
-reference tree is not needed at test time.
+Run once where a checkout of the reference (amd/ZenDNN-pytorch-plugin) is available, with
+ZENTORCH_REFERENCE_ROOT pointing at it; the resulting file is committed and is what the test-suite
+reads -- the reference tree is not needed at test time.
 
 Sources of truth used here (none of them is our code):
   * test/unittests/op_tests/_pack.py           -- the reference's independent int4 packer
@@ -20,7 +20,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(os.environ.get("ZENTORCH_REFERENCE_ROOT", "/root/reference"))
+if "ZENTORCH_REFERENCE_ROOT" not in os.environ:
+    raise SystemExit("set ZENTORCH_REFERENCE_ROOT to a checkout of amd/ZenDNN-pytorch-plugin")
+REF = Path(os.environ["ZENTORCH_REFERENCE_ROOT"])
 OUT = Path(__file__).resolve().parent / "zentorch_golden.npz"
 
 

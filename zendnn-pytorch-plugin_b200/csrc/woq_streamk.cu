@@ -884,12 +884,12 @@ int woq_streamk_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   const size_t stage = streamk_stage_bytes((int)a.M, a.zeros != nullptr);
   const size_t xslot = streamk_xslot_bytes((int)a.M, a.zeros != nullptr);
   const size_t tail = streamk_tail_bytes((int)a.M);
-  const size_t budget = 226 * 1024 - tail;
+  const size_t avail = 226 * 1024 - tail;   // dynamic shared memory left for the two rings
   // Activation slots are small and let the conversion run ahead of the weights: six of them for up to two
   // tokens, four up to four, three beyond; fewer when that buys no weight stage less than three.
   int xslots = a.M <= 2 ? 6 : a.M <= 4 ? 4 : 3;
-  while (xslots > 2 && (budget - xslots * xslot) / stage < 3) --xslots;
-  int stages = (int)((budget - xslots * xslot) / stage);
+  while (xslots > 2 && (avail - xslots * xslot) / stage < 3) --xslots;
+  int stages = (int)((avail - xslots * xslot) / stage);
   if (stages > kMaxStages) stages = kMaxStages;
   ZT_REQUIRE(stages >= 2, ZT_UNSUPPORTED, "zt_woq_linear: stream-K stage of %zu bytes does not fit twice", stage);
   p.stages = stages;
