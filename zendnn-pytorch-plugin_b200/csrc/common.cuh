@@ -66,6 +66,27 @@ inline cudaError_t launch_overlapped(Kernel kern, dim3 grid, dim3 block, size_t 
   cfg.numAttrs = overlap_launches() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, args...);
 }
+
+// The same, as thread-block clusters of `cluster` CTAs (the cluster spans the grid's y dimension).
+template <typename Kernel, typename... Args>
+inline cudaError_t launch_overlapped_cluster(Kernel kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                             unsigned cluster_y, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = cluster_y;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_launches() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
 #endif
 
 // ---- post-op chain ----------------------------------------------------------------------------

@@ -51,6 +51,8 @@ struct StreamParams {
   int nsplit;
   int scale_dtype, bias_dtype;
   int early_trigger;  // the grid is resident at once: let the next kernel in at entry rather than after the main loop
+  int cluster;        // the K slices of a column tile are one thread-block cluster: reduce through its shared memory
+  int cluster_off;    // byte offset of the cluster reduction buffer [nsplit][M][columns] in dynamic shared memory
   PostOpsDev post;
 };
 
@@ -288,7 +290,23 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   constexpr int kRowsPerPass = kThreads / kTileN;
   const int nl = tid % kTileN;
   const int n = n0 + nl;
-  if (p.nsplit > 1) {
+  float *cl = reinterpret_cast<float *>(smem_raw + p.cluster_off);   // [nsplit][M][kTileN], used in the first CTA
+  if (p.nsplit > 1 && p.cluster) {
+    // K slices of this column tile form a cluster (rank = slice): every CTA puts its sums into the first
+    // CTA's shared memory, which adds them in slice order after the cluster barrier -- no global round trip.
+    for (int ml = tid / kTileN; ml < p.M; ml += kRowsPerPass) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < W; ++w) v += red[(w * kCols + ml) * kRedStride + nl];
+      const uint32_t local = smem_u32(cl + ((size_t)split * p.M + ml) * kTileN + nl);
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0));
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (split != 0) return;
+  } else if (p.nsplit > 1) {
     for (int ml = tid / kTileN; ml < p.M; ml += kRowsPerPass) {
       float v = 0.f;
 #pragma unroll
@@ -306,7 +324,9 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   for (int ml = tid / kTileN; ml < p.M; ml += kRowsPerPass) {
     if (n >= p.N) continue;
     float v = 0.f;
-    if (p.nsplit > 1) {
+    if (p.nsplit > 1 && p.cluster) {
+      for (int s = 0; s < p.nsplit; ++s) v += cl[((size_t)s * p.M + ml) * kTileN + nl];
+    } else if (p.nsplit > 1) {
       for (int s = 0; s < p.nsplit; ++s) v += __ldcg(&p.partial[((size_t)s * p.M + ml) * p.N + n]);
     } else {
 #pragma unroll
@@ -347,14 +367,26 @@ int launch(const StreamParams &p_in, dim3 grid, cudaStream_t st) {
     ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
     configured = true;
   }
-  const size_t smem = stream_smem_bytes<MT, CFG>(p_in.M);
+  // clusters of up to eight K slices (the portable cluster size) reduce through shared memory
+  static const bool use_clusters = [] {
+    const char *e = std::getenv("ZENTORCH_B200_WOQ_CLUSTER");
+    return !(e && e[0] == '0');
+  }();
+  const bool cluster = use_clusters && p_in.nsplit >= 2 && p_in.nsplit <= 8 && (int)grid.y == p_in.nsplit;
+  const size_t base_smem = (stream_smem_bytes<MT, CFG>(p_in.M) + 15) / 16 * 16;
+  const size_t smem = base_smem + (cluster ? (size_t)p_in.nsplit * p_in.M * (16 * S::R) * sizeof(float) : 0);
   static int per_sm_for_m[17] = {0};   // resident CTAs per SM; the dynamic shared memory depends on M only
   int &per_sm = per_sm_for_m[p_in.M];
   if (per_sm == 0) ZT_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, S::W * 32, smem));
   StreamParams p = p_in;
+  p.cluster = cluster ? 1 : 0;
+  p.cluster_off = (int)base_smem;
   // half the resident capacity at most: the next kernel's CTAs then find room beside this grid's
   p.early_trigger = (long long)grid.x * grid.y * 2 <= (long long)per_sm * sm_count() ? 1 : 0;
-  ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(S::W * 32), smem, st, p));
+  if (cluster)
+    ZT_CUDA_OK(launch_overlapped_cluster(kern, grid, dim3(S::W * 32), smem, st, (unsigned)p.nsplit, p));
+  else
+    ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(S::W * 32), smem, st, p));
   return launch_status("woq_stream_kernel");
 }
 
