@@ -121,13 +121,14 @@ def test_skinny_quant_modes(capi, asym, scale_dtype, k, gs, n):
 
 
 @pytest.mark.parametrize("cfg", [0, 1, 2])
-@pytest.mark.parametrize("m", [1, 7, 13])
+@pytest.mark.parametrize("m", [1, 7, 13, 16])
 def test_stream_kernel_shapes(capi, cfg, m, monkeypatch):
     """Every compiled shape of the decode kernel (16 / 32 / 64 columns per CTA), with and without a
     K split across CTAs, ragged N, a K that is not a multiple of the activation chunk."""
     monkeypatch.setenv("ZENTORCH_B200_WOQ_STREAM_CFG", str(cfg))
     for (k, n, gs, asym, sdt) in ((4096, 200, 128, False, torch.float32), (1152, 1000, 128, True, torch.bfloat16),
-                                  (8192, 72, 256, False, torch.bfloat16), (2048, 4100, 128, True, torch.float32)):
+                                  (8192, 72, 256, False, torch.bfloat16), (2048, 4100, 128, True, torch.float32),
+                                  (4096, 1024, 128, False, torch.float32)):   # eight K slices in one cluster
         x, q, s, z, b = make_woq_case(m, k, n, gs, seed=cfg * 100 + m, asym=asym, scale_dtype=sdt)
         y, packed = _run(capi, x, q, s, z, b, capi.ZT_ALGO_SKINNY | (1 << 8))   # hint 1: register-ring kernel
         assert_close_bf16(y, O.woq_linear(x, packed.t(), s, z, b), what=f"cfg {cfg} M={m} K={k} N={n}")
