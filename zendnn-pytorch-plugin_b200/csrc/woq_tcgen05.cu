@@ -166,6 +166,8 @@ struct DqRegs {
 __global__ void __launch_bounds__(256) woq_splitk_reduce_kernel(const float *__restrict__ partial, int ksplit, int M, int N,
                                                                 const void *__restrict__ bias, int bias_dtype,
                                                                 PostOpsDev post, __nv_bfloat16 *__restrict__ y) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t quad = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // N % 4 == 0 here
   const int64_t base = quad * 4;
   if (base >= (int64_t)M * N) return;
@@ -211,6 +213,10 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
 
   constexpr uint32_t kTmemCols = 2 * BT <= 32 ? 32 : 2 * BT <= 64 ? 64 : 2 * BT <= 128 ? 128 : 2 * BT <= 256 ? 256 : 512;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Programmatic dependent launch: packed weights and scales are read before the wait for the preceding
+  // kernel, activations, partial sums and output after it.  The grouped form reads its tile list (made by the
+  // routing kernels before it) at once, so it waits first.
+  if (p.g_count) grid_dependency_wait();
   const int num_kb = p.kps;   // k-blocks per work item (all of K unless the host split it)
   const int num_chunks = (num_kb + kChunkKB - 1) / kChunkKB;
   const int n_mt = p.g_count ? *p.g_count : p.m_tiles;
@@ -239,6 +245,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ---------------- TMA producer: packed-weight chunks (running ahead) and activation tiles ----------------
@@ -279,6 +286,10 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
         }
         return true;
       };
+      // the packed ring fills before the wait for the preceding kernel, the activation tiles follow it
+      while (issue_packed(false)) {
+      }
+      grid_dependency_wait();
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const TileInfo t = decode_tile(p, tile, n_mt, BT);
         for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
@@ -478,6 +489,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
     }
   } else {
     // ---------------- epilogue warps ----------------
+    grid_dependency_wait();                // output, partial sums and post-op operands are shared with earlier work
     const int ew = warp - (2 + kDqWarps);  // 0..3
     const int quarter = warp & 3;          // TMEM lanes 32*quarter .. +31
     float *scratch = epi_scratch + ew * 32 * kEpiRowStride;
@@ -631,7 +643,7 @@ int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows,
       ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
       configured = true;
     }
-    kern<<<grid, kThreads, L::kTotal, st>>>(tx, tw, p);
+    ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, p));
   } else {
     auto kern = woq_tcgen05_kernel<BT, STAGES, PSTAGES, false>;
     static bool configured = false;
@@ -639,7 +651,7 @@ int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows,
       ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
       configured = true;
     }
-    kern<<<grid, kThreads, L::kTotal, st>>>(tx, tw, p);
+    ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, p));
   }
   return launch_status("woq_tcgen05_kernel");
 }
@@ -724,8 +736,8 @@ int woq_tcgen05_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   int rc = launch_any(bt, p, a.x, a.M, a.N, 0, asym, st);
   if (rc != ZT_SUCCESS || p.ksplit == 1) return rc;
   const int64_t quads = a.M * a.N / 4;
-  woq_splitk_reduce_kernel<<<(unsigned)ceil_div<int64_t>(quads, 256), 256, 0, st>>>(p.partial, p.ksplit, p.M, p.N, p.bias,
-                                                                                      p.bias_dtype, p.post, p.y);
+  ZT_CUDA_OK(launch_overlapped(woq_splitk_reduce_kernel, dim3((unsigned)ceil_div<int64_t>(quads, 256)), dim3(256), (size_t)0, st,
+                               (const float *)p.partial, p.ksplit, p.M, p.N, p.bias, p.bias_dtype, p.post, p.y));
   return launch_status("woq_splitk_reduce_kernel");
 }
 
