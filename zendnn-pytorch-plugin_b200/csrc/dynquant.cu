@@ -32,28 +32,27 @@ __device__ __forceinline__ void load8(const void *x, int dtype, int64_t off, flo
   }
 }
 
-__device__ __forceinline__ float block_reduce(float v, bool is_max, float *scratch) {
+// Row maximum of hi and row minimum of lo over the CTA in one pass: warp shuffles, one shared-memory slot per
+// warp and value, one barrier, and every thread folds the eight warp results itself (max and min are exact, so
+// the order does not matter).
+__device__ __forceinline__ void block_reduce_max_min(float &hi, float &lo, float *scratch) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    const float other = __shfl_xor_sync(0xffffffffu, v, o);
-    v = is_max ? fmaxf(v, other) : fminf(v, other);
+    hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
   }
+  constexpr int kWarps = kThreads / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) scratch[warp] = v;
-  __syncthreads();
-  if (warp == 0) {
-    float r = lane < kThreads / 32 ? scratch[lane] : scratch[0];
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1) {
-      const float other = __shfl_xor_sync(0xffffffffu, r, o);
-      r = is_max ? fmaxf(r, other) : fminf(r, other);
-    }
-    if (lane == 0) scratch[8] = r;
+  if (lane == 0) {
+    scratch[warp] = hi;
+    scratch[kWarps + warp] = lo;
   }
   __syncthreads();
-  const float out = scratch[8];
-  __syncthreads();
-  return out;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    hi = fmaxf(hi, scratch[w]);
+    lo = fminf(lo, scratch[kWarps + w]);
+  }
 }
 
 template <bool U8>
@@ -111,10 +110,9 @@ __global__ void __launch_bounds__(kThreads) dynquant_vec_kernel(const void *__re
       }
     }
   }
-  hi = block_reduce(hi, true, scratch);
+  block_reduce_max_min(hi, lo, scratch);
   float s, zp = 0.f;
   if (U8) {
-    lo = block_reduce(lo, false, scratch);
     s = __fdiv_rn(fmaxf(hi - lo, 1e-12f), 255.0f);
     zp = fminf(fmaxf(rintf(__fdiv_rn(-lo, s)), 0.f), 255.f);
   } else {
@@ -165,10 +163,9 @@ __global__ void __launch_bounds__(kThreads) dynquant_scalar_kernel(const void *_
       hi = fmaxf(hi, fabsf(t));
     }
   }
-  hi = block_reduce(hi, true, scratch);
+  block_reduce_max_min(hi, lo, scratch);
   float s, zp = 0.f;
   if (U8) {
-    lo = block_reduce(lo, false, scratch);
     s = __fdiv_rn(fmaxf(hi - lo, 1e-12f), 255.0f);
     zp = fminf(fmaxf(rintf(__fdiv_rn(-lo, s)), 0.f), 255.f);
   } else {
