@@ -48,6 +48,17 @@ typedef enum {
 
 #define ZT_MAX_POST_OPS 4
 
+/* Argument-block flags.
+ *
+ * The linears treat weights, weight scales, zero points and row sums as constants (the reference passes
+ * is_weights_const = true to the library for the same tensors, src/cpu/cpp/WOQ_Linear.cpp:107,
+ * src/cpu/cpp/DynamicQLinear.cpp:128): kernels start fetching them while the work submitted before on the
+ * same stream may still be running, and order themselves after that work only before they touch
+ * activations, scratch and output.  ZT_FLAG_WEIGHTS_VOLATILE tells a call that one of those tensors may
+ * have been written by work submitted to the stream directly before it (a repack, a copy, a cast): every
+ * kernel of the call then starts only after all earlier work on the stream has completed. */
+#define ZT_FLAG_WEIGHTS_VOLATILE 1
+
 /* Ordered post-op chain applied to the fp32 result after the bias (matmul_post_ops,
  * src/cpu/cpp/MatmulUtils.hpp:36-77).  MUL/ADD consume `buffers` in order; each buffer is a
  * contiguous [M, N] array of the output dtype. */
@@ -78,6 +89,10 @@ ZT_API int zt_device_supported(void);
  * (0 = none; 101..104 name the waiting role).  Synchronises with the device; `reset` clears it.
  * No counterpart in the reference (its failures are host exceptions, src/cpu/cpp/Utils.hpp:21-23). */
 ZT_API int zt_poll_device_status(int *status, int reset);
+/* Exercises that path without a fault: launches a one-thread kernel whose wait on a barrier nobody
+ * signals gives up after a few thousand polls (microseconds), records status 199 and returns normally.
+ * For tests of the host-side handling; no counterpart in the reference. */
+ZT_API int zt_selftest_expire_wait(void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Weight-only int4 linear.   zentorch_woq_linear_impl, src/cpu/cpp/WOQ_Linear.cpp:14-176, and the
@@ -94,7 +109,10 @@ ZT_API int zt_poll_device_status(int *status, int reset);
  *         nibbles are unsigned (0..15) and dq = (q-8)*s + z  (WOQ_Linear.cpp:47-49).
  * x, y    bf16, row-major, leading dimensions K and N.
  * workspace  device scratch of at least zt_woq_linear_workspace_bytes(M,N,K) bytes.  Its first
- *         ZT_WOQ_COUNTER_BYTES must be zero before the first call; every call leaves them zero.
+ *         ZT_WOQ_COUNTER_BYTES must be zero before the first call; every call that completes normally
+ *         leaves them zero.  A call in which a bounded device-side wait expired (zt_poll_device_status
+ *         reports a non-zero code) may leave counters behind: zero those bytes again before the
+ *         workspace is reused, or later calls elect no finisher for the affected column tiles.
  *         Calls that share a workspace must be ordered on one stream.
  */
 #define ZT_WOQ_COUNTER_BYTES 16384
@@ -113,7 +131,8 @@ typedef struct {
   void *y;
   void *workspace;
   size_t workspace_bytes;
-  int32_t algo; /* zt_algo_t */
+  int32_t algo;  /* zt_algo_t */
+  int32_t flags; /* ZT_FLAG_* bits, 0 for constant weights */
 } zt_woq_linear_args_t;
 
 ZT_API size_t zt_woq_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
@@ -162,6 +181,7 @@ typedef struct {
   void *workspace;
   size_t workspace_bytes;
   int32_t algo;
+  int32_t flags; /* ZT_FLAG_* bits, 0 for constant weights */
 } zt_dynamic_qlinear_args_t;
 
 ZT_API size_t zt_dynamic_qlinear_workspace_bytes(int64_t M, int64_t K);

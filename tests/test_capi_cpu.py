@@ -36,6 +36,24 @@ def test_aoti_shims_exported(zt):
         assert hasattr(lib, name), name
 
 
+def test_aoti_shim_returns_an_error_code_for_host_tensors(zt):
+    """The shims never let an exception cross the C boundary: CPU tensors (no CUDA kernel would accept
+    them) come back as a non-zero AOTITorchError and *ret0 stays untouched."""
+    lib = C.CDLL(str(ROOT / "zendnn-pytorch-plugin_b200" / "lib" / "libzentorch_b200_torch.so"))
+    from _util import aoti_handle, aoti_release
+    x = torch.zeros(2, 64, dtype=torch.bfloat16)
+    w = torch.zeros(32, 8, dtype=torch.int32).t()
+    sc = torch.ones(1, 32)
+    handles = [aoti_handle(t) for t in (x, w, sc)]
+    ret = C.c_void_p(None)
+    fn = lib.aoti_torch_cuda_zentorch_woq_linear
+    fn.restype = C.c_int32
+    rc = fn(*(C.c_void_p(addr) for _, addr in handles), None, None, b"zentorch::zentorch_woq_linear", C.byref(ret))
+    assert rc != 0 and ret.value is None
+    for cap, _ in handles:
+        aoti_release(cap)
+
+
 def test_argument_validation_precedes_device_work(zt):
     from zentorch_b200 import _capi
     lib = _capi.lib()

@@ -33,6 +33,34 @@ def test_dynamic_quantize_bit_exact(capi, dtype, m, k):
     assert torch.equal(su.cpu(), su_ref) and torch.equal(zpu.cpu(), zp_ref) and torch.equal(qu.cpu(), qu_ref)
 
 
+def test_dynamic_quantize_nan_and_signed_zero(capi):
+    """A NaN makes its own row's scale NaN (the CPU formula's amax propagates it) and with it the whole output
+    row of the linear; the other rows keep their exact bytes.  A row of -0.0 quantises like a row of zeros."""
+    g = torch.Generator().manual_seed(11)
+    m, k, n = 6, 512, 48
+    x = (torch.randn(m, k, generator=g) * 2).to(torch.bfloat16)
+    x[2, 77] = float("nan")
+    x[4] = -0.0
+    w = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8)
+    ws = torch.rand(n, generator=g) * 1e-3 + 1e-4
+    for act in (capi.ZT_ACT_S8_SYM, capi.ZT_ACT_U8_ASYM):
+        q, s, zp = capi.dynamic_quantize(x.cuda(), act)
+        if act == capi.ZT_ACT_S8_SYM:
+            q_ref, s_ref = O.dynamic_quantize_s8(x)
+            zp_ref = torch.zeros(m, dtype=torch.int32)
+        else:
+            q_ref, s_ref, zp_ref = O.dynamic_quantize_u8(x)
+        assert torch.isnan(s_ref[2]) and torch.isnan(s.cpu()[2])
+        keep = [0, 1, 3, 4, 5]
+        assert torch.equal(s.cpu()[keep], s_ref[keep]) and torch.equal(q.cpu()[keep], q_ref[keep])
+        if act == capi.ZT_ACT_U8_ASYM:
+            assert torch.equal(zp.cpu()[keep], zp_ref[keep])
+        assert float(s.cpu()[4]) == float(s_ref[4]) and not torch.signbit(s.cpu()[4])
+        y = capi.dynamic_qlinear(x.cuda(), w.cuda(), ws.cuda(), None, act_quant=act).float().cpu()
+        assert torch.isnan(y[2]).all() and torch.isfinite(y[keep]).all()
+        assert (y[4] == 0).all()
+
+
 TILES = [0, 64, 96, 128, 160, 192, 224, 256, 1128, 1160, 1192, 1256]  # +1000: 256-row CTA tiles
 
 

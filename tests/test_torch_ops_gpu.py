@@ -136,3 +136,135 @@ def test_cuda_graph_capture(ops):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(y, y_eager) and torch.equal(yi, yi_eager)
+
+
+def test_arguments_on_other_devices_are_refused(ops):
+    """Every tensor argument must live on the input's GPU; a host tensor raises before anything is launched."""
+    x, q, s, z, b = make_woq_case(2, 256, 64, 128, seed=12)
+    packed = ops.zentorch_woq_repack_weight(q.cuda())
+    with pytest.raises(RuntimeError, match="weight_scales must be on the input's device"):
+        ops.zentorch_woq_linear(x.cuda(), packed.t(), s, None, b.cuda())
+    with pytest.raises(RuntimeError, match="bias must be on the input's device"):
+        ops.zentorch_woq_linear(x.cuda(), packed.t(), s.cuda(), None, b)
+    with pytest.raises(RuntimeError, match="binary post-op operand must be on the input's device"):
+        ops.zentorch_woq_linear_add(x.cuda(), packed.t(), s.cuda(), None, torch.zeros(2, 64, dtype=torch.bfloat16), b.cuda())
+    xi, wi, wsi, bi = make_int8_case(4, 64, 16, seed=13)
+    with pytest.raises(RuntimeError, match="weight must be on the input's device"):
+        ops.zentorch_dynamic_qlinear(xi.cuda(), wi, wsi.cuda(), None)
+    with pytest.raises(RuntimeError, match="weight_scales must be on the input's device"):
+        ops.zentorch_dynamic_qlinear(xi.cuda(), wi.cuda(), wsi, None)
+    torch.cuda.synchronize()
+
+
+def test_weights_fresh_every_call_through_the_ops(ops):
+    """Weights that are made right before each call (no constant folding): the boundary has not seen them
+    before, or sees a new storage at an old address, and tells the kernels not to prefetch them."""
+    m, k, n = 3, 2048, 512
+    x, q, s, z, b = make_woq_case(m, k, n, 128, seed=14)
+    ref = O.woq_linear(x, O.woq_repack_weight(q).t(), s, None, b)
+    xd, qd, s_t, bd = x.cuda(), q.cuda(), s.t().contiguous().cuda(), b.cuda()
+    junk = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+    for rep in range(10):
+        junk.random_(0, 255)
+        y = ops.zentorch_woq_linear(xd, ops.zentorch_woq_repack_weight(qd).t(), s_t.t().contiguous(), None, bd)
+        assert_close_bf16(y, ref, what=f"fresh weights rep {rep}")
+    xi, wi, wsi, bi = make_int8_case(64, 512, 256, seed=15)
+    refi = O.dynamic_qlinear(xi, wi, wsi, bi)
+    wt = wi.t().contiguous().cuda()
+    for rep in range(10):
+        junk.random_(0, 255)
+        yi = ops.zentorch_dynamic_qlinear(xi.cuda(), wt.t(), wsi.cuda(), bi.cuda())   # non-contiguous: copied in the op
+        assert_close_bf16(yi, refi, what=f"int8 fresh weights rep {rep}")
+
+
+def test_aoti_shims_compute(zt):
+    """The C shims Inductor's cpp_wrapper calls (same parameter lists as aoti_torch_cpu_zentorch_*,
+    src/cpu/cpp/shim_cpu_zentorch.hpp:150-197), called for real: borrowed input handles, nullable optional
+    handles, a new owning handle in *ret0, zero return code."""
+    import ctypes as C
+    from pathlib import Path
+    from _util import aoti_handle, aoti_release, aoti_take
+    lib = C.CDLL(str(Path(zt.__file__).resolve().parent.parent / "lib" / "libzentorch_b200_torch.so"))
+    m, k, n = 9, 512, 128
+    x, q, s, z, b = make_woq_case(m, k, n, 128, seed=16)
+    packed = torch.ops.zentorch.zentorch_woq_repack_weight(q.cuda())
+    g = torch.Generator().manual_seed(17)
+    a1 = torch.randn(m, n, generator=g).to(torch.bfloat16)
+    a2 = torch.randn(m, n, generator=g).to(torch.bfloat16)
+    pc = packed.cpu().t()
+    vp = C.c_void_p
+
+    def call(name, extra, post, bufs):
+        """X, W, scales, no zero points, the binary operands, an optional bias passed by address."""
+        hs = [aoti_handle(t) for t in (x.cuda(), packed.t(), s.cuda())]
+        hextra = [aoti_handle(t.cuda()) for t in extra]
+        hb = aoti_handle(b.cuda())
+        bias_slot, ret = vp(hb[1]), vp(None)
+        fn = getattr(lib, name)
+        fn.restype = C.c_int32
+        rc = fn(*(vp(a) for _, a in hs), None, *(vp(a) for _, a in hextra), C.byref(bias_slot), b"from_test", C.byref(ret))
+        assert rc == 0, f"{name} returned {rc}"
+        y = aoti_take(ret.value)
+        for cap, _ in hs + hextra + [hb]:
+            aoti_release(cap)
+        assert_close_bf16(y, O.woq_linear(x, pc, s, None, b, post, bufs), what=name)
+
+    call("aoti_torch_cuda_zentorch_woq_linear", [], [], [])
+    call("aoti_torch_cuda_zentorch_woq_linear_gelu_tanh", [], [O.POST_GELU_TANH], [])
+    call("aoti_torch_cuda_zentorch_woq_linear_add", [a1], [O.POST_ADD], [a1])
+    call("aoti_torch_cuda_zentorch_woq_linear_mul_add", [a1, a2], [O.POST_MUL, O.POST_ADD], [a1, a2])
+    call("aoti_torch_cuda_zentorch_woq_linear_add_add", [a1, a2], [O.POST_ADD, O.POST_ADD], [a1, a2])
+
+    xi, wi, wsi, bi = make_int8_case(33, 256, 80, seed=18)
+    hs = [aoti_handle(t.cuda()) for t in (xi, wi, wsi, bi)]
+    bias_slot, ret = vp(hs[3][1]), vp(None)
+    fn = lib.aoti_torch_cuda_zentorch_dynamic_qlinear
+    fn.restype = C.c_int32
+    assert fn(vp(hs[0][1]), vp(hs[1][1]), vp(hs[2][1]), C.byref(bias_slot), b"from_test", C.byref(ret)) == 0
+    yi = aoti_take(ret.value)
+    for cap, _ in hs:
+        aoti_release(cap)
+    assert_close_bf16(yi, O.dynamic_qlinear(xi, wi, wsi, bi), what="aoti dynamic_qlinear")
+    # an invalid call comes back as a non-zero error code, not as an exception across the C boundary
+    hs = [aoti_handle(t) for t in (xi.cuda(), wi.cuda().int(), wsi.cuda())]
+    ret = vp(None)
+    assert fn(vp(hs[0][1]), vp(hs[1][1]), vp(hs[2][1]), None, b"from_test", C.byref(ret)) != 0
+    for cap, _ in hs:
+        aoti_release(cap)
+
+
+def test_expired_device_wait_is_reported_and_cleared(zt):
+    """A kernel whose bounded wait gives up (a barrier nobody signals, a few thousand polls) sets the device
+    status word and returns; the host reads the code, clearing it also re-zeroes the split-K counters of the
+    cached workspaces, and the context stays usable."""
+    from zentorch_b200 import _capi
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ws = _capi.woq_workspace(1 << 20, dev)
+    ws[:8].fill_(1)                                     # pretend a kernel that gave up left a counter behind
+    _capi.check(_capi.lib().zt_selftest_expire_wait(None))
+    torch.cuda.synchronize()
+    assert _capi.poll_device_status(reset=True) == 199
+    assert _capi.poll_device_status(reset=True) == 0
+    assert int(ws[:_capi.ZT_WOQ_COUNTER_BYTES].sum()) == 0
+    x, q, s, z, b = make_woq_case(1, 4096, 1024, 128, seed=19)     # a split-K shape works right after
+    y = _capi.woq_linear(x.cuda(), _capi.woq_repack_weight(q.cuda()), s.cuda(), None, b.cuda())
+    assert_close_bf16(y, O.woq_linear(x, O.woq_repack_weight(q).t(), s, None, b))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_one_process_two_devices(ops):
+    """Per-device kernel attributes: the same process runs both linears on cuda:0 and then on cuda:1."""
+    x, q, s, z, b = make_woq_case(40, 1024, 256, 128, seed=20)
+    ref = O.woq_linear(x, O.woq_repack_weight(q).t(), s, None, b)
+    xi, wi, wsi, bi = make_int8_case(130, 512, 192, seed=21)
+    refi = O.dynamic_qlinear(xi, wi, wsi, bi)
+    for d in (0, 1):
+        dev = torch.device("cuda", d)
+        with torch.cuda.device(dev):
+            packed = ops.zentorch_woq_repack_weight(q.to(dev))
+            for m in (40, 2):
+                y = ops.zentorch_woq_linear(x[:m].to(dev), packed.t(), s.to(dev), None, b.to(dev))
+                assert_close_bf16(y, ref[:m], what=f"woq on cuda:{d} M={m}")
+            yi = ops.zentorch_dynamic_qlinear(xi.to(dev), wi.to(dev), wsi.to(dev), bi.to(dev))
+            assert_close_bf16(yi, refi, what=f"int8 on cuda:{d}")
+            torch.cuda.synchronize(dev)

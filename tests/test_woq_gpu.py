@@ -216,7 +216,7 @@ def test_prefill_shape_vs_oracle(capi):
 
 
 # ---- benchmark shapes ---------------------------------------------------------------------------------
-@pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 1024), (14336, 4096)])
+@pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)])
 def test_config_shapes_vs_oracle(capi, k, n):
     """Projection shapes of the benchmark configs at M in {1, 8, 32, 64, 128}; the weight is
     dequantised once on the CPU and shared by all M."""
@@ -259,3 +259,27 @@ def test_full_size_linearity_and_checksum(capi):
     got = y1.double().sum(dim=1).cpu()
     scale = y1.abs().sum(dim=1).double().cpu()
     assert ((got - expect).abs() <= 4e-3 * scale + 0.5).all()
+
+
+# ---- weights written directly before the call -----------------------------------------------------------
+@pytest.mark.parametrize("m,k,n,algo_hint", [(1, 4096, 1024, 1), (2, 8192, 256, 2), (40, 1024, 512, 0), (24, 1096, 64, 0)])
+def test_weights_written_just_before_the_call(capi, m, k, n, algo_hint):
+    """ZT_FLAG_WEIGHTS_VOLATILE: the packed weight and the scale table are produced on the same stream right
+    before every call (a repack and a copy into fresh buffers), as a non-frozen graph does.  The kernels
+    normally fetch weights before they order themselves after earlier work; with the flag they must not.
+    Covered: the register-ring kernel (hint 1), the work-balanced decode kernel (hint 2), the tensor-core
+    kernel (M = 40) and the mma.sync kernel for shapes the tensor-core kernel does not take (K % 64 != 0)."""
+    gs = 128 if k % 128 == 0 else 8
+    x, q, s, z, b = make_woq_case(m, k, n, gs, seed=k + m)
+    dev = "cuda"
+    xd, qd, s_t, bd = x.to(dev), q.to(dev), s.t().contiguous().to(dev), b.to(dev)
+    algo = capi.ZT_ALGO_SKINNY | (algo_hint << 8) if algo_hint else capi.ZT_ALGO_AUTO
+    ref = O.woq_linear(x, O.woq_repack_weight(q).t(), s, None, b)
+    junk = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    for rep in range(12):
+        junk.random_(0, 255)                                  # a long-running kernel ahead on the stream
+        packed = capi.woq_repack_weight(qd)                   # fresh buffers, written just before the linear
+        scales = s_t.t().contiguous()
+        y = capi.woq_linear(xd, packed, scales, None, bd, algo=algo, flags=capi.ZT_FLAG_WEIGHTS_VOLATILE)
+        del packed, scales
+        assert_close_bf16(y, ref, what=f"volatile weights rep {rep} M={m} K={k} N={n}")

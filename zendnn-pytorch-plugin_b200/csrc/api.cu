@@ -42,13 +42,20 @@ int cuda_fail(cudaError_t e, const char *what) {
   return ZT_CUDA_ERROR;
 }
 
+namespace {
+thread_local bool g_call_overlap = true;
+}
+
 bool overlap_launches() {
   static const bool on = [] {
     const char *e = std::getenv("ZENTORCH_B200_PDL");
     return !(e && e[0] == '0');
   }();
-  return on;
+  return on && g_call_overlap;
 }
+
+CallOverlap::CallOverlap(bool allowed) : saved_(g_call_overlap) { g_call_overlap = allowed; }
+CallOverlap::~CallOverlap() { g_call_overlap = saved_; }
 
 int sm_count() {
   static int cached[64] = {0};
@@ -177,6 +184,29 @@ extern "C" int zt_poll_device_status(int *status, int reset) {
   return ZT_SUCCESS;
 }
 
+// ---- self-test of the bounded-wait path ------------------------------------------------------------
+namespace zt {
+namespace {
+// One thread waits on an mbarrier that nothing ever arrives at, with a short poll limit; the wait gives up,
+// the status word is set, and the kernel returns normally.
+__global__ void expire_wait_kernel(int *status, uint32_t polls) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&bar, 1);
+    tc::mbar_fence_init();
+    if (!tc::mbar_wait(&bar, 0, polls)) tc::report_timeout(status, kStatusSelfTest);
+  }
+}
+}  // namespace
+}  // namespace zt
+
+extern "C" int zt_selftest_expire_wait(void *stream) {
+  int *status = device_status_ptr();
+  ZT_REQUIRE(status != nullptr, ZT_CUDA_ERROR, "zt_selftest_expire_wait: no device status word");
+  expire_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, 2048u);
+  return launch_status("expire_wait_kernel");
+}
+
 // ---- weight-only int4 ---------------------------------------------------------------------------
 extern "C" size_t zt_woq_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0) return ZT_WOQ_COUNTER_BYTES;
@@ -204,6 +234,7 @@ extern "C" int zt_woq_linear(const zt_woq_linear_args_t *a, void *stream) {
   int rc = validate_post_ops(a->post);
   if (rc != ZT_SUCCESS) return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  CallOverlap overlap(!(a->flags & ZT_FLAG_WEIGHTS_VOLATILE));
 
   int algo = a->algo & 0xff;
   const bool stream_ok = woq_stream_supported(*a);
@@ -326,6 +357,7 @@ extern "C" int zt_dynamic_qlinear(const zt_dynamic_qlinear_args_t *a, void *stre
   ZT_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, ZT_INVALID_ARGUMENT,
              "zt_dynamic_qlinear: workspace must be 256-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
+  CallOverlap overlap(!(a->flags & ZT_FLAG_WEIGHTS_VOLATILE));
   char *ws = reinterpret_cast<char *>(a->workspace);
   void *q = ws;
   float *scales = reinterpret_cast<float *>(ws + align_up((size_t)a->M * a->K, 256));
@@ -349,6 +381,7 @@ extern "C" int zt_qlinear_prequantized(const zt_dynamic_qlinear_args_t *a, const
              "zt_qlinear_prequantized: the u8 mode needs zero points and w_rowsum");
   int rc = validate_post_ops(a->post);
   if (rc != ZT_SUCCESS) return rc;
+  CallOverlap overlap(overlap_launches() && !(a->flags & ZT_FLAG_WEIGHTS_VOLATILE));
   Int8GemmArgs g{};
   g.q = q;
   g.q_is_u8 = u8;

@@ -39,14 +39,45 @@ inline int launch_status(const char *kernel) {
 
 int sm_count();
 
+// cudaFuncSetAttribute applies to the current device only, so the "already configured" note is kept per
+// device.  `done` is one flag array per kernel instantiation (a function-local static at the call site).
+struct PerDeviceOnce {
+  bool done[64] = {};
+};
+template <typename Kernel>
+inline int allow_dynamic_smem(PerDeviceOnce &once, Kernel kern, int bytes) {
+  int dev = 0;
+  ZT_CUDA_OK(cudaGetDevice(&dev));
+  ZT_REQUIRE(dev >= 0 && dev < 64, ZT_UNSUPPORTED, "device index %d out of range", dev);
+  if (!once.done[dev]) {
+    ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    once.done[dev] = true;
+  }
+  return ZT_SUCCESS;
+}
+
 // ---- programmatic dependent launch ---------------------------------------------------------------
 // Decode kernels are launched with programmatic stream serialisation: a kernel lets its successor start
 // early (grid_launch_dependents) and itself waits for its predecessor (grid_dependency_wait) only before
 // it touches what earlier work may write -- activations, scratch, output.  Weights, scales and zero points
-// are read before that wait: they must not be written by the kernel launched directly before on the same
-// stream unless that kernel completes normally, which every kernel but these does.
-// ZENTORCH_B200_PDL=0 launches with ordinary stream ordering.
+// are read before that wait, so they must be constants of the call: a caller whose weights may have been
+// written by work submitted directly before sets ZT_FLAG_WEIGHTS_VOLATILE, and the call's kernels are then
+// launched with ordinary stream ordering (the wait instructions become no-ops).
+// ZENTORCH_B200_PDL=0 launches everything with ordinary stream ordering.
 bool overlap_launches();
+
+// Scope of one API call: `allowed = false` (ZT_FLAG_WEIGHTS_VOLATILE) makes every launch of the call on
+// this thread an ordinary stream-ordered one, so nothing is read before earlier work has completed.
+class CallOverlap {
+ public:
+  explicit CallOverlap(bool allowed);
+  ~CallOverlap();
+  CallOverlap(const CallOverlap &) = delete;
+  CallOverlap &operator=(const CallOverlap &) = delete;
+
+ private:
+  bool saved_;
+};
 
 #ifdef __CUDACC__
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -5,6 +5,9 @@
 // with warp shuffles, and written back as 8-bit values with 8-byte stores.  The scale uses IEEE
 // division and the quantised value round-half-even, so the bytes equal those of the CPU formula
 //   s = max(absmax, 1e-12) / 127,   q = clamp(rint(x / s), -128, 127).
+// A NaN anywhere in a row makes that row's scale NaN (as a maximum that propagates NaNs does, which is what
+// the CPU formula's amax is), so the whole output row of the linear is NaN; the row's quantised bytes are
+// then unspecified.  Other rows are not affected.  -0.0 counts as 0.
 #include "int8.cuh"
 
 namespace zt {
@@ -35,11 +38,16 @@ __device__ __forceinline__ void load8(const void *x, int dtype, int64_t off, flo
 // Row maximum of hi and row minimum of lo over the CTA in one pass: warp shuffles, one shared-memory slot per
 // warp and value, one barrier, and every thread folds the eight warp results itself (max and min are exact, so
 // the order does not matter).
-__device__ __forceinline__ void block_reduce_max_min(float &hi, float &lo, float *scratch) {
+// fmaxf / fminf return the other operand when one is NaN; these keep it.
+__device__ __forceinline__ float nan_max(float a, float b) { return (a != a) ? a : (b != b) ? b : fmaxf(a, b); }
+__device__ __forceinline__ float nan_min(float a, float b) { return (a != a) ? a : (b != b) ? b : fminf(a, b); }
+
+__device__ __forceinline__ void block_reduce_max_min(float &hi, float &lo, bool saw_nan, float *scratch) {
+  if (saw_nan) hi = lo = __int_as_float(0x7fc00000);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
-    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = nan_max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    lo = nan_min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
   }
   constexpr int kWarps = kThreads / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -50,8 +58,21 @@ __device__ __forceinline__ void block_reduce_max_min(float &hi, float &lo, float
   __syncthreads();
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) {
-    hi = fmaxf(hi, scratch[w]);
-    lo = fminf(lo, scratch[kWarps + w]);
+    hi = nan_max(hi, scratch[w]);
+    lo = nan_min(lo, scratch[kWarps + w]);
+  }
+}
+
+// Row scale (and zero point) from the reduced extremes; NaN extremes give a NaN scale.
+template <bool U8>
+__device__ __forceinline__ void row_scale(float hi, float lo, float &s, float &zp) {
+  zp = 0.f;
+  if (U8) {
+    const float range = hi - lo;
+    s = (range != range) ? range : __fdiv_rn(fmaxf(range, 1e-12f), 255.0f);
+    zp = fminf(fmaxf(rintf(__fdiv_rn(-lo, s)), 0.f), 255.f);
+  } else {
+    s = (hi != hi) ? hi : __fdiv_rn(fmaxf(hi, 1e-12f), 127.0f);
   }
 }
 
@@ -81,6 +102,7 @@ __global__ void __launch_bounds__(kThreads) dynquant_vec_kernel(const void *__re
   const int64_t chunks = K / kVec;
   float v[kCached][8];
   float hi = 0.f, lo = 0.f;  // u8: max(x,0), min(x,0); s8: hi = absmax
+  bool saw_nan = false;
 #pragma unroll
   for (int c = 0; c < kCached; ++c) {
     const int64_t ch = (int64_t)c * kThreads + threadIdx.x;
@@ -88,6 +110,7 @@ __global__ void __launch_bounds__(kThreads) dynquant_vec_kernel(const void *__re
       load8(x, x_dtype, base + ch * kVec, v[c]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
+        saw_nan |= (v[c][i] != v[c][i]);
         if (U8) {
           hi = fmaxf(hi, v[c][i]);
           lo = fminf(lo, v[c][i]);
@@ -102,6 +125,7 @@ __global__ void __launch_bounds__(kThreads) dynquant_vec_kernel(const void *__re
     load8(x, x_dtype, base + ch * kVec, t);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
+      saw_nan |= (t[i] != t[i]);
       if (U8) {
         hi = fmaxf(hi, t[i]);
         lo = fminf(lo, t[i]);
@@ -110,14 +134,9 @@ __global__ void __launch_bounds__(kThreads) dynquant_vec_kernel(const void *__re
       }
     }
   }
-  block_reduce_max_min(hi, lo, scratch);
-  float s, zp = 0.f;
-  if (U8) {
-    s = __fdiv_rn(fmaxf(hi - lo, 1e-12f), 255.0f);
-    zp = fminf(fmaxf(rintf(__fdiv_rn(-lo, s)), 0.f), 255.f);
-  } else {
-    s = __fdiv_rn(fmaxf(hi, 1e-12f), 127.0f);
-  }
+  block_reduce_max_min(hi, lo, saw_nan, scratch);
+  float s, zp;
+  row_scale<U8>(hi, lo, s, zp);
   if (threadIdx.x == 0) {
     scales[row] = s;
     if (U8 && zps) zps[row] = (int32_t)zp;
@@ -154,8 +173,10 @@ __global__ void __launch_bounds__(kThreads) dynquant_scalar_kernel(const void *_
   const int64_t row = blockIdx.x;
   const int64_t base = row * K;
   float hi = 0.f, lo = 0.f;
+  bool saw_nan = false;
   for (int64_t k = threadIdx.x; k < K; k += kThreads) {
     const float t = load_as_float(x, base + k, x_dtype);
+    saw_nan |= (t != t);
     if (U8) {
       hi = fmaxf(hi, t);
       lo = fminf(lo, t);
@@ -163,14 +184,9 @@ __global__ void __launch_bounds__(kThreads) dynquant_scalar_kernel(const void *_
       hi = fmaxf(hi, fabsf(t));
     }
   }
-  block_reduce_max_min(hi, lo, scratch);
-  float s, zp = 0.f;
-  if (U8) {
-    s = __fdiv_rn(fmaxf(hi - lo, 1e-12f), 255.0f);
-    zp = fminf(fmaxf(rintf(__fdiv_rn(-lo, s)), 0.f), 255.f);
-  } else {
-    s = __fdiv_rn(fmaxf(hi, 1e-12f), 127.0f);
-  }
+  block_reduce_max_min(hi, lo, saw_nan, scratch);
+  float s, zp;
+  row_scale<U8>(hi, lo, s, zp);
   if (threadIdx.x == 0) {
     scales[row] = s;
     if (U8 && zps) zps[row] = (int32_t)zp;

@@ -378,11 +378,8 @@ int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, 
   using L = SmemLayout<MH, BN, STAGES>;
   static_assert(L::kTotal <= 227 * 1024, "stage ring exceeds shared memory");
   auto kern = int8_tcgen05_kernel<MH, BN, STAGES, NBUF, EPI, A_SIGNED>;
-  static bool configured = false;
-  if (!configured) {
-    ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  if (int rc_cfg = allow_dynamic_smem(configured, kern, L::kTotal)) return rc_cfg;
   TcParams q = p;
   q.m_tiles = ceil_div(p.M, MH * kBM);
   q.n_tiles = ceil_div(p.N, BN);

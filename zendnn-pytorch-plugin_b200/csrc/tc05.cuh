@@ -22,7 +22,8 @@ enum DeviceStatus : int {
   kStatusProducerTimeout = 101,  // TMA producer waited for a free stage
   kStatusMmaTimeout = 102,       // MMA issuer waited for data
   kStatusEpilogueTimeout = 103,  // epilogue waited for the accumulator
-  kStatusConvertTimeout = 104    // dequant warps waited for a stage
+  kStatusConvertTimeout = 104,   // dequant warps waited for a stage
+  kStatusSelfTest = 199          // zt_selftest_expire_wait: the deliberately unanswered wait gave up
 };
 
 namespace tc {
@@ -55,9 +56,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 }
 
 // Returns false when the phase did not complete within the poll limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = kSpinLimit) {
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"

@@ -17,6 +17,7 @@
 #include <torch/library.h>
 
 #include <map>
+#include <tuple>
 #include <mutex>
 #include <optional>
 #include <string>
@@ -50,13 +51,74 @@ at::Tensor as_2d(const at::Tensor &t) {
   return c.view({last == 0 ? 0 : c.numel() / last, last});
 }
 
+// Every tensor argument must live on the input's GPU: the kernels take raw pointers, and a host pointer or
+// another device's pointer would fault on the GPU instead of raising here.
+void check_on_device(const at::Tensor &t, const at::Tensor &input, const char *op, const char *name) {
+  TORCH_CHECK(t.is_cuda() && t.device() == input.device(), op, ": ", name, " must be on the input's device (",
+              input.device(), "), got ", t.device());
+}
+void check_on_device(const std::optional<at::Tensor> &t, const at::Tensor &input, const char *op, const char *name) {
+  if (t.has_value() && t->defined()) check_on_device(*t, input, op, name);
+}
+
+// Weights are constants of a model, and the kernels read them before ordering themselves after earlier work
+// on the stream.  That is only sound for a tensor that earlier work cannot still be writing, so the boundary
+// keeps a record of the weight tensors it has seen: (storage, offset, version) with a weak reference that
+// tells a live storage from a new one at a recycled address.  A tensor seen in an earlier call, with its
+// storage still alive and its version unchanged, was produced before that call; anything else (first sight,
+// a temporary made inside this call) is passed on as ZT_FLAG_WEIGHTS_VOLATILE.
+class SeenWeights {
+ public:
+  bool seen_before(const at::Tensor &t) {
+    if (!t.defined() || !t.has_storage()) return false;
+    c10::StorageImpl *impl = t.storage().unsafeGetStorageImpl();
+    const Key key{impl, t.storage_offset(), t.numel()};
+    const int64_t version = t.is_inference() ? 0 : (int64_t)t._version();
+    std::lock_guard<std::mutex> lock(mu_);
+    auto it = map_.find(key);
+    if (it != map_.end() && !it->second.storage.expired() && it->second.version == version) return true;
+    if (map_.size() >= kMaxEntries) purge();
+    map_.insert_or_assign(key, Entry{t.storage().getWeakStorageImpl(), version});
+    return false;
+  }
+
+ private:
+  struct Key {
+    const void *storage;
+    int64_t offset, numel;
+    bool operator<(const Key &o) const { return std::tie(storage, offset, numel) < std::tie(o.storage, o.offset, o.numel); }
+  };
+  struct Entry {
+    c10::weak_intrusive_ptr<c10::StorageImpl> storage;
+    int64_t version;
+  };
+  static constexpr size_t kMaxEntries = 1 << 16;
+  void purge() {
+    for (auto it = map_.begin(); it != map_.end();) it = it->second.storage.expired() ? map_.erase(it) : std::next(it);
+    if (map_.size() >= kMaxEntries) map_.clear();
+  }
+  std::mutex mu_;
+  std::map<Key, Entry> map_;
+};
+SeenWeights &seen_weights() {
+  static SeenWeights s;
+  return s;
+}
+
 // Persistent scratch per (device, stream) for the split-K kernel: the counters at its front must
 // stay zero between calls, so it cannot come from a fresh allocation every time.
-at::Tensor &woq_workspace(size_t bytes, c10::DeviceIndex dev, cudaStream_t stream) {
+std::mutex &workspace_mutex() {
   static std::mutex mu;
+  return mu;
+}
+std::map<std::pair<int, void *>, at::Tensor> &workspace_pool() {
   static std::map<std::pair<int, void *>, at::Tensor> pool;
-  std::lock_guard<std::mutex> lock(mu);
-  at::Tensor &t = pool[{(int)dev, (void *)stream}];
+  return pool;
+}
+
+at::Tensor &woq_workspace(size_t bytes, c10::DeviceIndex dev, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(workspace_mutex());
+  at::Tensor &t = workspace_pool()[{(int)dev, (void *)stream}];
   if (!t.defined() || (size_t)t.numel() < bytes) {
     const size_t grow = std::max<size_t>(bytes, 1 << 20);
     t = at::zeros({(int64_t)grow}, at::TensorOptions().dtype(at::kByte).device(at::kCUDA, dev));
@@ -74,6 +136,11 @@ at::Tensor woq_linear_impl(const at::Tensor &input, const at::Tensor &weight, co
                            const PostSpec &post, const std::string &op_name) {
   RECORD_FUNCTION(op_name, std::vector<c10::IValue>({input, weight}));
   TORCH_CHECK(input.is_cuda(), "zentorch_woq_linear (CUDA): input must be a CUDA tensor");
+  check_on_device(weight, input, "zentorch_woq_linear", "weight");
+  check_on_device(weight_scales, input, "zentorch_woq_linear", "weight_scales");
+  check_on_device(weight_zero_points, input, "zentorch_woq_linear", "weight_zero_points");
+  check_on_device(bias, input, "zentorch_woq_linear", "bias");
+  for (const at::Tensor &t : post.operands) check_on_device(t, input, "zentorch_woq_linear", "binary post-op operand");
   TORCH_CHECK(weight.dtype() == at::kInt, "weight must have dtype int32, got ", weight.dtype());
   TORCH_CHECK(weight.dim() == 2, "weight must be 2D, got ", weight.dim(), "D");
   TORCH_CHECK(weight_scales.dim() == 2, "weight_scales must be 2D [groups, N], got ", weight_scales.dim(), "D");
@@ -102,11 +169,15 @@ at::Tensor woq_linear_impl(const at::Tensor &input, const at::Tensor &weight, co
   if (M == 0 || N == 0) return result;
 
   at::Tensor scales = weight_scales.contiguous();
+  // constants of the call: tensors seen in an earlier call and passed through unchanged (no temporary made here)
+  bool weights_const = seen_weights().seen_before(weight);
+  weights_const = seen_weights().seen_before(weight_scales) && scales.is_same(weight_scales) && weights_const;
   at::Tensor zeros;
   if (weight_zero_points.has_value() && weight_zero_points->defined()) {
     TORCH_CHECK(weight_zero_points->sizes() == weight_scales.sizes(),
                 "weight_zero_points must have the shape of weight_scales");
     zeros = weight_zero_points->to(scales.scalar_type()).contiguous();
+    weights_const = seen_weights().seen_before(*weight_zero_points) && zeros.is_same(*weight_zero_points) && weights_const;
   }
   at::Tensor bias_c;
   if (bias.has_value() && bias->defined()) {
@@ -128,6 +199,7 @@ at::Tensor woq_linear_impl(const at::Tensor &input, const at::Tensor &weight, co
   a.bias_dtype = bias_c.defined() ? to_zt_dtype(bias_c, "bias") : ZT_BF16;
   a.y = result.data_ptr();
   a.algo = ZT_ALGO_AUTO;
+  a.flags = weights_const ? 0 : ZT_FLAG_WEIGHTS_VOLATILE;
   std::vector<at::Tensor> keep;
   a.post.n_ops = (int)post.ids.size();
   size_t b = 0;
@@ -179,6 +251,7 @@ at::Tensor woq_repack_weight(const at::Tensor &unpacked_weight) {
   TORCH_CHECK(unpacked_weight.dtype() == at::kChar, "unpacked_weight must have dtype int8, got ",
               unpacked_weight.dtype());
   TORCH_CHECK(unpacked_weight.dim() == 2, "unpacked_weight must be 2D, got ", unpacked_weight.dim(), "D");
+  TORCH_CHECK(unpacked_weight.is_cuda(), "zentorch_woq_repack_weight (CUDA): unpacked_weight must be a CUDA tensor");
   const int64_t N = unpacked_weight.size(0), K = unpacked_weight.size(1);
   TORCH_CHECK(K >= 8, "K must be at least 8, got ", K);
   TORCH_CHECK(K % 8 == 0, "K must be divisible by 8, got ", K);
@@ -193,6 +266,7 @@ at::Tensor woq_repack_weight(const at::Tensor &unpacked_weight) {
 at::Tensor woq_repack_from_int4pack(const at::Tensor &packed_weight) {
   TORCH_CHECK(packed_weight.dtype() == at::kByte, "packed_weight must have dtype uint8, got ", packed_weight.dtype());
   TORCH_CHECK(packed_weight.dim() == 2, "packed_weight must be 2D, got ", packed_weight.dim(), "D");
+  TORCH_CHECK(packed_weight.is_cuda(), "zentorch_woq_repack_from_int4pack (CUDA): packed_weight must be a CUDA tensor");
   const int64_t N = packed_weight.size(0), K_half = packed_weight.size(1);
   TORCH_CHECK(N % 64 == 0, "packed_weight row count (", N, ") must be a multiple of ", 64,
               ". The int4pack format from PyTorch pads N to BLOCK_N; "
@@ -233,6 +307,10 @@ at::Tensor dynamic_qlinear_impl(const at::Tensor &input, const at::Tensor &weigh
   }
   TORCH_CHECK(weight_scales.numel() == N, "zentorch_dynamic_qlinear: weight_scales must hold N (", N, ") values");
   TORCH_CHECK(input.is_cuda(), "zentorch_dynamic_qlinear (CUDA): input must be a CUDA tensor");
+  check_on_device(weight, input, "zentorch_dynamic_qlinear", "weight");
+  check_on_device(weight_scales, input, "zentorch_dynamic_qlinear", "weight_scales");
+  check_on_device(bias, input, "zentorch_dynamic_qlinear", "bias");
+  check_on_device(weight_rowsum, input, "zentorch_dynamic_qlinear", "weight_rowsum");
   c10::cuda::CUDAGuard device_guard(input.device());
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
 
@@ -245,15 +323,19 @@ at::Tensor dynamic_qlinear_impl(const at::Tensor &input, const at::Tensor &weigh
   at::Tensor w = weight.contiguous();
   at::Tensor ws = weight_scales.contiguous();
   at::Tensor b = has_bias ? bias->contiguous() : at::Tensor();
+  bool weights_const = seen_weights().seen_before(weight);
+  weights_const = seen_weights().seen_before(weight_scales) && w.is_same(weight) && ws.is_same(weight_scales) && weights_const;
   at::Tensor rowsum;
   if (act_quant == ZT_ACT_U8_ASYM) {
     if (weight_rowsum.has_value() && weight_rowsum->defined()) {
       TORCH_CHECK(weight_rowsum->scalar_type() == at::kInt && weight_rowsum->numel() == N,
                   "weight_rowsum must be int32 with N values");
       rowsum = weight_rowsum->contiguous();
+      weights_const = seen_weights().seen_before(*weight_rowsum) && rowsum.is_same(*weight_rowsum) && weights_const;
     } else {
       rowsum = at::empty({N}, w.options().dtype(at::kInt));
       ZT_TORCH_CALL(zt_int8_weight_rowsum(w.data_ptr<int8_t>(), N, K, rowsum.data_ptr<int32_t>(), stream));
+      weights_const = false;
     }
   }
   const size_t ws_bytes = zt_dynamic_qlinear_workspace_bytes(M, K);
@@ -280,6 +362,7 @@ at::Tensor dynamic_qlinear_impl(const at::Tensor &input, const at::Tensor &weigh
   a.workspace = scratch.data_ptr();
   a.workspace_bytes = ws_bytes;
   a.algo = ZT_ALGO_AUTO;
+  a.flags = weights_const ? 0 : ZT_FLAG_WEIGHTS_VOLATILE;
   ZT_TORCH_CALL(zt_dynamic_qlinear(&a, stream));
   return result;
 }
@@ -445,6 +528,14 @@ static Registrar g_registrar;
 }  // namespace
 
 }  // namespace zentorch_b200
+
+// Zeroes the split-K counters of every pooled WOQ workspace; to be called after zt_poll_device_status
+// reported an expired device-side wait (the kernel that gave up may have left counters non-zero).
+extern "C" ZT_API void zentorch_b200_reset_workspaces() {
+  std::lock_guard<std::mutex> lock(zentorch_b200::workspace_mutex());
+  for (auto &kv : zentorch_b200::workspace_pool())
+    if (kv.second.defined()) kv.second.zero_();
+}
 
 // ---- AOTInductor C shims -------------------------------------------------------------------------------
 // Same parameter lists as aoti_torch_cpu_zentorch_* (src/cpu/cpp/shim_cpu_zentorch.hpp:150-197);

@@ -301,11 +301,8 @@ size_t skinny_smem_bytes(int mt, int kslice) {
 template <int MT, bool ASYM, bool FOLD>
 int launch(const SkinnyParams &p, dim3 grid, size_t smem, cudaStream_t st) {
   auto kern = woq_skinny_kernel<MT, ASYM, FOLD>;
-  static bool configured = false;  // per instantiation; the attribute is per function, set once
-  if (!configured) {
-    ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  if (int rc_cfg = allow_dynamic_smem(configured, kern, 160 * 1024)) return rc_cfg;
   kern<<<grid, kThreads, smem, st>>>(p);
   return launch_status("woq_skinny_kernel");
 }

@@ -173,6 +173,9 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   // The next kernel may come in at once when this grid is resident as a whole; otherwise only after the main
   // loop, when every CTA of this grid has started (its CTAs would take the places of this grid's later ones).
   if (p.early_trigger) grid_launch_dependents();
+  // cluster form: every CTA of the cluster must be running before a peer's shared memory is written; the
+  // matching wait sits right before the first remote store
+  if (p.cluster) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 #pragma unroll
   for (int s = 0; s < RING; ++s) prefetch(ring[s], step_k(s / kSPC, s % kSPC));
   grid_dependency_wait();
@@ -294,6 +297,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   if (p.nsplit > 1 && p.cluster) {
     // K slices of this column tile form a cluster (rank = slice): every CTA puts its sums into the first
     // CTA's shared memory, which adds them in slice order after the cluster barrier -- no global round trip.
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // pairs with the arrive at kernel entry
     for (int ml = tid / kTileN; ml < p.M; ml += kRowsPerPass) {
       float v = 0.f;
 #pragma unroll
@@ -303,6 +307,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
       asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0));
       asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
     }
+    __syncwarp();   // the loop's trip count differs between lanes; the aligned barrier needs the warp converged
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (split != 0) return;
@@ -364,11 +369,8 @@ template <int MT, int CFG, bool ASYM, bool SF32>
 int launch(const StreamParams &p_in, dim3 grid, cudaStream_t st) {
   using S = Shape<MT, CFG>;
   auto kern = woq_stream_kernel<MT, S::R, S::RING, S::W, ASYM, SF32>;
-  static bool configured = false;
-  if (!configured) {
-    ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  if (int rc_cfg = allow_dynamic_smem(configured, kern, kMaxDynSmem)) return rc_cfg;
   // clusters of up to eight K slices (the portable cluster size) reduce through shared memory
   static const bool use_clusters = [] {
     const char *e = std::getenv("ZENTORCH_B200_WOQ_CLUSTER");
@@ -379,9 +381,10 @@ int launch(const StreamParams &p_in, dim3 grid, cudaStream_t st) {
   bool cluster = use_clusters && p_in.nsplit >= 2 && p_in.nsplit <= 8 && (int)grid.y == p_in.nsplit &&
                  base_smem + cl_bytes <= (size_t)kMaxDynSmem;
   size_t smem = base_smem + (cluster ? cl_bytes : 0);
-  static int per_sm_for_m[17] = {0};   // resident CTAs per SM; the dynamic shared memory depends on M only
-  int &per_sm = per_sm_for_m[p_in.M];
-  if (per_sm == 0) ZT_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, S::W * 32, smem));
+  // resident CTAs per SM: depends on the device and on the shared-memory size (M, and the cluster buffer),
+  // so it is asked for every launch (a host-side computation from the function's attributes)
+  int per_sm = 0;
+  ZT_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, S::W * 32, smem));
   StreamParams p = p_in;
   p.cluster = cluster ? 1 : 0;
   p.cluster_off = (int)base_smem;

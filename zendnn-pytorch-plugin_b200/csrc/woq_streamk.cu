@@ -816,11 +816,8 @@ int build_maps(const zt_woq_linear_args_t &a, int mrows, uint32_t cs, Maps &m) {
 template <int NB, int CW, bool ASYM, bool SF32>
 int launch(const Maps &m, const SKParams &p, int grid, size_t smem_bytes, cudaStream_t st) {
   auto kern = woq_streamk_kernel<NB, CW, ASYM, SF32>;
-  static bool configured = false;
-  if (!configured) {
-    ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  if (int rc_cfg = allow_dynamic_smem(configured, kern, 226 * 1024)) return rc_cfg;
   ZT_CUDA_OK(launch_overlapped(kern, dim3((unsigned)grid), dim3((unsigned)sk_threads(CW)), smem_bytes, st, m.w8, m.x8, m.s,
                                m.z, p));
   return launch_status("woq_streamk_kernel");

@@ -638,19 +638,13 @@ int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows,
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   if (asym) {
     auto kern = woq_tcgen05_kernel<BT, STAGES, PSTAGES, true>;
-    static bool configured = false;
-    if (!configured) {
-      ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-      configured = true;
-    }
+    static PerDeviceOnce configured;
+    if (int rc_cfg = allow_dynamic_smem(configured, kern, L::kTotal)) return rc_cfg;
     ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, p));
   } else {
     auto kern = woq_tcgen05_kernel<BT, STAGES, PSTAGES, false>;
-    static bool configured = false;
-    if (!configured) {
-      ZT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-      configured = true;
-    }
+    static PerDeviceOnce configured;
+    if (int rc_cfg = allow_dynamic_smem(configured, kern, L::kTotal)) return rc_cfg;
     ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, p));
   }
   return launch_status("woq_tcgen05_kernel");

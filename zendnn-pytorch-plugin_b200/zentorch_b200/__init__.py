@@ -55,4 +55,8 @@ def register_backend() -> None:
     _compile.register_backend()
 
 
-load()
+# `python -m zentorch_b200._build` imports this package before it has built (or rebuilt) the libraries.
+import sys as _sys
+
+if "zentorch_b200._build" not in getattr(_sys, "orig_argv", ()):
+    load()

@@ -17,13 +17,14 @@ ZT_MAX_POST_OPS = 4
 ZT_WOQ_COUNTER_BYTES = 16384
 ZT_ALGO_AUTO, ZT_ALGO_GENERIC, ZT_ALGO_SKINNY, ZT_ALGO_TCGEN05 = 0, 1, 2, 3
 ZT_ACT_S8_SYM, ZT_ACT_U8_ASYM = 0, 1
+ZT_FLAG_WEIGHTS_VOLATILE = 1
 ZT_STATIC_SCRATCH_Q_BYTES, ZT_STATIC_SCRATCH_MAX_ROWS = 8 << 20, 16384
 (ZT_POST_NONE, ZT_POST_RELU, ZT_POST_GELU_TANH, ZT_POST_GELU_ERF, ZT_POST_SILU, ZT_POST_SIGMOID,
  ZT_POST_TANH, ZT_POST_MUL, ZT_POST_ADD) = range(9)
 
 # Every symbol include/zentorch_b200.h declares; the CPU test-suite checks the library exports all.
 EXPORTED_SYMBOLS = (
-    "zt_last_error", "zt_version", "zt_device_supported", "zt_poll_device_status",
+    "zt_last_error", "zt_version", "zt_device_supported", "zt_poll_device_status", "zt_selftest_expire_wait",
     "zt_woq_linear_workspace_bytes", "zt_woq_linear", "zt_woq_repack_weight", "zt_woq_repack_from_int4pack",
     "zt_dynamic_qlinear_workspace_bytes", "zt_dynamic_qlinear", "zt_dynamic_quantize", "zt_int8_gemm_s32",
     "zt_int8_weight_rowsum", "zt_qlinear_prequantized", "zt_dynamic_qlinear_static",
@@ -41,6 +42,7 @@ class WoqLinearArgs(C.Structure):
         ("wq", C.c_void_p), ("scales", C.c_void_p), ("zeros", C.c_void_p), ("scale_dtype", C.c_int32),
         ("n_groups", C.c_int64), ("bias", C.c_void_p), ("bias_dtype", C.c_int32), ("post", PostOps),
         ("y", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("algo", C.c_int32),
+        ("flags", C.c_int32),
     ]
 
 
@@ -50,6 +52,7 @@ class DynamicQLinearArgs(C.Structure):
         ("w", C.c_void_p), ("w_scales", C.c_void_p), ("w_scale_dtype", C.c_int32), ("bias", C.c_void_p),
         ("bias_dtype", C.c_int32), ("act_quant", C.c_int32), ("w_rowsum", C.c_void_p), ("post", PostOps),
         ("y", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("algo", C.c_int32),
+        ("flags", C.c_int32),
     ]
 
 
@@ -87,6 +90,7 @@ def lib() -> C.CDLL:
     L.zt_version.restype = C.c_char_p
     L.zt_device_supported.restype = C.c_int
     L.zt_poll_device_status.argtypes = [C.POINTER(C.c_int), C.c_int]
+    L.zt_selftest_expire_wait.argtypes = [C.c_void_p]
     L.zt_woq_linear_workspace_bytes.restype = C.c_size_t
     L.zt_woq_linear_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64]
     L.zt_woq_linear.argtypes = [C.POINTER(WoqLinearArgs), C.c_void_p]
@@ -115,9 +119,27 @@ def check(rc: int) -> None:
 
 
 def poll_device_status(reset: bool = True) -> int:
+    """The device status word (0 = no bounded wait expired).  With ``reset`` a non-zero status is cleared
+    and the split-K counters at the front of every cached WOQ workspace are zeroed again, as the header
+    asks after a timeout (a kernel that gave up may have left them non-zero)."""
     st = C.c_int(0)
     check(lib().zt_poll_device_status(C.byref(st), 1 if reset else 0))
+    if reset and st.value != 0:
+        for t in _woq_ws.values():
+            t[:ZT_WOQ_COUNTER_BYTES].zero_()
+        torch_lib = _torch_boundary()
+        if torch_lib is not None:
+            torch_lib.zentorch_b200_reset_workspaces()
     return st.value
+
+
+def _torch_boundary():
+    """The operator library, when the package has loaded it (it keeps its own workspace pool)."""
+    path = LIB_PATH.with_name("libzentorch_b200_torch.so")
+    try:
+        return C.CDLL(str(path), mode=C.RTLD_NOLOAD)
+    except OSError:
+        return None
 
 
 # ---- torch-tensor conveniences (raw pointers underneath) ------------------------------------------
@@ -159,7 +181,7 @@ def woq_workspace(nbytes: int, device):
     return t
 
 
-def woq_linear(x, wq_rows, scales, zeros=None, bias=None, post_ops=(), buffers=(), algo=ZT_ALGO_AUTO):
+def woq_linear(x, wq_rows, scales, zeros=None, bias=None, post_ops=(), buffers=(), algo=ZT_ALGO_AUTO, flags=0):
     """x: [M, K] bf16 CUDA; wq_rows: the contiguous [N, K/8] int32 packed tensor (i.e. the op's
     weight argument transposed back); scales/zeros: [G, N]."""
     import torch
@@ -179,6 +201,7 @@ def woq_linear(x, wq_rows, scales, zeros=None, bias=None, post_ops=(), buffers=(
     ws = woq_workspace(lib().zt_woq_linear_workspace_bytes(m, n, k), x.device)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     a.algo = algo
+    a.flags = flags
     check(lib().zt_woq_linear(C.byref(a), _stream_ptr()))
     return y
 
@@ -247,7 +270,7 @@ def dynamic_qlinear_args(x, w, w_scales, bias, act_quant, post_ops, buffers, w_r
 
 
 def dynamic_qlinear(x, w, w_scales, bias=None, act_quant=ZT_ACT_S8_SYM, post_ops=(), buffers=(), w_rowsum=None,
-                    algo=ZT_ALGO_AUTO):
+                    algo=ZT_ALGO_AUTO, flags=0):
     import torch
     m, k = x.shape
     n = w.shape[0]
@@ -265,6 +288,7 @@ def dynamic_qlinear(x, w, w_scales, bias=None, act_quant=ZT_ACT_S8_SYM, post_ops
     a.w_rowsum = w_rowsum.data_ptr() if w_rowsum is not None else None
     a.post = _post(post_ops, buffers)
     a.y, a.workspace, a.workspace_bytes, a.algo = y.data_ptr(), ws.data_ptr(), nbytes, algo
+    a.flags = flags
     check(lib().zt_dynamic_qlinear(C.byref(a), _stream_ptr()))
     return y
 
