@@ -1,22 +1,29 @@
 #!/usr/bin/env python
 """Benchmark of the zentorch quantized-linear hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--quick]
 
-Workload (BASELINE config 2): dynamic int8 linear, x bf16 [512, 4096] ~ N(0,1) quantised per token
-at run time, W int8 [11008, 4096] (per-channel scales), fp32 bias, fused SiLU.  Metric: achieved
-int8 TOP/s = 2*M*N*K / time.  One "step" is one pass over a batch of CALLS_PER_STEP such linears
-(each call = the per-token quantisation kernel + the tcgen05 GEMM with fused epilogue), rotating
-over operand sets whose total size exceeds L2 so that no call finds its weights cached.
+One GPU (the headline, BASELINE config 2): dynamic int8 linear, x bf16 [512, 4096] ~ N(0,1) quantised per
+token at run time, W int8 [11008, 4096] (per-channel scales), fp32 bias, fused SiLU.  Metric: achieved int8
+TOP/s = 2*M*N*K / time.  One "step" is one pass over a batch of CALLS_PER_STEP such linears (each call = the
+per-token quantisation kernel + the tcgen05 GEMM with fused epilogue), rotating over operand sets whose
+total size exceeds L2 so that no call finds its weights cached.
+
+Several GPUs (torchrun, BASELINE config 5): the seven projections of a Llama-3-70B decoder layer, int8
+dynamic at M = 4096, sharded column-/row-parallel over the ranks (one NCCL all-reduce after each
+row-parallel projection).  Total work is fixed, so this is strong scaling; the value is the layer's
+2*M*sum(N*K) operations per second over all ranks.  The same layer is measured in `tp_layer` for weight-only
+int4 and int8 at M in {1, 32, 4096} at every N (N = 1 included), so the curve has its one-GPU point.
 
 The JSON line carries, besides the driver contract's keys:
-  roofline       the tcgen05 GEMM kernel alone against the tensor roofline
-  woq_decode     the weight-only int4 GEMV (config 1, M=1) against the HBM roofline
-  cpu_baseline   the CPU oracle (torch CPU kernels) timed on this box's host cores
-  e2e            the same metric through torch.ops.zentorch with host buffers (pinned H2D of x,
-                 D2H of y inside the timed region)
-With N > 1 (torchrun) every rank runs the same workload on its own batch (data-parallel replicas,
-no collective on the data path) and the value is the sum over ranks: weak scaling.
+  roofline        the dominant kernel alone against its roofline (tensor for int8, with ncu DRAM traffic)
+  woq_*           weight-only int4 cases: config 1 (M = 1, 128, 2048), a 117 MB layer at M = 1
+  llama8b_layer   config 3, llama70b_projections / tp_layer   config 5, moe_int4   config 4
+  cpu_baseline    the CPU oracle (torch CPU kernels) timed on this box's host cores
+  e2e             the same metric through torch.ops.zentorch with host buffers (pinned H2D of x, D2H of y
+                  inside the timed region)
+Every timed WOQ operand set is checked once, before timing, against a plain fp32 torch evaluation of sampled
+output columns (written here, independent of the kernels).
 """
 import argparse
 import json
@@ -37,7 +44,23 @@ M, K, N = 512, 4096, 11008
 CALLS_PER_STEP = 256
 OPS_PER_CALL = 2.0 * M * N * K
 L2_BYTES = 126 * 1024 * 1024
+GS = 128
 METRIC = "dynamic int8 qlinear (u8 per-token act x s8 per-channel weight, fused SiLU) achieved TOP/s"
+METRIC_TP = "dynamic int8 qlinear achieved TOP/s, Llama-3-70B decoder-layer projections, tensor-parallel"
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under
+# profiles/ (file named beside each figure); None where no capture exists for that kernel and workload.
+NCU_TRAFFIC = {
+    "int8_tcgen05_kernel/config2": (47.4e6 + 11.3e6, "profiles/int8_tcgen05_kernel_config2.md"),
+    "woq_streamk_kernel/8192x28672_M1": (132.0e6, "profiles/woq_streamk_kernel_config3_layer.md"),
+    "woq_tcgen05_kernel/4096x14336_M2048": (67.6e6, "profiles/woq_tcgen05_kernel_prefill.md"),
+}
+
+# Llama-3-70B decoder layer (BASELINE config 5): name -> (K, N)
+LLAMA70B = {"q": (8192, 8192), "k": (8192, 1024), "v": (8192, 1024), "o": (8192, 8192),
+            "gate": (8192, 28672), "up": (8192, 28672), "down": (28672, 8192)}
+LLAMA8B = {"q": (4096, 4096), "k": (4096, 1024), "v": (4096, 1024), "o": (4096, 4096),
+           "gate": (4096, 14336), "up": (4096, 14336), "down": (14336, 4096)}
 
 
 def peaks():
@@ -47,6 +70,11 @@ def peaks():
         return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
                 "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def traffic(key):
+    v = NCU_TRAFFIC.get(key)
+    return None if v is None else {"dram_bytes_per_launch": v[0], "source": v[1]}
 
 
 class ClockSampler:
@@ -118,6 +146,381 @@ def time_region(torch, fn, reps):
     return start.elapsed_time(end)
 
 
+def capture_graph(torch, stream, body):
+    """Runs body once on `stream` (warm-up; also lets the boundary see the weights as constants), then
+    captures it.  Must be called with `stream` current."""
+    body()
+    stream.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        body()
+    return g
+
+
+# ---- synthetic weights and the in-bench check ---------------------------------------------------------
+def device_woq_weights(torch, _capi, dev, k, n, seed, gs=GS):
+    """Synthetic int4 weights made on the device from a seed: uniform nibbles in [-8, 7], fp32 group scales
+    around 0.01 (the magnitude max|w|/7 of N(0, 0.02) weights gives), packed by the repack kernel."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    q = torch.randint(-8, 8, (n, k), generator=g, device=dev, dtype=torch.int8)
+    scales = (torch.rand(k // gs, n, generator=g, device=dev) * 0.006 + 0.007).contiguous()
+    packed = _capi.woq_repack_weight(q)
+    del q
+    return packed, scales
+
+
+def device_int8_weights(torch, dev, k, n, seed):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    w = torch.randint(-127, 128, (n, k), generator=g, device=dev, dtype=torch.int8)
+    ws = (torch.rand(n, generator=g, device=dev) * 2e-4 + 4e-4).contiguous()
+    return w, ws
+
+
+def seeded_x(torch, dev, m, k, seed):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    return torch.randn(m, k, generator=g, device=dev).to(torch.bfloat16)
+
+
+def check_woq_sample(torch, x, packed, scales, bias, y, what, ncols=64, nrows=16):
+    """Plain fp32 torch evaluation of sampled output columns of y = x . dq(W) + bias straight from the packed
+    words (nibble i of word j of row n is element k = 8j + i; two's complement; dq = q * s[k // gs, n]),
+    compared with the kernel's output.  Independent of the library's kernels."""
+    n = packed.shape[0]
+    k = packed.shape[1] * 8
+    cols = torch.linspace(0, n - 1, ncols, device=x.device).long().unique()
+    rows = torch.linspace(0, x.shape[0] - 1, min(nrows, x.shape[0]), device=x.device).long().unique()
+    words = packed[cols].long() & 0xFFFFFFFF                                    # [C, K/8]
+    shifts = torch.arange(8, device=x.device) * 4
+    nib = (words.unsqueeze(-1) >> shifts) & 0xF                                 # [C, K/8, 8]
+    qv = torch.where(nib >= 8, nib - 16, nib).reshape(len(cols), k).float()
+    gs = k // scales.shape[0]
+    dq = qv * scales.float()[:, cols].t().repeat_interleave(gs, dim=1)
+    ref = x[rows].float() @ dq.t()
+    if bias is not None:
+        ref = ref + bias.float()[cols]
+    got = y[rows][:, cols].float()
+    err = float((got - ref).norm() / ref.norm().clamp(min=1e-6))
+    assert err < 1e-2, f"{what}: kernel output differs from the fp32 check (relative Frobenius error {err:.3e})"
+    return err
+
+
+# ---- weight-only int4 cases ------------------------------------------------------------------------------
+def woq_kernel_name(m, k, n):
+    """The dispatcher's choice for a group-128, 16-byte aligned WOQ problem (csrc/api.cu)."""
+    if m <= 16:
+        return "woq_streamk_kernel" if (m <= 4 and n * k // 2 >= (48 << 20)) else "woq_stream_kernel"
+    return "woq_tcgen05_kernel"
+
+
+def bench_woq_case(torch, _capi, lib, dev, stream, sptr, steps, pk, m, k, n, label, copies_factor=2.0, reps=None):
+    """One weight-only int4 linear y = x[m,k] . dq(W)[k,n] + bias (fp32 scales per group of 128, bf16 bias),
+    rotating over enough weight copies to exceed L2.  Small m is HBM-bound (algorithmic GB/s against the
+    HBM roofline); larger m is reported against both rooflines, the binding one named."""
+    import ctypes as C
+    w_bytes = n * k // 2 + (k // GS) * n * 4
+    alg_bytes = w_bytes + m * k * 2 + m * n * 2 + n * 2
+    copies = max(2, -(-int(copies_factor * L2_BYTES) // w_bytes))
+    packed0, scales0 = device_woq_weights(torch, _capi, dev, k, n, seed=k + n)
+    xs = seeded_x(torch, dev, m, k, seed=m)
+    bs = (torch.randn(n, generator=torch.Generator(device=dev).manual_seed(7), device=dev) * 0.01).to(torch.bfloat16)
+    ws = _capi.woq_workspace(lib.zt_woq_linear_workspace_bytes(m, n, k), dev)
+    arglist, keep = [], []
+    for i in range(copies):
+        wq, sc = (packed0, scales0) if i == 0 else (packed0.clone(), scales0.clone())
+        y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        a = _capi.WoqLinearArgs()
+        a.x, a.M, a.K, a.N = xs.data_ptr(), m, k, n
+        a.wq, a.scales, a.zeros = wq.data_ptr(), sc.data_ptr(), None
+        a.scale_dtype, a.n_groups = _capi.ZT_F32, k // GS
+        a.bias, a.bias_dtype = bs.data_ptr(), _capi.ZT_BF16
+        a.y, a.workspace, a.workspace_bytes, a.algo = y.data_ptr(), ws.data_ptr(), ws.numel(), _capi.ZT_ALGO_AUTO
+        arglist.append(a)
+        keep.append((wq, sc, y))
+
+    def one_pass():
+        for a in arglist:
+            _capi.check(lib.zt_woq_linear(C.byref(a), sptr))
+
+    g = capture_graph(torch, stream, one_pass)
+    err = check_woq_sample(torch, xs, packed0, scales0, bs, keep[0][2], label)
+    err = max(err, check_woq_sample(torch, xs, keep[-1][0], keep[-1][1], bs, keep[-1][2], label))
+    for _ in range(3):
+        g.replay()
+    reps = reps or max(steps, 10)
+    ms = time_region(torch, g.replay, reps) / (reps * copies)
+    gbs = alg_bytes / (ms * 1e-3) / 1e9
+    tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    t_hbm, t_tensor = alg_bytes / (pk["hbm_gbs"] * 1e9), 2.0 * m * n * k / (pk["bf16_tflops"] * 1e12)
+    kernel = woq_kernel_name(m, k, n)
+    out = {"workload": f"{label}: WOQ int4 (group 128, fp32 scales) M={m} K={k} N={n}, bf16 bias",
+           "kernel": kernel, "us_per_call": round(ms * 1e3, 3), "l2": f"rotating over {copies} weight copies",
+           "launch": "CUDA graph, back-to-back", "checked": f"sampled columns vs fp32 torch, rel. error {err:.1e}",
+           "algorithmic_bytes": alg_bytes, "hbm": {"achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                                   "frac": round(gbs / pk["hbm_gbs"], 4)},
+           "tensor": {"achieved": round(tf, 1), "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                      "frac": round(tf / pk["bf16_tflops"], 4)},
+           "bound": "hbm" if t_hbm >= t_tensor else "tensor",
+           "peak_note": f"STREAM-style copy / cuBLAS bf16 burst, {pk['source']}",
+           "traffic": traffic(f"{kernel}/{k}x{n}_M{m}")}
+    b = out[out["bound"]]
+    out.update({"achieved": b["achieved"], "peak": b["peak"], "unit": b["unit"], "frac": b["frac"]})
+    del keep
+    return out
+
+
+def bench_woq(torch, _capi, lib, dev, stream, sptr, steps, pk, quick):
+    cases = {"woq_decode": (1, 4096, 4096, "BASELINE config 1 at M=1"),
+             "woq_config1_m128": (128, 4096, 4096, "BASELINE config 1 at M=128"),
+             "woq_decode_large_layer": (1, 8192, 28672, "BASELINE config 5 up-projection (unsharded) at M=1"),
+             "woq_prefill": (2048, 4096, 4096, "BASELINE config 3 q-projection at M=2048")}
+    if quick:
+        cases = {k: cases[k] for k in ("woq_decode", "woq_decode_large_layer")}
+    return {name: bench_woq_case(torch, _capi, lib, dev, stream, sptr, steps, pk, m, k, n, label)
+            for name, (m, k, n, label) in cases.items()}
+
+
+def bench_layer(torch, _capi, lib, dev, stream, sptr, pk, shapes, batches, label, reps=5):
+    """A decoder layer's WOQ int4 projections, one launch each, per M: each projection's time (its own graph,
+    weights rotating over copies larger than L2), the layer's sum, algorithmic bytes per second (decode) or
+    flops per second (prefill)."""
+    import ctypes as C
+    weights = {}
+    for k, n in set(shapes.values()):
+        w_bytes = n * k // 2 + (k // GS) * n * 4
+        copies = max(2, -(-int(1.5 * L2_BYTES) // w_bytes))
+        packed0, scales0 = device_woq_weights(torch, _capi, dev, k, n, seed=k + n)
+        weights[(k, n)] = [(packed0, scales0)] + [(packed0.clone(), scales0.clone()) for _ in range(copies - 1)]
+    out = {}
+    for m in batches:
+        total_us, total_bytes, total_flops, per_proj = 0.0, 0, 0.0, {}
+        for name, (k, n) in shapes.items():
+            xs = seeded_x(torch, dev, m, k, seed=m + k)
+            bs = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+            ws = _capi.woq_workspace(lib.zt_woq_linear_workspace_bytes(m, n, k), dev)
+            ys = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            arglist = []
+            for wq, sc in weights[(k, n)]:
+                a = _capi.WoqLinearArgs()
+                a.x, a.M, a.K, a.N = xs.data_ptr(), m, k, n
+                a.wq, a.scales, a.zeros = wq.data_ptr(), sc.data_ptr(), None
+                a.scale_dtype, a.n_groups = _capi.ZT_F32, k // GS
+                a.bias, a.bias_dtype = bs.data_ptr(), _capi.ZT_BF16
+                a.y, a.workspace, a.workspace_bytes, a.algo = ys.data_ptr(), ws.data_ptr(), ws.numel(), _capi.ZT_ALGO_AUTO
+                arglist.append(a)
+
+            def one_pass():
+                for a in arglist:
+                    _capi.check(lib.zt_woq_linear(C.byref(a), sptr))
+
+            g = capture_graph(torch, stream, one_pass)
+            check_woq_sample(torch, xs, weights[(k, n)][-1][0], weights[(k, n)][-1][1], bs, ys, f"{label} {name} M={m}")
+            g.replay()
+            us = time_region(torch, g.replay, reps) * 1e3 / (reps * len(arglist))
+            byts = n * k // 2 + (k // GS) * n * 4 + m * k * 2 + m * n * 2 + n * 2
+            total_us += us
+            total_bytes += byts
+            total_flops += 2.0 * m * n * k
+            per_proj[name] = round(us, 2)
+        entry = {"layer_us": round(total_us, 2), "per_projection_us": per_proj}
+        if m <= 64:
+            gbs = total_bytes / (total_us * 1e-6) / 1e9
+            entry.update({"algorithmic_GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / pk["hbm_gbs"], 4)})
+        else:
+            tf = total_flops / (total_us * 1e-6) / 1e12
+            entry.update({"TFLOPps": round(tf, 1), "frac_of_bf16_peak": round(tf / pk["bf16_tflops"], 4)})
+        out[f"M={m}"] = entry
+    del weights
+    return {"workload": f"{label}: seven WOQ int4 (group 128) projections, one launch each, weights not in L2; every "
+                        "operand set checked on sampled columns before timing", "per_batch": out}
+
+
+def bench_moe_config(torch, _capi, dev, pk):
+    """BASELINE config 4: Mixtral-style int4 expert FFN, 8 experts, top-2 over 256 tokens, hidden 4096, ffn 14336."""
+    t, h, inter, e, topk, gs = 256, 4096, 14336, 8, 2, 128
+    g = torch.Generator(device=dev).manual_seed(3)
+    x = torch.randn(t, h, generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn(t, e, generator=g, device=dev)
+    wts, ids = torch.topk(torch.softmax(logits, dim=-1), topk, dim=-1)
+    wts = (wts / wts.sum(dim=-1, keepdim=True)).float().contiguous()
+    ids = ids.to(torch.int32).contiguous()
+    w13 = torch.randint(-2**31, 2**31 - 1, (e, 2 * inter, h // 8), generator=g, device=dev, dtype=torch.int32)
+    s13 = (torch.rand(e, h // gs, 2 * inter, generator=g, device=dev) * 0.006 + 0.007).contiguous()
+    w2 = torch.randint(-2**31, 2**31 - 1, (e, h, inter // 8), generator=g, device=dev, dtype=torch.int32)
+    s2 = (torch.rand(e, inter // gs, h, generator=g, device=dev) * 0.006 + 0.007).contiguous()
+    for _ in range(2):
+        _capi.moe_woq(x, wts, ids, w13, s13, w2, s2)
+    torch.cuda.synchronize()
+    reps = 5
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        _capi.moe_woq(x, wts, ids, w13, s13, w2, s2)
+    end.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(end) * 1e3 / reps
+    w_bytes = w13.numel() * 4 + w2.numel() * 4 + s13.numel() * 4 + s2.numel() * 4
+    flops = 2.0 * t * topk * (h * 2 * inter + inter * h)
+    return {"workload": "BASELINE config 4: int4 MoE FFN, 8 experts, top-2, 256 tokens, hidden 4096, ffn 14336 "
+                        "(routing, grouping, two grouped tcgen05 GEMMs, SiLU-mul, combine)",
+            "us_per_call": round(us, 1), "weight_bytes": w_bytes, "weight_GBps": round(w_bytes / (us * 1e-6) / 1e9, 1),
+            "frac_of_hbm_peak": round(w_bytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 4),
+            "TFLOPps": round(flops / (us * 1e-6) / 1e12, 1),
+            "l2": "705 MB of expert weights per call exceed L2", "launch": "plain launches on the current stream"}
+
+
+# ---- config 5: tensor-parallel decoder layer ----------------------------------------------------------------
+def make_layer_params(torch, _capi, dev, kind, shapes, seed0):
+    """Unsharded synthetic parameters of a decoder layer, identical on every rank (same seeds)."""
+    full = {}
+    for i, (name, (k, n)) in enumerate(shapes.items()):
+        if kind == "woq":
+            packed, scales = device_woq_weights(torch, _capi, dev, k, n, seed=seed0 + i)
+            full[name] = (packed.t(), scales, None, None)
+        else:
+            w, ws = device_int8_weights(torch, dev, k, n, seed=seed0 + i)
+            full[name] = (w, ws, None)
+    return full
+
+
+def bench_tp_layer(torch, dist, dev, stream, pk, world, rank, batches, kinds, reps=10):
+    """BASELINE config 5: the projections of a Llama-3-70B decoder layer sharded over `world` ranks
+    (zentorch_b200.tp.DecoderLayerLinears: fused q/k/v and gate/up column-parallel, o and down row-parallel
+    with an NCCL all-reduce each), one CUDA graph per step, two independent weight sets alternating so that a
+    step never finds its weights in L2.  Before timing, the sharded result is compared with the unsharded
+    layer computed on every rank from the same seeds.  Device-timed, max over ranks; the all-reduces alone
+    are timed the same way and reported separately."""
+    from zentorch_b200 import _capi, tp
+    hidden, inter = 8192, 28672
+    out = {}
+    for kind in kinds:
+        fulls = [make_layer_params(torch, _capi, dev, kind, LLAMA70B, seed0=100 * (s + 1)) for s in range(2)]
+        layers = [tp.DecoderLayerLinears(kind, f, rank, world) for f in fulls]
+        ref_layer = tp.DecoderLayerLinears(kind, fulls[0], 0, 1) if world > 1 else None
+        if world == 1:
+            fulls = None      # the shards of a single rank are the parameters themselves
+        w_bytes = layers[0].weight_bytes()
+        total_nk = sum(k * n for k, n in LLAMA70B.values())
+        res = {}
+        for m in batches:
+            x = seeded_x(torch, dev, m, hidden, seed=m)
+            attn_full = seeded_x(torch, dev, m, hidden, seed=m + 1)
+            attn = attn_full[:, rank * hidden // world:(rank + 1) * hidden // world].contiguous()
+            with torch.cuda.stream(stream):
+                # parity of the sharded step against the unsharded one (same seeds on every rank)
+                if ref_layer is not None:
+                    _, y_ref = ref_layer(x, attn_full)
+                    _, y_tp = layers[0](x, attn)
+                    stream.synchronize()
+                    err = float((y_tp.float() - y_ref.float()).norm() / y_ref.float().norm())
+                    assert err < 3e-2, f"tensor-parallel {kind} M={m}: differs from the unsharded layer ({err:.3e})"
+                else:
+                    err = 0.0
+
+                def step():
+                    for layer in layers:
+                        layer(x, attn)
+
+                g = capture_graph(torch, stream, step)
+                g.replay()
+                stream.synchronize()
+                if world > 1:
+                    dist.barrier()
+                ms = time_region(torch, g.replay, reps) / (reps * len(layers))
+                # the collectives alone: two all-reduces of [M, hidden] bf16 per layer
+                if world > 1:
+                    buf = torch.zeros(m, hidden, dtype=torch.bfloat16, device=dev)
+
+                    def coll():
+                        for _ in range(2 * len(layers)):
+                            dist.all_reduce(buf)
+
+                    gc = capture_graph(torch, stream, coll)
+                    gc.replay()
+                    stream.synchronize()
+                    dist.barrier()
+                    ms_coll = time_region(torch, gc.replay, reps) / (reps * len(layers))
+                else:
+                    ms_coll = 0.0
+            t = torch.tensor([ms, ms_coll], device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms, ms_coll = float(t[0]), float(t[1])
+            entry = {"layer_us": round(ms * 1e3, 2), "collective_us": round(ms_coll * 1e3, 2),
+                     "vs_unsharded_rel_error": round(err, 5), "layers_timed": reps * len(layers)}
+            if m <= 64:
+                gbs = w_bytes / (ms * 1e-3) / 1e9
+                entry.update({"per_gpu_weight_GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / pk["hbm_gbs"], 4)})
+            else:
+                tops = 2.0 * m * total_nk / (ms * 1e-3) / 1e12
+                peak = pk["bf16_tflops"] * (2.0 if kind == "int8" else 1.0) * world
+                entry.update({"total_Tops": round(tops, 1), "frac_of_tensor_peak": round(tops / peak, 4)})
+            res[f"M={m}"] = entry
+        out[kind] = {"weight_bytes_per_gpu": w_bytes, "per_batch": res}
+        del layers, fulls, ref_layer
+        torch.cuda.empty_cache()
+    return {"workload": f"BASELINE config 5: Llama-3-70B decoder-layer projections, tensor-parallel over {world} GPU(s): "
+                        "fused q/k/v and gate/up column-parallel, o and down row-parallel + NCCL all-reduce of "
+                        "[M, 8192] bf16; one CUDA graph per step; two weight sets alternate (> L2)",
+            "scaling": "strong", "n_gpus": world, "kinds": out,
+            "collective": "ncclAllReduce x 2 per layer (after o and after down)" if world > 1 else "none"}
+
+
+def bench_e2e(torch, dev, sets, steps, world):
+    """The user-facing call with host buffers: pinned x -> device, op, y -> pinned host, every step."""
+    ops = torch.ops.zentorch
+    s = sets[0]
+    x_host = s["x"].cpu().pin_memory()
+    y_host = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty_like(s["x"])
+
+    def step(i):
+        st = sets[i % len(sets)]
+        x_dev.copy_(x_host, non_blocking=True)
+        y = ops.zentorch_dynamic_qlinear_ext(x_dev, st["w"], st["ws"], st["b"], st["rowsum"], act_quant="u8_asym",
+                                             post_op="silu")
+        y_host.copy_(y, non_blocking=True)
+
+    for i in range(2 * len(sets)):
+        step(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        step(i)
+    end.record()
+    torch.cuda.synchronize()
+    return {"ms": start.elapsed_time(end), "h2d": M * K * 2, "d2h": M * N * 2}
+
+
+def bench_e2e_tp(torch, dist, dev, layer, m, steps, world):
+    """End to end for the sharded layer: the step's input rows come from pinned host memory, the layer's
+    output goes back to pinned host memory, every step; eager launches through torch.ops.zentorch."""
+    hidden = 8192
+    x_host = torch.randn(m, hidden, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).pin_memory()
+    y_host = torch.empty(m, hidden, dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty(m, hidden, dtype=torch.bfloat16, device=dev)
+    rank = dist.get_rank() if world > 1 else 0
+    lo, hi = rank * hidden // world, (rank + 1) * hidden // world
+
+    def step():
+        x_dev.copy_(x_host, non_blocking=True)
+        _, y = layer(x_dev, x_dev[:, lo:hi].contiguous())
+        y_host.copy_(y, non_blocking=True)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    end.record()
+    torch.cuda.synchronize()
+    return {"ms": start.elapsed_time(end), "h2d": m * hidden * 2, "d2h": m * hidden * 2}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -135,8 +538,9 @@ def run_ours(args):
     assert zentorch_b200.is_supported_device(), "bench.py needs an sm_100 GPU; there is no fallback path"
     pk = peaks()
     lib = _capi.lib()
+    steps, warmup = args.steps, max(args.warmup, 3)
 
-    # ---- operands: enough distinct sets that the rotation exceeds L2 ---------------------------------
+    # ---- config 2 operands: enough distinct sets that the rotation exceeds L2 ---------------------------
     set_bytes = N * K + M * K * 2 + M * N * 2
     n_sets = max(4, -(-int(1.5 * L2_BYTES) // set_bytes))
     x0, w0, ws0, b0 = make_operands(torch, dev, seed=rank)
@@ -164,27 +568,18 @@ def run_ours(args):
         for i in range(CALLS_PER_STEP):
             _capi.check(lib.zt_dynamic_qlinear(C.byref(arglist[i % n_sets]), sptr))
 
-    def capture(body):
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(stream):
-            body()
-            stream.synchronize()
-            with torch.cuda.graph(g, stream=stream):
-                body()
-        return g
-
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     with torch.cuda.stream(stream):
-        graph_u8 = capture(lambda: one_pass(arg_u8))
-        graph_s8 = capture(lambda: one_pass(arg_s8))
-        for _ in range(max(args.warmup, 3)):
+        graph_u8 = capture_graph(torch, stream, lambda: one_pass(arg_u8))
+        graph_s8 = capture_graph(torch, stream, lambda: one_pass(arg_s8))
+        for _ in range(warmup):
             graph_u8.replay()
         stream.synchronize()
         if world > 1:
             dist.barrier()
-        ms = time_region(torch, graph_u8.replay, args.steps)
+        ms = time_region(torch, graph_u8.replay, steps)
         if world > 1:
             dist.barrier()
         t = torch.tensor([ms], device=dev)
@@ -193,7 +588,7 @@ def run_ours(args):
         ms_max = float(t.item())
         for _ in range(3):
             graph_s8.replay()
-        ms_s8 = time_region(torch, graph_s8.replay, args.steps)
+        ms_s8 = time_region(torch, graph_s8.replay, steps)
 
         # ---- roofline of the dominant kernel: the tcgen05 GEMM alone ---------------------------------
         pre = []
@@ -214,331 +609,143 @@ def run_ours(args):
                 _capi.check(lib.zt_dynamic_quantize(s["x"].data_ptr(), _capi.ZT_BF16, M, K, _capi.ZT_ACT_U8_ASYM,
                                                     q.data_ptr(), sc.data_ptr(), zp.data_ptr(), sptr))
 
-        graph_gemm, graph_quant = capture(gemm_pass), capture(quant_pass)
+        graph_gemm, graph_quant = capture_graph(torch, stream, gemm_pass), capture_graph(torch, stream, quant_pass)
         for _ in range(3):
             graph_gemm.replay()
             graph_quant.replay()
-        ms_gemm = time_region(torch, graph_gemm.replay, args.steps) / (args.steps * CALLS_PER_STEP)
-        ms_quant = time_region(torch, graph_quant.replay, args.steps) / (args.steps * CALLS_PER_STEP)
+        ms_gemm = time_region(torch, graph_gemm.replay, steps) / (steps * CALLS_PER_STEP)
+        ms_quant = time_region(torch, graph_quant.replay, steps) / (steps * CALLS_PER_STEP)
 
-        # ---- weight-only int4 decode GEMV (config 1, M = 1), HBM-bound ---------------------------------
-        woq = bench_woq(torch, _capi, lib, dev, stream, sptr, args.steps, pk) if rank == 0 else {}
-        layer_cfg = bench_layer_configs(torch, _capi, lib, dev, stream, sptr, pk) if rank == 0 else None
-    moe_cfg = bench_moe_config(torch, _capi, dev, pk) if rank == 0 else None
+        solo = rank == 0 and world == 1
+        woq = bench_woq(torch, _capi, lib, dev, stream, sptr, steps, pk, args.quick) if solo else {}
+        layer8b = (bench_layer(torch, _capi, lib, dev, stream, sptr, pk, LLAMA8B, (1, 8, 32, 64, 2048),
+                               "BASELINE config 3: Llama-3-8B decoder layer") if solo and not args.quick else None)
+        layer70b = (bench_layer(torch, _capi, lib, dev, stream, sptr, pk, LLAMA70B, (1, 32, 4096),
+                                "BASELINE config 5 (unsharded): Llama-3-70B decoder layer", reps=3)
+                    if solo and not args.quick else None)
+    moe_cfg = bench_moe_config(torch, _capi, dev, pk) if solo and not args.quick else None
 
     # ---- end to end through torch.ops with host buffers ---------------------------------------------------
-    e2e = bench_e2e(torch, dev, sets, args.steps, world)
-    tp_mlp = bench_tp_mlp(torch, dist, dev, args.steps, world)
+    e2e = bench_e2e(torch, dev, sets, steps, world)
+    del sets, pre, arg_u8, arg_s8, graph_u8, graph_s8, graph_gemm, graph_quant
+    torch.cuda.empty_cache()
+    tp_batches = (1, 32) if args.quick else (1, 32, 4096)
+    tp_layer = bench_tp_layer(torch, dist, dev, stream, pk, world, rank, tp_batches, ("woq", "int8"),
+                              reps=max(steps // 2, 3))
+    e2e_tp = None
+    if world > 1:
+        from zentorch_b200 import tp
+        layer = tp.DecoderLayerLinears("int8", make_layer_params(torch, _capi, dev, "int8", LLAMA70B, 100), rank, world)
+        e2e_tp = bench_e2e_tp(torch, dist, dev, layer, 4096, max(steps, 5), world)
+        te = torch.tensor([e2e["ms"], e2e_tp["ms"]], device=dev)
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e["ms"], e2e_tp["ms"] = float(te[0]), float(te[1])
+        del layer
     clocks = sampler.stop() if rank == 0 else None
     torch.cuda.synchronize()
     status = _capi.poll_device_status()
     assert status == 0, f"a kernel reported a bounded-wait timeout (code {status})"
 
-    total_calls = args.steps * CALLS_PER_STEP
-    value = world * total_calls * OPS_PER_CALL / (ms_max * 1e-3) / 1e12
-    if world > 1:
-        te = torch.tensor([e2e["ms"]], device=dev)
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e["ms"] = float(te.item())
-    e2e_value = world * args.steps * OPS_PER_CALL / (e2e["ms"] * 1e-3) / 1e12
+    total_calls = steps * CALLS_PER_STEP
+    replica_value = world * total_calls * OPS_PER_CALL / (ms_max * 1e-3) / 1e12
+    replica_e2e = world * steps * OPS_PER_CALL / (e2e["ms"] * 1e-3) / 1e12
 
     if rank == 0:
         int8_peak = 2.0 * pk["bf16_tflops"]
         cpu = cpu_baseline_sample()
-        line = {
-            "metric": METRIC, "value": round(value, 2), "unit": "TOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_max / args.steps, 5), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "s8/u8 x s8 -> s32, fp32 epilogue", "data": "synthetic",
-            "config": {
-                "workload": f"BASELINE config 2: dynamic int8 linear M={M} K={K} N={N}, per-token u8 asymmetric "
-                            "activations, per-channel s8 weights, fp32 bias, fused SiLU",
-                "calls_per_step": CALLS_PER_STEP,
-                "l2": f"rotating over {n_sets} operand sets ({n_sets * set_bytes / 2**20:.0f} MiB > L2)",
-                "parallelism": f"dp{world} (independent batches per GPU, no collective on the data path)",
-                "launch": "CUDA graph of one step",
-            },
-            "variants": {
-                "s8_symmetric_no_postop (the reference op zentorch_dynamic_qlinear)": {
-                    "value": round(total_calls * OPS_PER_CALL / (ms_s8 * 1e-3) / 1e12, 2), "unit": "TOP/s"},
-                "quant_kernel_us": round(ms_quant * 1e3, 3), "gemm_kernel_us": round(ms_gemm * 1e3, 3),
-            },
-            "roofline": {
-                "kernel": "int8_tcgen05_kernel", "bound": "tensor",
-                "achieved": round(OPS_PER_CALL / (ms_gemm * 1e-3) / 1e12, 2), "peak": round(int8_peak, 1),
-                "unit": "TOP/s", "frac": round(OPS_PER_CALL / (ms_gemm * 1e-3) / 1e12 / int8_peak, 4),
-                "peak_note": f"2 x cuBLAS bf16 burst ({pk['bf16_tflops']} TF/s, {pk['source']}): kind::i8 issues at "
-                             "twice the kind::f16 rate",
-                "frac_of_sustained_peak": round(OPS_PER_CALL / (ms_gemm * 1e-3) / 1e12 / (2.0 * pk["bf16_tflops_sustained"]), 4),
-                "traffic": None,
-            },
-            "woq_decode": woq.get("woq_decode"), "woq_decode_large_layer": woq.get("woq_decode_large_layer"),
-            "woq_prefill": woq.get("woq_prefill"), "tp_mlp": tp_mlp,
-            "llama8b_layer": layer_cfg, "moe_int4": moe_cfg,
-            "cpu_baseline": cpu,
-            "e2e": {"value": round(e2e_value, 3), "unit": "TOP/s", "h2d_bytes_per_step": e2e["h2d"],
-                    "d2h_bytes_per_step": e2e["d2h"], "calls_per_step": 1,
-                    "api": "torch.ops.zentorch.zentorch_dynamic_qlinear_ext(act_quant='u8_asym', post_op='silu')"},
-            "gpu_launches": total_calls * 2,
-            "clocks": clocks,
+        gemm_tops = OPS_PER_CALL / (ms_gemm * 1e-3) / 1e12
+        roofline = {
+            "kernel": "int8_tcgen05_kernel", "bound": "tensor", "achieved": round(gemm_tops, 2),
+            "peak": round(int8_peak, 1), "unit": "TOP/s", "frac": round(gemm_tops / int8_peak, 4),
+            "peak_note": f"2 x cuBLAS bf16 burst ({pk['bf16_tflops']} TF/s, {pk['source']}): kind::i8 issues at "
+                         "twice the kind::f16 rate; no int8 peak is measured",
+            "frac_of_sustained_peak": round(gemm_tops / (2.0 * pk["bf16_tflops_sustained"]), 4),
+            "algorithmic_bytes": N * K + M * K + M * N * 2 + N * 12,
+            "traffic": NCU_TRAFFIC["int8_tcgen05_kernel/config2"][0],
+            "traffic_source": NCU_TRAFFIC["int8_tcgen05_kernel/config2"][1],
         }
+        config2 = {
+            "workload": f"BASELINE config 2: dynamic int8 linear M={M} K={K} N={N}, per-token u8 asymmetric "
+                        "activations, per-channel s8 weights, fp32 bias, fused SiLU",
+            "calls_per_step": CALLS_PER_STEP,
+            "l2": f"rotating over {n_sets} operand sets ({n_sets * set_bytes / 2**20:.0f} MiB > L2)",
+            "launch": "CUDA graph of one step",
+        }
+        variants = {
+            "s8_symmetric_no_postop (the reference op zentorch_dynamic_qlinear)": {
+                "value": round(total_calls * OPS_PER_CALL / (ms_s8 * 1e-3) / 1e12, 2), "unit": "TOP/s"},
+            "quant_kernel_us": round(ms_quant * 1e3, 3), "gemm_kernel_us": round(ms_gemm * 1e3, 3),
+        }
+        if world == 1:
+            line = {
+                "metric": METRIC, "value": round(replica_value, 2), "unit": "TOP/s", "n_gpus": world, "steps": steps,
+                "warmup": warmup, "ms_per_step": round(ms_max / steps, 5), "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "s8/u8 x s8 -> s32, fp32 epilogue", "data": "synthetic",
+                "config": dict(config2, parallelism="1 GPU"),
+                "e2e": {"value": round(replica_e2e, 3), "unit": "TOP/s", "h2d_bytes_per_step": e2e["h2d"],
+                        "d2h_bytes_per_step": e2e["d2h"], "calls_per_step": 1,
+                        "api": "torch.ops.zentorch.zentorch_dynamic_qlinear_ext(act_quant='u8_asym', post_op='silu')"},
+                "gpu_launches": total_calls * 2,
+            }
+        else:
+            t70 = tp_layer["kinds"]["int8"]["per_batch"].get("M=4096") or next(iter(tp_layer["kinds"]["int8"]["per_batch"].values()))
+            m_head = 4096 if "M=4096" in tp_layer["kinds"]["int8"]["per_batch"] else tp_batches[-1]
+            total_nk = sum(k * n for k, n in LLAMA70B.values())
+            value = 2.0 * m_head * total_nk / (t70["layer_us"] * 1e-6) / 1e12
+            e2e_val = 2.0 * 4096 * total_nk * max(steps, 5) / (e2e_tp["ms"] * 1e-3) / 1e12
+            line = {
+                "metric": METRIC_TP, "value": round(value, 2), "unit": "TOP/s", "n_gpus": world,
+                "steps": t70["layers_timed"],
+                "warmup": warmup, "ms_per_step": round(t70["layer_us"] * 1e-3, 5), "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "s8 x s8 -> s32, fp32 epilogue", "data": "synthetic",
+                "config": {"workload": f"BASELINE config 5: Llama-3-70B decoder-layer projections (q,k,v,o,gate,up,down), "
+                                       f"int8 dynamic (per-token s8 activations), M={m_head}, tensor-parallel over "
+                                       f"{world} GPUs; a step is one layer (4 launches of the quantise+GEMM pair, "
+                                       "2 all-reduces)",
+                           "l2": "two weight sets alternate (> L2 per GPU)", "parallelism": f"tp{world}",
+                           "launch": "CUDA graph of one step", "collective_us": t70["collective_us"]},
+                "e2e": {"value": round(e2e_val, 3), "unit": "TOP/s", "h2d_bytes_per_step": e2e_tp["h2d"],
+                        "d2h_bytes_per_step": e2e_tp["d2h"],
+                        "api": "zentorch_b200.tp.DecoderLayerLinears over torch.ops.zentorch.zentorch_dynamic_qlinear"},
+                "gpu_launches": t70["layers_timed"] * 8,
+                "replicas_config2": {"value": round(replica_value, 2), "unit": "TOP/s", "scaling": "weak",
+                                     "e2e_value": round(replica_e2e, 3), "config": config2,
+                                     "note": "independent config-2 batches per GPU, no collective on the data path"},
+            }
+        line.update({
+            "variants": variants, "roofline": roofline,
+            "woq_decode": woq.get("woq_decode"), "woq_config1_m128": woq.get("woq_config1_m128"),
+            "woq_decode_large_layer": woq.get("woq_decode_large_layer"), "woq_prefill": woq.get("woq_prefill"),
+            "llama8b_layer": layer8b, "llama70b_projections": layer70b, "moe_int4": moe_cfg, "tp_layer": tp_layer,
+            "cpu_baseline": cpu, "clocks": clocks,
+        })
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
-def device_woq_weights(torch, _capi, dev, k, n, seed, gs=128):
-    """Synthetic int4 weights made on the device: uniform nibbles in [-8, 7], fp32 group scales around
-    0.01 (the magnitude max|w|/7 of N(0, 0.02) weights gives), packed by the repack kernel."""
-    g = torch.Generator(device=dev).manual_seed(seed)
-    q = torch.randint(-8, 8, (n, k), generator=g, device=dev, dtype=torch.int8)
-    scales = (torch.rand(k // gs, n, generator=g, device=dev) * 0.006 + 0.007).contiguous()
-    packed = _capi.woq_repack_weight(q)
-    del q
-    return packed, scales
-
-
-def bench_woq_case(torch, _capi, lib, dev, stream, sptr, steps, pk, m, k, n, label):
-    """One weight-only int4 linear y = x[m,k] . dq(W)[k,n] + bias (fp32 scales per group of 128, bf16
-    bias), rotating over enough weight copies to exceed L2.  Small m is HBM-bound (reported as algorithmic
-    GB/s of the HBM roofline), large m tensor-bound (TFLOP/s of the bf16 roofline)."""
-    import ctypes as C
-    gs = 128
-    w_bytes = n * k // 2 + (k // gs) * n * 4
-    alg_bytes = w_bytes + m * k * 2 + m * n * 2 + n * 2
-    copies = max(2, -(-int(2.0 * L2_BYTES) // w_bytes))
-    packed0, scales0 = device_woq_weights(torch, _capi, dev, k, n, seed=0)
-    xs = torch.randn(m, k, device=dev).to(torch.bfloat16)
-    bs = (torch.randn(n, device=dev) * 0.01).to(torch.bfloat16)
-    ws = _capi.woq_workspace(lib.zt_woq_linear_workspace_bytes(m, n, k), dev)
-    arglist, keep = [], []
-    for i in range(copies):
-        wq = packed0.clone()
-        sc = scales0.clone()
-        y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-        a = _capi.WoqLinearArgs()
-        a.x, a.M, a.K, a.N = xs.data_ptr(), m, k, n
-        a.wq, a.scales, a.zeros = wq.data_ptr(), sc.data_ptr(), None
-        a.scale_dtype, a.n_groups = _capi.ZT_F32, k // gs
-        a.bias, a.bias_dtype = bs.data_ptr(), _capi.ZT_BF16
-        a.y, a.workspace, a.workspace_bytes, a.algo = y.data_ptr(), ws.data_ptr(), ws.numel(), _capi.ZT_ALGO_AUTO
-        arglist.append(a)
-        keep.append((wq, sc, y))
-
-    def one_pass():
-        for a in arglist:
-            _capi.check(lib.zt_woq_linear(C.byref(a), sptr))
-
-    g = torch.cuda.CUDAGraph()
-    one_pass()
-    stream.synchronize()
-    with torch.cuda.graph(g, stream=stream):
-        one_pass()
-    for _ in range(3):
-        g.replay()
-    reps = max(steps, 10)
-    ms = time_region(torch, g.replay, reps) / (reps * copies)
-    out = {"workload": f"{label}: WOQ int4 (group 128, fp32 scales) M={m} K={k} N={n}, bf16 bias",
-           "us_per_call": round(ms * 1e3, 3), "l2": f"rotating over {copies} weight copies",
-           "launch": "CUDA graph, back-to-back"}
-    if m <= 16:
-        gbs = alg_bytes / (ms * 1e-3) / 1e9
-        # the dispatcher's rule: TMA-staged stream-K kernel from 48 MB of packed weights, register ring below
-        kernel = "woq_streamk_kernel" if n * k // 2 >= (48 << 20) else "woq_stream_kernel"
-        out.update({"kernel": kernel, "bound": "hbm", "algorithmic_bytes": alg_bytes, "achieved": round(gbs, 1),
-                    "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / pk["hbm_gbs"], 4),
-                    "peak_note": f"STREAM-style copy, {pk['source']}"})
-    else:
-        tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
-        out.update({"kernel": "woq_tcgen05_kernel", "bound": "tensor", "achieved": round(tf, 1),
-                    "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": round(tf / pk["bf16_tflops"], 4),
-                    "peak_note": f"cuBLAS bf16 burst, {pk['source']}"})
-    del keep
-    return out
-
-
-def bench_woq(torch, _capi, lib, dev, stream, sptr, steps, pk):
-    cases = {"woq_decode": (1, 4096, 4096, "BASELINE config 1 at M=1"),
-             "woq_decode_large_layer": (1, 8192, 28672, "BASELINE config 3 layer (70B-class up-projection) at M=1"),
-             "woq_prefill": (2048, 4096, 4096, "BASELINE config 1 at M=2048")}
-    return {name: bench_woq_case(torch, _capi, lib, dev, stream, sptr, steps, pk, m, k, n, label)
-            for name, (m, k, n, label) in cases.items()}
-
-
-def bench_layer_configs(torch, _capi, lib, dev, stream, sptr, pk):
-    """BASELINE config 2: the seven WOQ int4 projections of a Llama-3-8B decoder layer at decode batch
-    M in {1, 8, 32, 64} and prefill M = 2048.  Per M: the layer's summed time, its algorithmic bytes per
-    second (decode) or flops per second (prefill).  Weights rotate over copies larger than L2 in total."""
-    import ctypes as C
-    shapes = [("q", 4096, 4096), ("k", 4096, 1024), ("v", 4096, 1024), ("o", 4096, 4096), ("gate", 4096, 14336),
-              ("up", 4096, 14336), ("down", 14336, 4096)]
-    gs = 128
-    weights = {}
-    for _, k, n in shapes:
-        if (k, n) not in weights:
-            w_bytes = n * k // 2 + (k // gs) * n * 4
-            copies = max(2, -(-int(1.5 * L2_BYTES) // w_bytes))
-            packed0, scales0 = device_woq_weights(torch, _capi, dev, k, n, seed=k + n)
-            weights[(k, n)] = [(packed0.clone(), scales0.clone()) for _ in range(copies)]
-    out = {}
-    for m in (1, 8, 32, 64, 2048):
-        total_us, total_bytes, total_flops = 0.0, 0, 0.0
-        for _, k, n in shapes:
-            xs = torch.randn(m, k, device=dev).to(torch.bfloat16)
-            bs = torch.zeros(n, dtype=torch.bfloat16, device=dev)
-            ws = _capi.woq_workspace(lib.zt_woq_linear_workspace_bytes(m, n, k), dev)
-            ys = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-            arglist = []
-            for wq, sc in weights[(k, n)]:
-                a = _capi.WoqLinearArgs()
-                a.x, a.M, a.K, a.N = xs.data_ptr(), m, k, n
-                a.wq, a.scales, a.zeros = wq.data_ptr(), sc.data_ptr(), None
-                a.scale_dtype, a.n_groups = _capi.ZT_F32, k // gs
-                a.bias, a.bias_dtype = bs.data_ptr(), _capi.ZT_BF16
-                a.y, a.workspace, a.workspace_bytes, a.algo = ys.data_ptr(), ws.data_ptr(), ws.numel(), _capi.ZT_ALGO_AUTO
-                arglist.append(a)
-
-            def one_pass():
-                for a in arglist:
-                    _capi.check(lib.zt_woq_linear(C.byref(a), sptr))
-
-            g = torch.cuda.CUDAGraph()
-            one_pass()
-            stream.synchronize()
-            with torch.cuda.graph(g, stream=stream):
-                one_pass()
-            g.replay()
-            reps = 5
-            us = time_region(torch, g.replay, reps) * 1e3 / (reps * len(arglist))
-            total_us += us
-            total_bytes += n * k // 2 + (k // gs) * n * 4 + m * k * 2 + m * n * 2 + n * 2
-            total_flops += 2.0 * m * n * k
-        entry = {"layer_us": round(total_us, 2)}
-        if m <= 64:
-            gbs = total_bytes / (total_us * 1e-6) / 1e9
-            entry.update({"algorithmic_GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / pk["hbm_gbs"], 4)})
-        else:
-            tf = total_flops / (total_us * 1e-6) / 1e12
-            entry.update({"TFLOPps": round(tf, 1), "frac_of_bf16_peak": round(tf / pk["bf16_tflops"], 4)})
-        out[f"M={m}"] = entry
-    return {"workload": "BASELINE config 2: Llama-3-8B decoder layer, seven WOQ int4 (group 128) projections, "
-                        "one launch each, weights not in L2", "per_batch": out}
-
-
-def bench_moe_config(torch, _capi, dev, pk):
-    """BASELINE config 3: Mixtral-style int4 expert FFN, 8 experts, top-2 over 256 tokens, hidden 4096, ffn 14336."""
-    t, h, inter, e, topk, gs = 256, 4096, 14336, 8, 2, 128
-    g = torch.Generator(device=dev).manual_seed(3)
-    x = torch.randn(t, h, generator=g, device=dev).to(torch.bfloat16)
-    logits = torch.randn(t, e, generator=g, device=dev)
-    wts, ids = torch.topk(torch.softmax(logits, dim=-1), topk, dim=-1)
-    wts = (wts / wts.sum(dim=-1, keepdim=True)).float().contiguous()
-    ids = ids.to(torch.int32).contiguous()
-    w13 = torch.randint(-2**31, 2**31 - 1, (e, 2 * inter, h // 8), generator=g, device=dev, dtype=torch.int32)
-    s13 = (torch.rand(e, h // gs, 2 * inter, generator=g, device=dev) * 0.006 + 0.007).contiguous()
-    w2 = torch.randint(-2**31, 2**31 - 1, (e, h, inter // 8), generator=g, device=dev, dtype=torch.int32)
-    s2 = (torch.rand(e, inter // gs, h, generator=g, device=dev) * 0.006 + 0.007).contiguous()
-    for _ in range(2):
-        _capi.moe_woq(x, wts, ids, w13, s13, w2, s2)
-    torch.cuda.synchronize()
-    reps = 5
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(reps):
-        _capi.moe_woq(x, wts, ids, w13, s13, w2, s2)
-    end.record()
-    torch.cuda.synchronize()
-    us = start.elapsed_time(end) * 1e3 / reps
-    w_bytes = w13.numel() * 4 + w2.numel() * 4 + s13.numel() * 4 + s2.numel() * 4
-    flops = 2.0 * t * topk * (h * 2 * inter + inter * h)
-    return {"workload": "BASELINE config 3: int4 MoE FFN, 8 experts, top-2, 256 tokens, hidden 4096, ffn 14336 "
-                        "(routing, grouping, two grouped tcgen05 GEMMs, SiLU-mul, combine)",
-            "us_per_call": round(us, 1), "weight_bytes": w_bytes, "weight_GBps": round(w_bytes / (us * 1e-6) / 1e9, 1),
-            "frac_of_hbm_peak": round(w_bytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 4),
-            "TFLOPps": round(flops / (us * 1e-6) / 1e12, 1),
-            "l2": "705 MB of expert weights per call exceed L2", "launch": "plain launches on the current stream"}
-
-
-def bench_tp_mlp(torch, dist, dev, steps, world):
-    """Tensor-parallel WOQ MLP at decode size (M=16): up-projection column-parallel [8192 -> 28672/world],
-    SiLU-gated product, down-projection row-parallel [28672/world -> 8192] followed by the NCCL all-reduce.
-    Device-timed per call, max over ranks.  Shards are generated directly (weights are synthetic)."""
-    from zentorch_b200 import _capi, tp
-    m, hidden, inter = 16, 8192, 28672
-    shard = inter // world
-    ops = torch.ops.zentorch
-
-    def shard_params(k, n, seed):
-        packed, scales = device_woq_weights(torch, _capi, dev, k, n, seed)
-        return packed.t(), scales, None, None
-
-    rank = dist.get_rank() if world > 1 else 0
-    gate = tp.ParallelLinear("woq", "column", shard_params(hidden, shard, 10 + rank))
-    up = tp.ParallelLinear("woq", "column", shard_params(hidden, shard, 20 + rank))
-    down = tp.ParallelLinear("woq", "row", shard_params(shard, hidden, 30 + rank))
-    mlp = tp.ParallelMLP(gate, up, down)
-    x = torch.randn(m, hidden, device=dev).to(torch.bfloat16)
-    for _ in range(3):
-        mlp(x)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    reps = max(steps, 10)
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(reps):
-        mlp(x)
-    end.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([start.elapsed_time(end) / reps], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    w_bytes = 3 * (hidden * shard // 2 + (hidden // 128) * shard * 4)
-    us = float(t.item()) * 1e3
-    return {"workload": f"WOQ int4 SiLU-gated MLP {hidden}->{inter}->{hidden}, M={m}, tensor-parallel over {world} GPU(s)",
-            "us_per_call": round(us, 2), "weight_bytes_per_gpu": w_bytes,
-            "weight_stream_gbs_per_gpu": round(w_bytes / (us * 1e-6) / 1e9, 1),
-            "collective": "one NCCL all-reduce of [16, 8192] bf16 per call" if world > 1 else "none"}
-
-
-def bench_e2e(torch, dev, sets, steps, world):
-    """The user-facing call with host buffers: pinned x -> device, op, y -> pinned host, every step."""
-    ops = torch.ops.zentorch
-    s = sets[0]
-    x_host = s["x"].cpu().pin_memory()
-    y_host = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
-    x_dev = torch.empty_like(s["x"])
-
-    def step(i):
-        st = sets[i % len(sets)]
-        x_dev.copy_(x_host, non_blocking=True)
-        y = ops.zentorch_dynamic_qlinear_ext(x_dev, st["w"], st["ws"], st["b"], st["rowsum"], act_quant="u8_asym",
-                                             post_op="silu")
-        y_host.copy_(y, non_blocking=True)
-
-    for i in range(3):
-        step(i)
-    torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for i in range(steps):
-        step(i)
-    end.record()
-    torch.cuda.synchronize()
-    return {"ms": start.elapsed_time(end), "h2d": M * K * 2, "d2h": M * N * 2}
-
-
 def run_profile_case(name):
     """A few plain launches (no CUDA graph) of one kernel on a case that is small enough to profile
-    with `ncu --set full` and still larger than L2:  python bench.py --profile int8_gemm|woq_decode|dynquant"""
+    with `ncu --set full` and still larger than L2:
+        python bench.py --profile int8_gemm|dynquant|woq_decode|woq_decode_small|woq_mid|woq_prefill|moe
+    and `--profile woq_timeline`, which prints where the time of the small-layer decode kernel goes."""
     import ctypes as C
     import torch
     import zentorch_b200  # noqa: F401
     from zentorch_b200 import _capi
-    from _util import make_woq_case
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     lib = _capi.lib()
+
+    def woq_loop(m, k, n, launches, copies=2):
+        x = seeded_x(torch, dev, m, k, seed=1)
+        bias = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        sets = [device_woq_weights(torch, _capi, dev, k, n, seed=s) for s in range(copies)]
+        for i in range(launches):
+            wq, sc = sets[i % copies]
+            _capi.woq_linear(x, wq, sc, None, bias)
+
     if name in ("int8_gemm", "dynquant"):
         x0, w0, ws0, b0 = make_operands(torch, dev, seed=0)
         sets = []
@@ -552,29 +759,92 @@ def run_profile_case(name):
             if name == "int8_gemm":
                 a = _capi.dynamic_qlinear_args(x, w, ws, b, _capi.ZT_ACT_U8_ASYM, (4,), (), rs, y, None, _capi.ZT_ALGO_AUTO)
                 _capi.check(lib.zt_qlinear_prequantized(C.byref(a), q.data_ptr(), sc.data_ptr(), zp.data_ptr(), None))
-    elif name == "woq_decode":
-        m, k, n, gs = 1, 8192, 28672, 128
-        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
-        bias = torch.zeros(n, dtype=torch.bfloat16, device=dev)
-        copies = [(torch.randint(-2**31, 2**31 - 1, (n, k // 8), dtype=torch.int32, device=dev),
-                   torch.rand(k // gs, n, device=dev) * 0.01) for _ in range(2)]
-        for i in range(6):
-            wq, sc = copies[i % 2]
-            _capi.woq_linear(x, wq, sc, None, bias)
+    elif name == "woq_decode":            # work-balanced decode kernel, 117 MB layer
+        woq_loop(1, 8192, 28672, 6)
+    elif name == "woq_decode_small":      # register-ring decode kernel, config 1 (32 copies = 285 MB > L2)
+        woq_loop(1, 4096, 4096, 40, copies=32)
+    elif name == "woq_mid":               # tensor-core kernel split over K, decode batch of 32 on the 8B up-projection
+        woq_loop(32, 4096, 14336, 8, copies=5)
     elif name == "woq_prefill":
-        m, k, n, gs = 2048, 4096, 14336, 128
-        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
-        bias = torch.zeros(n, dtype=torch.bfloat16, device=dev)
-        copies = [(torch.randint(-2**31, 2**31 - 1, (n, k // 8), dtype=torch.int32, device=dev),
-                   torch.rand(k // gs, n, device=dev) * 0.01) for _ in range(2)]
-        for i in range(4):
-            wq, sc = copies[i % 2]
-            _capi.woq_linear(x, wq, sc, None, bias)
+        woq_loop(2048, 4096, 14336, 4)
+    elif name == "moe":
+        pk = peaks()
+        print(json.dumps(bench_moe_config(torch, _capi, dev, pk)))
+    elif name == "woq_timeline":
+        print(json.dumps(woq_timeline(torch, _capi, lib, dev)))
+        return
     else:
         raise SystemExit(f"unknown profile case {name}")
     torch.cuda.synchronize()
     assert _capi.poll_device_status() == 0
     print(json.dumps({"profile_case": name, "status": "ok"}))
+
+
+def woq_timeline(torch, _capi, lib, dev, m=1, k=4096, n=4096, chain=24):
+    """Phase stamps (zt_debug_set_timeline) of a chain of config-1 decode launches replayed as one CUDA graph:
+    for each launch, nanoseconds from the previous launch's last store to this launch's phases."""
+    import ctypes as C
+    stream = torch.cuda.Stream()
+    sptr = C.c_void_p(stream.cuda_stream)
+    copies = 32
+    sets = [device_woq_weights(torch, _capi, dev, k, n, seed=s) for s in range(copies)]
+    x = seeded_x(torch, dev, m, k, seed=1)
+    bias = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+    ws = _capi.woq_workspace(lib.zt_woq_linear_workspace_bytes(m, n, k), dev)
+    ys = [torch.empty(m, n, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    args = []
+    for i in range(chain):
+        a = _capi.WoqLinearArgs()
+        a.x, a.M, a.K, a.N = x.data_ptr(), m, k, n
+        a.wq, a.scales, a.zeros = sets[i % copies][0].data_ptr(), sets[i % copies][1].data_ptr(), None
+        a.scale_dtype, a.n_groups = _capi.ZT_F32, k // GS
+        a.bias, a.bias_dtype = bias.data_ptr(), _capi.ZT_BF16
+        a.y, a.workspace, a.workspace_bytes, a.algo = ys[i % 2].data_ptr(), ws.data_ptr(), ws.numel(), _capi.ZT_ALGO_AUTO
+        args.append(a)
+    max_ctas = 4096
+    buf = torch.zeros(chain * max_ctas * 8, dtype=torch.int64, device=dev)
+    with torch.cuda.stream(stream):
+        for a in args:
+            _capi.check(lib.zt_woq_linear(C.byref(a), sptr))
+        stream.synchronize()
+        _capi.check(lib.zt_debug_set_timeline(buf.data_ptr(), buf.numel() * 8))
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for a in args:
+                _capi.check(lib.zt_woq_linear(C.byref(a), sptr))
+        _capi.check(lib.zt_debug_set_timeline(None, 0))
+        for _ in range(3):
+            g.replay()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        g.replay()
+        end.record()
+        stream.synchronize()
+    us_per_launch = start.elapsed_time(end) * 1e3 / chain
+    rec = buf.cpu().view(-1, 8)
+    used = rec[:, 0] != 0
+    rec = rec[used]
+    # launches are consecutive blocks of equal size in the buffer
+    ctas = int(used.sum()) // chain
+    rec = rec[: ctas * chain].view(chain, ctas, 8).double()
+    names = ["entry", "prefetch_issued", "after_dependency_wait", "activations_staged", "main_loop_done",
+             "cta_reduced", "cross_cta_reduced", "output_written"]
+    rows = []
+    for i in range(4, chain):
+        prev_end = rec[i - 1, :, 7].max()
+        row = {}
+        for s, nm in enumerate(names):
+            v = rec[i, :, s]
+            v = v[v > 0]
+            row[nm] = {"first": round(float(v.min() - prev_end)), "median": round(float(v.median() - prev_end)),
+                       "last": round(float(v.max() - prev_end))}
+        rows.append(row)
+    med = {nm: {q: statistics.median(r[nm][q] for r in rows) for q in ("first", "median", "last")} for nm in names}
+    return {"profile_case": "woq_timeline", "workload": f"WOQ int4 M={m} K={k} N={n}, {chain} launches in one graph",
+            "ctas_per_launch": ctas, "us_per_launch": round(us_per_launch, 3),
+            "ns_after_previous_launch_last_store": med,
+            "note": "median over launches 4.. of (first / median / last CTA) per phase; negative = before the "
+                    "previous launch finished"}
 
 
 def cpu_oracle_call():
@@ -606,29 +876,54 @@ def cpu_baseline_sample():
                     "zentorch's own CPU path is unavailable on this box"}
 
 
+def cpu_tp_layer_call(m):
+    """CPU arm of the sharded workload: the int8-dynamic oracle over a bounded sample of the 70B layer (the
+    k/v projection 8192 -> 1024 at M rows), scaled to the metric by its own operation count."""
+    import torch
+    import zentorch_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(0)
+    k, n = 8192, 1024
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8)
+    ws = torch.rand(n, generator=g) * 2e-4 + 4e-4
+
+    def call():
+        return O.dynamic_qlinear(x, w, ws, None)
+    return call, 2.0 * m * k * n
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
     import torch
-    call = cpu_oracle_call()
+    if world == 1:
+        call, ops = cpu_oracle_call(), OPS_PER_CALL
+        metric, scaling = METRIC, "weak"
+        workload = (f"BASELINE config 2: dynamic int8 linear M={M} K={K} N={N}, per-token u8 asymmetric "
+                    "activations, per-channel s8 weights, fp32 bias, fused SiLU")
+        sample = f"{args.steps} steps of one full config-2 call each"
+    else:
+        call, ops = cpu_tp_layer_call(4096)
+        metric, scaling = METRIC_TP, "strong"
+        workload = ("BASELINE config 5: Llama-3-70B decoder-layer projections, int8 dynamic, M=4096 "
+                    "(host cores of rank 0; sampled on the k/v projection)")
+        sample = f"{args.steps} steps of the 8192->1024 projection at M=4096 (1/104 of the layer's operations)"
     for _ in range(max(args.warmup, 1)):
         call()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         call()
     dt = time.perf_counter() - t0
-    value = args.steps * OPS_PER_CALL / dt / 1e12
-    sample = f"{args.steps} steps of one full config-2 call each"
+    value = args.steps * ops / dt / 1e12
     line = {
-        "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": "TOP/s", "n_gpus": world,
+        "impl": "reference", "metric": metric, "value": round(value, 4), "unit": "TOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(dt / args.steps * 1e3, 3),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8/u8 x s8 -> s32, fp32 epilogue",
+        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "s8/u8 x s8 -> s32, fp32 epilogue",
         "data": "synthetic",
-        "config": {"workload": f"BASELINE config 2: dynamic int8 linear M={M} K={K} N={N}, per-token u8 asymmetric "
-                               "activations, per-channel s8 weights, fp32 bias, fused SiLU", "calls_per_step": 1,
-                   "parallelism": "host cores of rank 0"},
+        "config": {"workload": workload, "parallelism": "host cores of rank 0"},
         "cpu_baseline": {"value": round(value, 4), "unit": "TOP/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample,
                          "note": "oracle port on torch CPU kernels; zentorch's own CPU path (ZenDNN) cannot be "
@@ -644,8 +939,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile", default=None, help="run a few plain launches of one kernel (for ncu): "
-                                                    "int8_gemm | woq_decode | woq_prefill | dynquant")
+    ap.add_argument("--quick", action="store_true", help="skip the per-layer sweeps, the MoE and the M=4096 cases")
+    ap.add_argument("--profile", default=None, help="run a few plain launches of one kernel (for ncu), or woq_timeline")
     args = ap.parse_args()
     if args.profile:
         run_profile_case(args.profile)

@@ -5,6 +5,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "int8.cuh"
 #include "tc05.cuh"
@@ -56,6 +57,21 @@ bool overlap_launches() {
 
 CallOverlap::CallOverlap(bool allowed) : saved_(g_call_overlap) { g_call_overlap = allowed; }
 CallOverlap::~CallOverlap() { g_call_overlap = saved_; }
+
+namespace {
+std::mutex g_timeline_mu;
+unsigned long long *g_timeline_buf = nullptr;
+size_t g_timeline_entries = 0, g_timeline_used = 0;
+}  // namespace
+
+TimelineSink timeline_for_launch(int ctas) {
+  std::lock_guard<std::mutex> lock(g_timeline_mu);
+  const size_t need = (size_t)ctas * kTimelineSlots;
+  if (!g_timeline_buf || g_timeline_used + need > g_timeline_entries) return TimelineSink{nullptr};
+  TimelineSink t{g_timeline_buf + g_timeline_used};
+  g_timeline_used += need;
+  return t;
+}
 
 int sm_count() {
   static int cached[64] = {0};
@@ -181,6 +197,14 @@ extern "C" int zt_poll_device_status(int *status, int reset) {
     const int zero = 0;
     ZT_CUDA_OK(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
   }
+  return ZT_SUCCESS;
+}
+
+extern "C" int zt_debug_set_timeline(void *device_buffer, size_t bytes) {
+  std::lock_guard<std::mutex> lock(g_timeline_mu);
+  g_timeline_buf = reinterpret_cast<unsigned long long *>(device_buffer);
+  g_timeline_entries = device_buffer ? bytes / sizeof(unsigned long long) : 0;
+  g_timeline_used = 0;
   return ZT_SUCCESS;
 }
 

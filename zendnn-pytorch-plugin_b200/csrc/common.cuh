@@ -120,6 +120,27 @@ inline cudaError_t launch_overlapped_cluster(Kernel kern, dim3 grid, dim3 block,
 }
 #endif
 
+// ---- phase stamps for latency analysis -----------------------------------------------------------
+// zt_debug_set_timeline() gives the decode kernels a device buffer; while it is set, thread 0 of every CTA
+// stores %globaltimer (ns) at up to kTimelineSlots points of the kernel, one record per CTA and launch
+// (records of consecutive launches follow each other; the host hands out the record offsets).  Null (the
+// default) costs a uniform predicated-off branch per stamp.
+constexpr int kTimelineSlots = 8;
+struct TimelineSink {
+  unsigned long long *base;  // null: disabled
+};
+TimelineSink timeline_for_launch(int ctas);   // reserves ctas * kTimelineSlots entries (or returns {nullptr})
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void stamp(const TimelineSink &t, int cta, int slot) {
+  if (t.base != nullptr && threadIdx.x == 0) {
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    t.base[(size_t)cta * kTimelineSlots + slot] = ns;
+  }
+}
+#endif
+
 // ---- post-op chain ----------------------------------------------------------------------------
 struct PostOpsDev {
   int n_ops;

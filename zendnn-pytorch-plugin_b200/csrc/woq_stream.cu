@@ -53,6 +53,7 @@ struct StreamParams {
   int early_trigger;  // the grid is resident at once: let the next kernel in at entry rather than after the main loop
   int cluster;        // the K slices of a column tile are one thread-block cluster: reduce through its shared memory
   int cluster_off;    // byte offset of the cluster reduction buffer [nsplit][M][columns] in dynamic shared memory
+  TimelineSink timeline;
   PostOpsDev post;
 };
 
@@ -172,13 +173,17 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   // wait for that kernel before touching activations, scratch and output.
   // The next kernel may come in at once when this grid is resident as a whole; otherwise only after the main
   // loop, when every CTA of this grid has started (its CTAs would take the places of this grid's later ones).
+  const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+  stamp(p.timeline, cta, 0);
   if (p.early_trigger) grid_launch_dependents();
   // cluster form: every CTA of the cluster must be running before a peer's shared memory is written; the
   // matching wait sits right before the first remote store
   if (p.cluster) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 #pragma unroll
   for (int s = 0; s < RING; ++s) prefetch(ring[s], step_k(s / kSPC, s % kSPC));
+  stamp(p.timeline, cta, 1);
   grid_dependency_wait();
+  stamp(p.timeline, cta, 2);
   stage(0, 0);
 
   float acc[R][MT][4];
@@ -197,6 +202,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
       if (c < nchunks) {
         cp_async_wait_all();
         __syncthreads();  // chunk c has landed for everybody; chunk c-1 (other buffer) is no longer read
+        if (c == 0) stamp(p.timeline, cta, 3);
         if (c + 1 < nchunks) stage(c + 1, h2 ^ 1);
         const uint4 *xb = xs + h2 * buf_slots;
 #pragma unroll
@@ -273,6 +279,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
   }
 
   // ---- reduce the warps (they split K) through shared memory ------------------------------------------
+  stamp(p.timeline, cta, 4);
   if (!p.early_trigger) grid_launch_dependents();
   __syncthreads();
   float *red = reinterpret_cast<float *>(smem_raw);  // [W][kCols][kTileN + 1]
@@ -288,6 +295,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
         red[(warp * kCols + ml) * kRedStride + nl] = acc[r][m][e];
       }
   __syncthreads();
+  stamp(p.timeline, cta, 5);
 
   __shared__ int s_ticket;
   constexpr int kRowsPerPass = kThreads / kTileN;
@@ -326,6 +334,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
     __threadfence();
     if (tid == 0) p.counters[blockIdx.x] = 0;
   }
+  stamp(p.timeline, cta, 6);
   for (int ml = tid / kTileN; ml < p.M; ml += kRowsPerPass) {
     if (n >= p.N) continue;
     float v = 0.f;
@@ -342,6 +351,7 @@ __global__ void __launch_bounds__(W * 32) woq_stream_kernel(const StreamParams p
     v = apply_post_ops(v, p.post, idx, ZT_BF16);
     p.y[idx] = __float2bfloat16_rn(v);
   }
+  stamp(p.timeline, cta, 7);
 }
 
 // Kernel shapes.  cfg 0: 16 columns per CTA, cfg 1: 32 columns (both 8 warps for M <= 8, ring of 4);
@@ -386,6 +396,7 @@ int launch(const StreamParams &p_in, dim3 grid, cudaStream_t st) {
   int per_sm = 0;
   ZT_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, S::W * 32, smem));
   StreamParams p = p_in;
+  p.timeline = timeline_for_launch((int)(grid.x * grid.y));
   p.cluster = cluster ? 1 : 0;
   p.cluster_off = (int)base_smem;
   // half the resident capacity at most: the next kernel's CTAs then find room beside this grid's

@@ -24,7 +24,7 @@ ZT_STATIC_SCRATCH_Q_BYTES, ZT_STATIC_SCRATCH_MAX_ROWS = 8 << 20, 16384
 
 # Every symbol include/zentorch_b200.h declares; the CPU test-suite checks the library exports all.
 EXPORTED_SYMBOLS = (
-    "zt_last_error", "zt_version", "zt_device_supported", "zt_poll_device_status", "zt_selftest_expire_wait",
+    "zt_last_error", "zt_version", "zt_device_supported", "zt_poll_device_status", "zt_selftest_expire_wait", "zt_debug_set_timeline",
     "zt_woq_linear_workspace_bytes", "zt_woq_linear", "zt_woq_repack_weight", "zt_woq_repack_from_int4pack",
     "zt_dynamic_qlinear_workspace_bytes", "zt_dynamic_qlinear", "zt_dynamic_quantize", "zt_int8_gemm_s32",
     "zt_int8_weight_rowsum", "zt_qlinear_prequantized", "zt_dynamic_qlinear_static",
@@ -91,6 +91,7 @@ def lib() -> C.CDLL:
     L.zt_device_supported.restype = C.c_int
     L.zt_poll_device_status.argtypes = [C.POINTER(C.c_int), C.c_int]
     L.zt_selftest_expire_wait.argtypes = [C.c_void_p]
+    L.zt_debug_set_timeline.argtypes = [C.c_void_p, C.c_size_t]
     L.zt_woq_linear_workspace_bytes.restype = C.c_size_t
     L.zt_woq_linear_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64]
     L.zt_woq_linear.argtypes = [C.POINTER(WoqLinearArgs), C.c_void_p]

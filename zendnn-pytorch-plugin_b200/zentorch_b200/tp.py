@@ -144,3 +144,78 @@ def slice_activation_for_row_parallel(x: torch.Tensor, group=None) -> torch.Tens
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     k = x.shape[-1]
     return x[..., rank * k // world:(rank + 1) * k // world].contiguous()
+
+
+# ---- fused projections and a whole decoder layer's linears --------------------------------------------
+def fuse_woq_columns(parts):
+    """Horizontal fusion of WOQ linears that share their input (q/k/v, gate/up): one linear whose output is
+    the concatenation of theirs.  The packed layout is N-major, so fusing is a row concatenation of the
+    packed tensors and a column concatenation of the scale tables; it is done once at load time (the
+    reference's qkv fusion concatenates weights the same way at compile time,
+    src/cpu/python/zentorch/_custom_op_replacement.py:675-810).  `parts` is a list of (weight, scales, zeros,
+    bias) with weight in the op's [K/8, N_i] form."""
+    ws, ss, zs, bs = zip(*parts)
+    w = torch.cat([x.t() for x in ws], dim=0).contiguous().t()
+    s = torch.cat(ss, dim=1).contiguous()
+    z = None if zs[0] is None else torch.cat(zs, dim=1).contiguous()
+    b = None if bs[0] is None else torch.cat(bs, dim=0).contiguous()
+    return w, s, z, b
+
+
+def fuse_int8_rows(parts):
+    """The same for dynamic-int8 linears: (weight [N_i, K], w_scales [N_i], bias) concatenated along N."""
+    ws, ss, bs = zip(*parts)
+    return (torch.cat(ws, dim=0).contiguous(), torch.cat([x.reshape(-1) for x in ss]).contiguous(),
+            None if bs[0] is None else torch.cat(bs).contiguous())
+
+
+class DecoderLayerLinears:
+    """The seven projections of a Llama-style decoder layer as four launches and two collectives per rank:
+
+        qkv  = x . [Wq | Wk | Wv]   column-parallel (each of q, k, v sharded, then fused per rank)
+        o    = attn . Wo            row-parallel, all-reduce
+        gu   = o . [Wgate | Wup]    column-parallel, fused; h = silu(gate) * up stays sharded
+        down = h . Wdown            row-parallel, all-reduce
+
+    Attention itself is outside this path; `attn` is whatever buffer the caller passes (its shard of the
+    attention output).  `kind` is 'woq' or 'int8'; `full` maps a projection name to its unsharded
+    parameters (woq: weight [K/8, N] view, scales, zeros, bias; int8: weight [N, K], w_scales, bias).
+    Every step is plain launches on the current stream plus NCCL calls, so a whole step can be captured
+    in a CUDA graph and replayed without host code between the kernels."""
+
+    def __init__(self, kind, full, rank=0, world=1, group=None):
+        self.kind, self.rank, self.world, self.group = kind, rank, world, group
+        shard = (lambda p, mode: shard_woq(*p, mode, rank, world)) if kind == "woq" else \
+            (lambda p, mode: shard_int8(*p, mode, rank, world))
+        fuse = fuse_woq_columns if kind == "woq" else fuse_int8_rows
+        self.qkv = fuse([shard(full[n], "column") for n in ("q", "k", "v")])
+        self.o = shard(full["o"], "row")
+        self.gate_up = fuse([shard(full[n], "column") for n in ("gate", "up")])
+        self.down = shard(full["down"], "row")
+
+    def _lin(self, x, params):
+        if self.kind == "woq":
+            return torch.ops.zentorch.zentorch_woq_linear(x, *params)
+        return torch.ops.zentorch.zentorch_dynamic_qlinear(x, *params)
+
+    def _reduce(self, y):
+        if self.world > 1:
+            dist.all_reduce(y, group=self.group)
+        return y
+
+    def __call__(self, x, attn):
+        qkv = self._lin(x, self.qkv)
+        o = self._reduce(self._lin(attn, self.o))
+        gu = self._lin(o, self.gate_up)
+        half = gu.shape[-1] // 2
+        h = torch.nn.functional.silu(gu[..., :half]) * gu[..., half:]
+        return qkv, self._reduce(self._lin(h, self.down))
+
+    def weight_bytes(self):
+        """Bytes of weights, scales and zero points this rank streams per step."""
+        total = 0
+        for p in (self.qkv, self.o, self.gate_up, self.down):
+            for t in p[:-1]:
+                if t is not None:
+                    total += t.numel() * t.element_size()
+        return total
