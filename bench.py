@@ -770,8 +770,11 @@ def run_profile_case(name):
     elif name == "moe":
         pk = peaks()
         print(json.dumps(bench_moe_config(torch, _capi, dev, pk)))
-    elif name == "woq_timeline":
+    elif name == "woq_timeline":          # config 1 (small layer)
         print(json.dumps(woq_timeline(torch, _capi, lib, dev)))
+        return
+    elif name == "woq_timeline_large":    # 117 MB layer
+        print(json.dumps(woq_timeline(torch, _capi, lib, dev, k=8192, n=28672, chain=12, copies=3)))
         return
     else:
         raise SystemExit(f"unknown profile case {name}")
@@ -780,13 +783,12 @@ def run_profile_case(name):
     print(json.dumps({"profile_case": name, "status": "ok"}))
 
 
-def woq_timeline(torch, _capi, lib, dev, m=1, k=4096, n=4096, chain=24):
+def woq_timeline(torch, _capi, lib, dev, m=1, k=4096, n=4096, chain=24, copies=32):
     """Phase stamps (zt_debug_set_timeline) of a chain of config-1 decode launches replayed as one CUDA graph:
     for each launch, nanoseconds from the previous launch's last store to this launch's phases."""
     import ctypes as C
     stream = torch.cuda.Stream()
     sptr = C.c_void_p(stream.cuda_stream)
-    copies = 32
     sets = [device_woq_weights(torch, _capi, dev, k, n, seed=s) for s in range(copies)]
     x = seeded_x(torch, dev, m, k, seed=1)
     bias = torch.zeros(n, dtype=torch.bfloat16, device=dev)
@@ -827,8 +829,8 @@ def woq_timeline(torch, _capi, lib, dev, m=1, k=4096, n=4096, chain=24):
     # launches are consecutive blocks of equal size in the buffer
     ctas = int(used.sum()) // chain
     rec = rec[: ctas * chain].view(chain, ctas, 8).double()
-    names = ["entry", "prefetch_issued", "after_dependency_wait", "activations_staged", "main_loop_done",
-             "cta_reduced", "cross_cta_reduced", "output_written"]
+    names = ["0_entry", "1_weight_prefetch_issued", "2_ordered_after_earlier_work", "3_first_activations_ready",
+             "4_main_loop_done", "5_cta_reduced", "6_cross_cta_reduced", "7_output_written"]
     rows = []
     for i in range(4, chain):
         prev_end = rec[i - 1, :, 7].max()
@@ -836,10 +838,13 @@ def woq_timeline(torch, _capi, lib, dev, m=1, k=4096, n=4096, chain=24):
         for s, nm in enumerate(names):
             v = rec[i, :, s]
             v = v[v > 0]
+            if v.numel() == 0:
+                continue
             row[nm] = {"first": round(float(v.min() - prev_end)), "median": round(float(v.median() - prev_end)),
                        "last": round(float(v.max() - prev_end))}
         rows.append(row)
-    med = {nm: {q: statistics.median(r[nm][q] for r in rows) for q in ("first", "median", "last")} for nm in names}
+    med = {nm: {q: statistics.median(r[nm][q] for r in rows) for q in ("first", "median", "last")}
+           for nm in names if all(nm in r for r in rows)}
     return {"profile_case": "woq_timeline", "workload": f"WOQ int4 M={m} K={k} N={n}, {chain} launches in one graph",
             "ctas_per_launch": ctas, "us_per_launch": round(us_per_launch, 3),
             "ns_after_previous_launch_last_store": med,

@@ -95,10 +95,11 @@ ZT_API int zt_poll_device_status(int *status, int reset);
 ZT_API int zt_selftest_expire_wait(void *stream);
 /* Latency analysis of the decode kernels (no counterpart in the reference).  While a device buffer is set,
  * every launch of zt_woq_linear's decode kernels reserves one record per CTA in it, in launch order, and
- * thread 0 of each CTA stores the GPU's nanosecond timer at eight points: 0 entry, 1 weight prefetch
- * issued, 2 ordered after earlier work, 3 first activations staged, 4 main loop done, 5 CTA reduction
- * done, 6 cross-CTA reduction done, 7 output written.  Records hold 8 uint64 each; launches that no longer
- * fit are not recorded.  Pass NULL to switch it off (the default). */
+ * one thread of each CTA stores the GPU's nanosecond timer at up to eight points: 0 entry, 1 weight
+ * prefetch issued, 2 ordered after earlier work, 3 first activations ready for the arithmetic, 4 main loop
+ * done, 5 CTA reduction done, 6 cross-CTA reduction done, 7 output written (points a kernel does not have
+ * stay zero).  Records hold 8 uint64 each; launches that no longer fit are not recorded.  Pass NULL to
+ * switch it off (the default). */
 ZT_API int zt_debug_set_timeline(void *device_buffer, size_t bytes);
 
 /* ---------------------------------------------------------------------------------------------

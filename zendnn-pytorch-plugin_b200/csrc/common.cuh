@@ -132,12 +132,16 @@ struct TimelineSink {
 TimelineSink timeline_for_launch(int ctas);   // reserves ctas * kTimelineSlots entries (or returns {nullptr})
 
 #ifdef __CUDACC__
-__device__ __forceinline__ void stamp(const TimelineSink &t, int cta, int slot) {
-  if (t.base != nullptr && threadIdx.x == 0) {
+// by whichever single thread calls it
+__device__ __forceinline__ void stamp_here(const TimelineSink &t, int cta, int slot) {
+  if (t.base != nullptr) {
     unsigned long long ns;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
     t.base[(size_t)cta * kTimelineSlots + slot] = ns;
   }
+}
+__device__ __forceinline__ void stamp(const TimelineSink &t, int cta, int slot) {
+  if (threadIdx.x == 0) stamp_here(t, cta, slot);
 }
 #endif
 

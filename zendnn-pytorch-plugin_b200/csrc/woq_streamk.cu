@@ -86,6 +86,7 @@ struct SKParams {
   int scale_dtype, bias_dtype;
   int stages, stage_bytes;   // ring of weight stages
   int xslots, xslot_bytes;   // ring of activation slots
+  TimelineSink timeline;
   PostOpsDev post;
 };
 
@@ -212,6 +213,7 @@ __global__ void __launch_bounds__(sk_threads(CW), 1)
 
   // The weight producer sets up its own barriers and fills the ring once before anybody else is ready:
   // weights do not depend on earlier work, and the first bytes take the longest to arrive.
+  stamp(p.timeline, blockIdx.x, 0);
   Iter w_iter(c_begin, c_end, p.ksteps);
   constexpr uint32_t kWTxBytes = (uint32_t)kWBytes + (uint32_t)kSBytes * (ASYM ? 2u : 1u);
   int w_pre = 0;
@@ -239,6 +241,7 @@ __global__ void __launch_bounds__(sk_threads(CW), 1)
       }
       ++w_pre;
     }
+    if (lane == 0) stamp_here(p.timeline, blockIdx.x, 1);
   }
   if (tid == 0) {
     tc::prefetch_tensormap(&map_x8);
@@ -291,6 +294,7 @@ __global__ void __launch_bounds__(sk_threads(CW), 1)
   } else if (warp == kComputeWarps + 1) {
     // ---------------- activation producer: its own, deeper ring of small slots ----------------
     grid_dependency_wait();
+    if (lane == 0) stamp_here(p.timeline, blockIdx.x, 2);
     Iter iter(c_begin, c_end, p.ksteps);
     Chunk ch;
     uint32_t s = 0, ph = 0;
@@ -452,6 +456,7 @@ __global__ void __launch_bounds__(sk_threads(CW), 1)
       buf ^= 1;
       if (buf == 0) bph ^= 1;
     }
+    if (lane == 0) stamp_here(p.timeline, blockIdx.x, 7);
   } else if (warp > kComputeWarps + 2) {
     // ---------------- converter warps: bf16 activations -> integer digit fragments ----------------
     // Four lanes per (token, cell); a lane converts four of the cell's sixteen 8-value pieces.
@@ -588,11 +593,14 @@ __global__ void __launch_bounds__(sk_threads(CW), 1)
     uint32_t s = 0, ph = 0, xs_i = 0, xph = 0;   // weight stage / activation slot and their phase bits
     uint32_t rbuf = 0, rph = 0;                  // reduction buffer and its phase bit
     bool ok = true;
+    bool first_chunk = true;
     while (iter.next(ch)) {
       if (ok && !(tc::mbar_wait_suspend(&full_bar[s], ph, 60) && tc::mbar_wait_suspend(&frag_bar[xs_i], xph, 60))) {
         tc::report_timeout(p.status, kStatusConvertTimeout);
         ok = false;
       }
+      if (first_chunk && tid == 0) stamp_here(p.timeline, blockIdx.x, 3);
+      first_chunk = false;
       const unsigned char *stage = smem + (size_t)s * p.stage_bytes;
       const unsigned char *xslot = xring + (size_t)xs_i * p.xslot_bytes;
       if (ok && my_step < ch.nsteps) {
@@ -718,6 +726,7 @@ __global__ void __launch_bounds__(sk_threads(CW), 1)
         if (rbuf == 0) rph ^= 1;
       }
     }
+    if (tid == 0) stamp_here(p.timeline, blockIdx.x, 4);
   }
 }
 
@@ -896,6 +905,7 @@ int woq_streamk_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   int grid = sm_count();
   if ((long long)grid > p.total_cells) grid = (int)p.total_cells;
   const size_t smem_bytes = (size_t)stages * stage + (size_t)xslots * xslot + tail;
+  p.timeline = timeline_for_launch(grid);
   Maps maps;
   int rc = build_maps(a, (int)a.M, (uint32_t)chunk_steps(nb), maps);
   if (rc != ZT_SUCCESS) return rc;

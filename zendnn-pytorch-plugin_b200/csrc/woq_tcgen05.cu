@@ -24,11 +24,17 @@
 // weight and scale tensors; the number of tiles is read from device memory, so no host
 // synchronisation is needed between routing and the GEMM.
 //
-// All eight dequantisation warps take every k-block together, in order.  Giving different k-blocks to
-// different warp teams (to overlap the conversion latency of several k-blocks) is only sound when the
-// number of stages is a multiple of the number of teams: otherwise consecutive uses of a stage belong to
-// different teams, a team can reach its wait two uses ahead of the stage's barrier, and an mbarrier
-// parity wait that far ahead passes at once.
+// Conversion teams.  One k-block's conversion is a chain of dependent steps (wait for the stage, shared-memory
+// load, ALU, shared-memory store, proxy fence, barrier arrive) whose latency, about 1200 cycles, is several
+// times its issue time; with all sixteen warps on the same k-block the kernel converted one k-block per such
+// latency.  For token tiles up to 128 the sixteen warps therefore form four teams of four warps, team t
+// taking the ring positions congruent to t modulo 4 (a thread converts one whole weight row of the k-block:
+// 32 packed bytes in, 128 bytes of bf16 out), so four k-blocks are in flight at once.  This is sound because
+// the number of stages is a multiple of the number of teams: a stage is always converted by the same team,
+// so a team sees every phase of the stage barriers it waits on.  (With a stage count that is not, consecutive
+// uses of a stage belong to different teams, a team can reach its wait two uses ahead of the barrier, and
+// an mbarrier parity wait that far ahead passes at once.)  A stage count that is not a multiple of four falls back to
+// all sixteen warps converting every k-block together.
 //
 // Accumulators are double buffered in tensor memory: the epilogue of a tile overlaps the next tile's
 // main loop.  All waits are bounded (see tc05.cuh).
@@ -107,15 +113,19 @@ __device__ __forceinline__ TileInfo decode_tile(const TcParams &p, int tile, int
   return t;
 }
 
-template <int BT, int STAGES, int PSTAGES>
+// Three rings: STAGES converted weight blocks (bf16, 16 KB each), XSTAGES activation tiles, PSTAGES packed chunks.
+// The activation tiles have a ring of their own so that they can be requested many k-blocks ahead: a tile
+// load takes about a microsecond, and a slot that could only be refilled once its weight stage was free again
+// would limit the kernel to (stages / that latency) k-blocks per second.
+template <int BT, int STAGES, int XSTAGES, int PSTAGES>
 struct SmemLayout {
   static constexpr int kWBytes = kBN * 128;
   static constexpr int kXBytes = BT * 128;
-  static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kTileBytes = STAGES * kStageBytes;
+  static constexpr int kWRingBytes = STAGES * kWBytes;
+  static constexpr int kTileBytes = kWRingBytes + XSTAGES * kXBytes;
   static constexpr int kPackedBytes = PSTAGES * kChunkBytes;
   static constexpr int kEpiBytes = kEpiWarps * 32 * kEpiRowStride * 4;
-  static constexpr int kBarBytes = (3 * STAGES + 2 * PSTAGES + 4) * 8 + 8;
+  static constexpr int kBarBytes = (2 * STAGES + 2 * XSTAGES + 2 * PSTAGES + 4) * 8 + 8;
   static constexpr int kTotal = kTileBytes + kPackedBytes + kEpiBytes + kBarBytes + 1024;
 };
 
@@ -193,18 +203,22 @@ __global__ void __launch_bounds__(256) woq_splitk_reduce_kernel(const float *__r
   *reinterpret_cast<uint2 *>(y + base) = o;
 }
 
-template <int BT, int STAGES, int PSTAGES, bool ASYM>
+constexpr int kTeams = 4;                      // conversion teams (token tiles up to 128)
+constexpr int kTeamWarps = kDqWarps / kTeams;  // 4 warps = 128 threads = one weight row per thread
+
+template <int BT, int STAGES, int XSTAGES, int PSTAGES, bool ASYM>
 __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                   const __grid_constant__ CUtensorMap tmap_w,
                                                                   const TcParams p) {
-  using L = SmemLayout<BT, STAGES, PSTAGES>;
+  using L = SmemLayout<BT, STAGES, XSTAGES, PSTAGES>;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char *smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
   unsigned char *packed = smem + L::kTileBytes;  // ring of packed-weight chunks (1024-byte aligned)
   float *epi_scratch = reinterpret_cast<float *>(smem + L::kTileBytes + L::kPackedBytes);
   uint64_t *full_x = reinterpret_cast<uint64_t *>(smem + L::kTileBytes + L::kPackedBytes + L::kEpiBytes);
-  uint64_t *full_w = full_x + STAGES;
-  uint64_t *empty_bar = full_w + STAGES;
+  uint64_t *empty_x = full_x + XSTAGES;      // activation slot read by the MMAs of its k-block
+  uint64_t *full_w = empty_x + XSTAGES;      // converted weight block written
+  uint64_t *empty_bar = full_w + STAGES;     // converted weight block read by the MMAs of its k-block
   uint64_t *full_p = empty_bar + STAGES;     // packed chunk landed
   uint64_t *empty_p = full_p + PSTAGES;      // packed chunk consumed by all dequantisation warps
   uint64_t *tmem_full = empty_p + PSTAGES;   // [2]
@@ -212,6 +226,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
 
   constexpr uint32_t kTmemCols = 2 * BT <= 32 ? 32 : 2 * BT <= 64 ? 64 : 2 * BT <= 128 ? 128 : 2 * BT <= 256 ? 256 : 512;
+  constexpr bool kUseTeams = (STAGES % kTeams == 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Programmatic dependent launch: packed weights and scales are read before the wait for the preceding
   // kernel, activations, partial sums and output after it.  The grouped form reads its tile list (made by the
@@ -225,9 +240,12 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
   if (threadIdx.x == 0) {
     tc::prefetch_tensormap(&tmap_x);
     tc::prefetch_tensormap(&tmap_w);
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < XSTAGES; ++s) {
       tc::mbar_init(&full_x[s], 1);
-      tc::mbar_init(&full_w[s], kDqWarps);
+      tc::mbar_init(&empty_x[s], 1);
+    }
+    for (int s = 0; s < STAGES; ++s) {
+      tc::mbar_init(&full_w[s], kUseTeams ? kTeamWarps : kDqWarps);
       tc::mbar_init(&empty_bar[s], 1);
     }
     for (int s = 0; s < PSTAGES; ++s) {
@@ -298,15 +316,15 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
           }
           const long long need = (long long)((tile - blockIdx.x) / gridDim.x) * num_chunks + kb / kChunkKB;
           while (ok && (long long)pit <= need) issue_packed(true);
-          const uint32_t s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
+          const uint32_t s = it % XSTAGES;
+          const uint32_t ph = (it / XSTAGES) & 1;
+          if (!tc::mbar_wait(&empty_x[s], ph ^ 1)) {
             tc::report_timeout(p.status, kStatusProducerTimeout);
             ok = false;
             break;
           }
           tc::mbar_expect_tx(&full_x[s], L::kXBytes);
-          tc::tma_load_2d(smem + s * L::kStageBytes + L::kWBytes, &tmap_x, &full_x[s], (t.kb0 + kb) * kBK, t.m0);
+          tc::tma_load_2d(smem + L::kWRingBytes + s * L::kXBytes, &tmap_x, &full_x[s], (t.kb0 + kb) * kBK, t.m0);
         }
       }
     }
@@ -327,25 +345,137 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
         tc::fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BT;
         for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
-          const uint32_t s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!tc::mbar_wait(&full_x[s], ph) || !tc::mbar_wait(&full_w[s], ph)) {
+          const uint32_t s = it % STAGES, xs = it % XSTAGES;
+          const uint32_t ph = (it / STAGES) & 1, xph = (it / XSTAGES) & 1;
+          if (!tc::mbar_wait(&full_x[xs], xph) || !tc::mbar_wait(&full_w[s], ph)) {
             tc::report_timeout(p.status, kStatusMmaTimeout);
             ok = false;
             break;
           }
           tc::fence_after_sync();
-          const uint32_t w_addr = smem_u32(smem + s * L::kStageBytes);
-          const uint64_t a_desc = tc::smem_desc_k_sw128(w_addr);
-          const uint64_t b_desc = tc::smem_desc_k_sw128(w_addr + L::kWBytes);
+          const uint64_t a_desc = tc::smem_desc_k_sw128(smem_u32(smem + s * L::kWBytes));
+          const uint64_t b_desc = tc::smem_desc_k_sw128(smem_u32(smem + L::kWRingBytes + xs * L::kXBytes));
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             // 16 bf16 = 32 bytes of K per instruction: advance the start addresses by 32 >> 4 = 2
             tc::mma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          tc::mma_commit(&empty_bar[s]);
+          tc::mma_commit(&empty_bar[s]);   // both rings' slots are free once these MMAs have read them
+          tc::mma_commit(&empty_x[xs]);
         }
         tc::mma_commit(&tmem_full[buf]);
+      }
+    }
+  } else if (kUseTeams && warp < 2 + kDqWarps) {
+    // ---------------- dequantisation warps, four teams: a thread converts one weight row of a k-block ----------------
+    const int dw = warp - 2;
+    const uint32_t team = (uint32_t)dw / kTeamWarps;       // takes ring positions it with it % 4 == team
+    const int row = (dw % kTeamWarps) * 32 + lane;          // weight row (output column) within the tile
+    const uint32_t row_x = row & 7;
+    const int gs_shift = (p.gs & (p.gs - 1)) == 0 ? __ffs(p.gs) - 1 : -1;
+    const bool exact_scale = (p.scale_dtype == ZT_BF16);
+    const int my_tiles = blockIdx.x < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // Scales (zero points) of the two 32-k halves of a k-block, fetched from global memory one k-block of this
+    // team ahead.  Position = (local tile index, chunk); the team's k-block in a chunk is 4 * chunk + jt with
+    // jt = (team - local * num_kb) mod 4, when that k-block exists.
+    struct Sc {
+      float s0, s1, z0, z1;
+    };
+    auto fetch = [&](int local, int chunk, Sc &out) {
+      if (local >= my_tiles) return;
+      const uint32_t jt = (team - (uint32_t)local * (uint32_t)num_kb) & 3u;
+      const int kb = chunk * kChunkKB + (int)jt;
+      if (kb >= num_kb) return;
+      const TileInfo t = decode_tile(p, blockIdx.x + local * gridDim.x, n_mt, BT);
+      const int64_t base = (int64_t)t.expert * p.s_estride + min(t.n0 + row, p.N - 1);
+      const int k = (t.kb0 + kb) * kBK;
+      const int g0 = gs_shift >= 0 ? (k >> gs_shift) : (k / p.gs);
+      const int g1 = gs_shift >= 0 ? ((k + 32) >> gs_shift) : ((k + 32) / p.gs);
+      out.s0 = load_as_float(p.scales, base + (int64_t)g0 * p.N, p.scale_dtype);
+      out.s1 = g1 == g0 ? out.s0 : load_as_float(p.scales, base + (int64_t)g1 * p.N, p.scale_dtype);
+      if (ASYM) {
+        out.z0 = load_as_float(p.zeros, base + (int64_t)g0 * p.N, p.scale_dtype);
+        out.z1 = g1 == g0 ? out.z0 : load_as_float(p.zeros, base + (int64_t)g1 * p.N, p.scale_dtype);
+      }
+    };
+    Sc nxt{0.f, 0.f, 0.f, 0.f};
+    fetch(0, 0, nxt);
+    uint32_t pit = 0;   // packed chunks walked so far (every team walks every chunk)
+    bool ok = true;
+    for (int local = 0; local < my_tiles; ++local) {
+      const uint32_t it0 = (uint32_t)local * (uint32_t)num_kb;   // ring position of the tile's first k-block
+      const uint32_t jt = (team - it0) & 3u;
+      for (int chunk = 0; chunk < num_chunks; ++chunk, ++pit) {
+        const Sc cur = nxt;
+        if (chunk + 1 < num_chunks) fetch(local, chunk + 1, nxt); else fetch(local + 1, 0, nxt);
+        const uint32_t ps = pit % PSTAGES;
+        if (ok && !tc::mbar_wait(&full_p[ps], (pit / PSTAGES) & 1)) {
+          tc::report_timeout(p.status, kStatusConvertTimeout);
+          ok = false;
+        }
+        const int kb = chunk * kChunkKB + (int)jt;
+        if (kb < num_kb) {
+          const uint32_t it = it0 + (uint32_t)kb;
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (ok && !tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
+            tc::report_timeout(p.status, kStatusConvertTimeout);
+            ok = false;
+          }
+          if (ok) {
+            // the row's 32 packed bytes of this k-block: 16-byte chunks 2 jt and 2 jt + 1 of the swizzled 128-byte row
+            const unsigned char *prow = packed + ps * kChunkBytes + row * 128;
+            const uint4 w0 = *reinterpret_cast<const uint4 *>(prow + (((2u * jt) ^ row_x) << 4));
+            const uint4 w1 = *reinterpret_cast<const uint4 *>(prow + (((2u * jt + 1u) ^ row_x) << 4));
+            const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            unsigned char *wrow = smem + s * L::kWBytes + row * 128;
+            uint32_t sh[2] = {0, 0}, sl[2] = {0, 0};
+            if (!ASYM) {
+              split_bf16x2(cur.s0, sh[0], sl[0]);
+              split_bf16x2(cur.s1, sh[1], sl[1]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int hf = i >> 2;   // which 32 k of the k-block
+              uint4 o;
+              if (ASYM) {
+                const float sc = hf ? cur.s1 : cur.s0, zp = hf ? cur.z1 : cur.z0;
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const uint32_t bits = ((words[i] >> (4 * e)) & 0xFu) | 0x4B000000u;  // 2^23 + q
+                  f[e] = fmaf(__uint_as_float(bits) - 8388616.0f, sc, zp);           // (q - 8) * s + z
+                }
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(f[0], f[1]);
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(f[2], f[3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(f[4], f[5]);
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(f[6], f[7]);
+                o.x = *reinterpret_cast<uint32_t *>(&p0);
+                o.y = *reinterpret_cast<uint32_t *>(&p1);
+                o.z = *reinterpret_cast<uint32_t *>(&p2);
+                o.w = *reinterpret_cast<uint32_t *>(&p3);
+              } else {
+                uint32_t r[4];
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp) {
+                  uint32_t v = nib_pair_to_bf16x2<true>(words[i] >> (4 * pp));
+                  v = bf2_sub(v, 0x43084308u);  // exact: (128 + u) - 136 = q
+                  r[pp] = exact_scale ? bf2_mul(v, sh[hf]) : bf2_fma(v, sh[hf], bf2_mul(v, sl[hf]));  // (k = p, k = p + 4)
+                }
+                o.x = prmt(r[0], r[1], 0x5410);  // (k0, k1)
+                o.y = prmt(r[2], r[3], 0x5410);  // (k2, k3)
+                o.z = prmt(r[0], r[1], 0x7632);  // (k4, k5)
+                o.w = prmt(r[2], r[3], 0x7632);  // (k6, k7)
+              }
+              *reinterpret_cast<uint4 *>(wrow + (((uint32_t)i ^ row_x) << 4)) = o;
+            }
+            tc::fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+          }
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&full_w[s]);
+        }
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&empty_p[ps]);   // this warp is done with the chunk (or had nothing in it)
       }
     }
   } else if (warp < 2 + kDqWarps) {
@@ -435,7 +565,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
               words[0] = wv.x;
               words[1] = wv.y;
             }
-            unsigned char *wstage = smem + s * L::kStageBytes;
+            unsigned char *wstage = smem + s * L::kWBytes;
             uint32_t s_hi = 0, s_lo = 0;
             if (!ASYM) split_bf16x2(cur.s, s_hi, s_lo);
 #pragma unroll
@@ -619,10 +749,10 @@ int cached_map(CUtensorMap *out, const void *ptr, CUtensorMapDataType dt, uint64
   return ZT_SUCCESS;
 }
 
-template <int BT, int STAGES, int PSTAGES>
+template <int BT, int STAGES, int XSTAGES, int PSTAGES>
 int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows, int max_row_tiles, bool asym,
               cudaStream_t st) {
-  using L = SmemLayout<BT, STAGES, PSTAGES>;
+  using L = SmemLayout<BT, STAGES, XSTAGES, PSTAGES>;
   static_assert(L::kTotal <= 227 * 1024, "rings exceed shared memory");
   TcParams p = p0;
   p.m_tiles = ceil_div(p.M, BT);
@@ -637,12 +767,12 @@ int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows,
   const int sms = sm_count();
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   if (asym) {
-    auto kern = woq_tcgen05_kernel<BT, STAGES, PSTAGES, true>;
+    auto kern = woq_tcgen05_kernel<BT, STAGES, XSTAGES, PSTAGES, true>;
     static PerDeviceOnce configured;
     if (int rc_cfg = allow_dynamic_smem(configured, kern, L::kTotal)) return rc_cfg;
     ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, p));
   } else {
-    auto kern = woq_tcgen05_kernel<BT, STAGES, PSTAGES, false>;
+    auto kern = woq_tcgen05_kernel<BT, STAGES, XSTAGES, PSTAGES, false>;
     static PerDeviceOnce configured;
     if (int rc_cfg = allow_dynamic_smem(configured, kern, L::kTotal)) return rc_cfg;
     ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, p));
@@ -653,10 +783,11 @@ int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows,
 int launch_any(int bt, const TcParams &p, const void *x, int64_t x_rows, int64_t w_rows, int max_row_tiles, bool asym,
                cudaStream_t st) {
   switch (bt) {
-    case 32: return launch_bt<32, 6, 5>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
-    case 64: return launch_bt<64, 5, 5>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
-    case 128: return launch_bt<128, 4, 4>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
-    case 256: return launch_bt<256, 3, 3>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+    // <token tile, converted-weight stages, activation slots, packed chunks>
+    case 32: return launch_bt<32, 4, 12, 5>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+    case 64: return launch_bt<64, 4, 7, 5>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+    case 128: return launch_bt<128, 4, 4, 4>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+    case 256: return launch_bt<256, 4, 3, 2>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
     default: break;
   }
   set_error("zt_woq_linear: unsupported token-tile width %d for the tcgen05 kernel", bt);

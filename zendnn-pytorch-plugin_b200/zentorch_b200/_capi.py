@@ -7,6 +7,7 @@ shipped C entry points themselves.  Tensors are passed as raw device pointers.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libzentorch_b200.so"
@@ -138,7 +139,7 @@ def _torch_boundary():
     """The operator library, when the package has loaded it (it keeps its own workspace pool)."""
     path = LIB_PATH.with_name("libzentorch_b200_torch.so")
     try:
-        return C.CDLL(str(path), mode=C.RTLD_NOLOAD)
+        return C.CDLL(str(path), mode=os.RTLD_NOLOAD | os.RTLD_NOW)
     except OSError:
         return None
 
