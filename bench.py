@@ -412,7 +412,11 @@ def bench_tp_layer(torch, dist, dev, stream, pk, world, rank, batches, kinds, re
                     _, y_tp = layers[0](x, attn)
                     stream.synchronize()
                     err = float((y_tp.float() - y_ref.float()).norm() / y_ref.float().norm())
-                    assert err < 3e-2, f"tensor-parallel {kind} M={m}: differs from the unsharded layer ({err:.3e})"
+                    # int8: a row-parallel rank quantises its K slice with its own per-token scale, so the two
+                    # chains of four quantised linears differ by their quantisation noise (a few percent);
+                    # per-operator parity against the oracle is what tests/test_tp_gpu.py checks
+                    limit = 3e-2 if kind == "woq" else 8e-2
+                    assert err < limit, f"tensor-parallel {kind} M={m}: differs from the unsharded layer ({err:.3e})"
                 else:
                     err = 0.0
 
