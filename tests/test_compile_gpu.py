@@ -58,3 +58,60 @@ def test_compiled_mlp_uses_fused_ops(zt):
     assert _compile.counters["zentorch"]["zentorch_woq_linear_gelu_tanh"] == 1
     h = model.up.oracle(x, [O.POST_GELU_TANH])
     assert_close_bf16(y, model.down.oracle(h))
+
+
+class DynLinear(torch.nn.Module):
+    """A dynamic-int8 linear calling the reference's operator directly (what the torchao / compressed-tensors
+    handlers emit)."""
+
+    def __init__(self, n, k, seed):
+        super().__init__()
+        from _util import make_int8_case
+        _, w, ws, b = make_int8_case(1, k, n, seed=seed)
+        self.w, self.ws, self.b = torch.nn.Buffer(w), torch.nn.Buffer(ws), torch.nn.Buffer(b)
+
+    def forward(self, x):
+        return torch.ops.zentorch.zentorch_dynamic_qlinear(x, self.w, self.ws, self.b)
+
+
+@pytest.mark.parametrize("cpp_wrapper", [False, True])
+def test_lowerings_python_and_cpp_wrapper(zt, cpp_wrapper, monkeypatch):
+    """The operators lowered to extern kernels: the Python wrapper calls the overload, the C++ wrapper calls the
+    aoti_torch_cuda_zentorch_* shims (the generated code is checked for the shim names, so this is the test
+    that runs them from Inductor's own caller).  Also compiles through backend="zentorch"."""
+    from zentorch_b200 import _compile
+    from torch._inductor.utils import run_and_get_code
+    zt.register_backend()
+    _compile.counters.clear()
+    torch._dynamo.reset()
+    model = MLP().cuda()
+    dyn = DynLinear(96, 256, seed=4).cuda()
+
+    def fn(x):
+        return dyn(torch.relu(model(x)))
+
+    x = torch.randn(24, 256, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    options = {"cpp_wrapper": True} if cpp_wrapper else {}
+    if cpp_wrapper:
+        # Inductor builds its C++ wrapper with -fopenmp; where the compiler driver runs under another prefix it
+        # does not find its own libgomp.spec unless the directory is on the library search path
+        import glob
+        import os
+        specs = glob.glob("/usr/lib/gcc/x86_64-linux-gnu/*/libgomp.spec")
+        if specs:
+            extra = os.path.dirname(specs[0])
+            monkeypatch.setenv("LIBRARY_PATH", extra + os.pathsep + os.environ.get("LIBRARY_PATH", ""))
+    with torch.no_grad():
+        y, codes = run_and_get_code(torch.compile(fn, backend="zentorch", options=options), x.cuda())
+    code = "\n".join(codes)
+    if cpp_wrapper:
+        # the relu after the second linear is folded into it by the unary-fusion pass
+        for shim in ("aoti_torch_cuda_zentorch_woq_linear_gelu_tanh", "aoti_torch_cuda_zentorch_woq_linear_relu",
+                     "aoti_torch_cuda_zentorch_dynamic_qlinear"):
+            assert shim in code, f"{shim} not called by the generated C++ wrapper"
+    else:
+        assert "zentorch_woq_linear" in code and "zentorch_dynamic_qlinear" in code
+    h = model.up.oracle(x, [O.POST_GELU_TANH])
+    h2 = torch.relu(model.down.oracle(h).float()).to(torch.bfloat16)
+    ref = O.dynamic_qlinear(h2, dyn.w.cpu(), dyn.ws.cpu(), dyn.b.cpu())
+    assert_close_bf16(y, ref, rtol=2e-2, atol=2e-2, frob=1e-2, what=f"compiled chain cpp_wrapper={cpp_wrapper}")

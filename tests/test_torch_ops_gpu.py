@@ -233,6 +233,27 @@ def test_aoti_shims_compute(zt):
         aoti_release(cap)
 
 
+def test_rowsum_cache_follows_the_weight(ops):
+    """The u8 mode keeps the weight's row sums with the boundary's record of the weight.  Repeated calls give the
+    same result, and a weight that is modified in place (its version changes) or replaced by a new tensor at
+    the same address gets fresh row sums."""
+    x, w, ws, b = make_int8_case(48, 256, 64, seed=22)
+    xd, wd, wsd, bd = x.cuda(), w.cuda(), ws.cuda(), b.cuda()
+    ref = O.dynamic_qlinear(x, w, ws, b, act_quant="u8_asym")
+    for _ in range(3):
+        y = ops.zentorch_dynamic_qlinear_ext(xd, wd, wsd, bd, act_quant="u8_asym")
+        assert_close_bf16(y, ref, what="u8 with cached row sums")
+    w2 = w.clone()
+    w2[::2] = -w2[::2]                                   # row sums change sign on every other row
+    wd.copy_(w2.cuda())                                  # in place: same storage, new version
+    ref2 = O.dynamic_qlinear(x, w2, ws, b, act_quant="u8_asym")
+    assert_close_bf16(ops.zentorch_dynamic_qlinear_ext(xd, wd, wsd, bd, act_quant="u8_asym"), ref2, what="after in-place update")
+    del wd
+    w3 = torch.roll(w, 1, 0).cuda()                      # very likely the same address, a new storage
+    ref3 = O.dynamic_qlinear(x, w3.cpu(), ws, b, act_quant="u8_asym")
+    assert_close_bf16(ops.zentorch_dynamic_qlinear_ext(xd, w3, wsd, bd, act_quant="u8_asym"), ref3, what="new tensor")
+
+
 def test_expired_device_wait_is_reported_and_cleared(zt):
     """A kernel whose bounded wait gives up (a barrier nobody signals, a few thousand polls) sets the device
     status word and returns; the host reads the code, clearing it also re-zeroes the split-K counters of the

@@ -16,6 +16,7 @@
 #include <torch/csrc/inductor/aoti_torch/utils.h>
 #include <torch/library.h>
 
+#include <functional>
 #include <map>
 #include <tuple>
 #include <mutex>
@@ -67,18 +68,38 @@ void check_on_device(const std::optional<at::Tensor> &t, const at::Tensor &input
 // tells a live storage from a new one at a recycled address.  A tensor seen in an earlier call, with its
 // storage still alive and its version unchanged, was produced before that call; anything else (first sight,
 // a temporary made inside this call) is passed on as ZT_FLAG_WEIGHTS_VOLATILE.
+//
+// The same record is the prepacked-weight cache (the reference lets ZenDNN reorder a constant weight once and
+// keep it: is_weights_const = true, src/cpu/cpp/WOQ_Linear.cpp:107, src/cpu/cpp/DynamicQLinear.cpp:128): an
+// entry can carry a by-product of the weight that is computed on first sight and reused afterwards -- here the
+// int32 row sums of an int8 weight, which the u8 activation mode needs in its epilogue.
 class SeenWeights {
  public:
   bool seen_before(const at::Tensor &t) {
-    if (!t.defined() || !t.has_storage()) return false;
+    at::Tensor unused;
+    return lookup(t, nullptr, &unused);
+  }
+  // `make` is called on first sight (or after the tensor changed) and its result kept with the entry; returns
+  // whether the tensor had been seen before, `*payload` receives the kept by-product.
+  bool lookup(const at::Tensor &t, const std::function<at::Tensor()> *make, at::Tensor *payload) {
+    if (!t.defined() || !t.has_storage()) {
+      if (make) *payload = (*make)();
+      return false;
+    }
     c10::StorageImpl *impl = t.storage().unsafeGetStorageImpl();
     const Key key{impl, t.storage_offset(), t.numel()};
     const int64_t version = t.is_inference() ? 0 : (int64_t)t._version();
     std::lock_guard<std::mutex> lock(mu_);
     auto it = map_.find(key);
-    if (it != map_.end() && !it->second.storage.expired() && it->second.version == version) return true;
+    if (it != map_.end() && !it->second.storage.expired() && it->second.version == version) {
+      if (make && !it->second.payload.defined()) it->second.payload = (*make)();
+      *payload = it->second.payload;
+      return true;
+    }
     if (map_.size() >= kMaxEntries) purge();
-    map_.insert_or_assign(key, Entry{t.storage().getWeakStorageImpl(), version});
+    Entry e{t.storage().getWeakStorageImpl(), version, make ? (*make)() : at::Tensor()};
+    *payload = e.payload;
+    map_.insert_or_assign(key, std::move(e));
     return false;
   }
 
@@ -91,6 +112,7 @@ class SeenWeights {
   struct Entry {
     c10::weak_intrusive_ptr<c10::StorageImpl> storage;
     int64_t version;
+    at::Tensor payload;   // prepack by-product, may be undefined
   };
   static constexpr size_t kMaxEntries = 1 << 16;
   void purge() {
@@ -323,20 +345,29 @@ at::Tensor dynamic_qlinear_impl(const at::Tensor &input, const at::Tensor &weigh
   at::Tensor w = weight.contiguous();
   at::Tensor ws = weight_scales.contiguous();
   at::Tensor b = has_bias ? bias->contiguous() : at::Tensor();
-  bool weights_const = seen_weights().seen_before(weight);
-  weights_const = seen_weights().seen_before(weight_scales) && w.is_same(weight) && ws.is_same(weight_scales) && weights_const;
+  const bool given_rowsum = weight_rowsum.has_value() && weight_rowsum->defined();
   at::Tensor rowsum;
-  if (act_quant == ZT_ACT_U8_ASYM) {
-    if (weight_rowsum.has_value() && weight_rowsum->defined()) {
-      TORCH_CHECK(weight_rowsum->scalar_type() == at::kInt && weight_rowsum->numel() == N,
-                  "weight_rowsum must be int32 with N values");
-      rowsum = weight_rowsum->contiguous();
-      weights_const = seen_weights().seen_before(*weight_rowsum) && rowsum.is_same(*weight_rowsum) && weights_const;
-    } else {
-      rowsum = at::empty({N}, w.options().dtype(at::kInt));
-      ZT_TORCH_CALL(zt_int8_weight_rowsum(w.data_ptr<int8_t>(), N, K, rowsum.data_ptr<int32_t>(), stream));
-      weights_const = false;
-    }
+  bool weights_const;
+  if (act_quant == ZT_ACT_U8_ASYM && !given_rowsum) {
+    // prepack by-product, computed when the weight is first seen and kept with its record
+    bool computed_now = false;
+    const std::function<at::Tensor()> make = [&]() {
+      at::Tensor r = at::empty({N}, w.options().dtype(at::kInt));
+      const int rc = zt_int8_weight_rowsum(w.data_ptr<int8_t>(), N, K, r.data_ptr<int32_t>(), stream);
+      TORCH_CHECK(rc == ZT_SUCCESS, zt_last_error());
+      computed_now = true;
+      return r;
+    };
+    weights_const = seen_weights().lookup(weight, &make, &rowsum) && !computed_now;
+  } else {
+    weights_const = seen_weights().seen_before(weight);
+  }
+  weights_const = seen_weights().seen_before(weight_scales) && w.is_same(weight) && ws.is_same(weight_scales) && weights_const;
+  if (act_quant == ZT_ACT_U8_ASYM && given_rowsum) {
+    TORCH_CHECK(weight_rowsum->scalar_type() == at::kInt && weight_rowsum->numel() == N,
+                "weight_rowsum must be int32 with N values");
+    rowsum = weight_rowsum->contiguous();
+    weights_const = seen_weights().seen_before(*weight_rowsum) && rowsum.is_same(*weight_rowsum) && weights_const;
   }
   const size_t ws_bytes = zt_dynamic_qlinear_workspace_bytes(M, K);
   at::Tensor scratch = at::empty({(int64_t)ws_bytes}, w.options().dtype(at::kByte));

@@ -249,15 +249,26 @@ class OptimizePass:
 
 
 def zentorch_b200_backend(gm: torch.fx.GraphModule, example_inputs, **kwargs):
-    """``torch.compile(model, backend="zentorch_b200")``."""
+    """``torch.compile(model, backend="zentorch_b200")`` (and ``backend="zentorch"`` when no other package
+    has taken that name).  ``options={"cpp_wrapper": True}`` and the other Inductor options pass through."""
     from torch._inductor import config as inductor_config
     from torch._inductor.compile_fx import compile_fx
 
-    with inductor_config.patch(joint_custom_post_pass=OptimizePass()):
+    options = kwargs.pop("options", None) or {}
+    with inductor_config.patch({"joint_custom_post_pass": OptimizePass(), **options}):
         return compile_fx(gm, example_inputs, **kwargs)
 
 
 @functools.lru_cache(None)
 def register_backend() -> None:
-    from torch._dynamo import register_backend as _reg
+    """Registers the Inductor lowerings of the operators and the compile backend.  The reference registers its
+    backend as "zentorch" (src/cpu/python/zentorch/_compile_backend.py:93-95); that name is taken here as well
+    unless a real zentorch has registered it already, so ``torch.compile(model, backend="zentorch")`` keeps
+    working for a model that moved to CUDA."""
+    from torch._dynamo import list_backends, register_backend as _reg
+
+    from . import _lowerings
+    _lowerings.register()
     _reg(name="zentorch_b200", compiler_fn=zentorch_b200_backend)
+    if "zentorch" not in list_backends(exclude_tags=()):
+        _reg(name="zentorch", compiler_fn=zentorch_b200_backend)
