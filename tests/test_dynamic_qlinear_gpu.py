@@ -157,3 +157,29 @@ def test_full_size_checksum_70b(capi):
     assert torch.equal(rows, (q.double() @ w_colsum.double()).round().long())
     expect_cols = torch.cat([(w[i:i + 4096].double() @ q_colsum.double()).round().long() for i in range(0, n, 4096)])
     assert torch.equal(cols, expect_cols)
+
+
+@pytest.mark.parametrize("bn", [128, 160, 192, 256])
+def test_cta_pair_tiles_match_the_one_cta_kernel(capi, bn):
+    """The tcgen05.mma.cta_group::2 form (two CTAs share every weight block): same int32 sums and the same fp32
+    epilogue as the one-CTA kernel, so the outputs are identical bit for bit.  Ragged M (a last pair tile with
+    one CTA partly or wholly past M), ragged N, K shorter than the ring, several tiles per CTA pair, both
+    activation forms, a post-op chain with a binary operand."""
+    cases = [(512, 4096, 1000, capi.ZT_ACT_U8_ASYM, (capi.ZT_POST_SILU,)), (600, 256, 3 * bn + 40, capi.ZT_ACT_S8_SYM, ()),
+             (257, 144, 72, capi.ZT_ACT_U8_ASYM, ()), (1300, 1024, 75 * bn, capi.ZT_ACT_S8_SYM, (capi.ZT_POST_GELU_TANH,))]
+    for (m, k, n, act, post) in cases:
+        x, w, ws, b = [t.cuda() for t in make_int8_case(m, k, n, seed=m + n)]
+        rowsum = capi.int8_weight_rowsum(w)
+        expect = capi.dynamic_qlinear(x, w, ws, b, act_quant=act, post_ops=post, w_rowsum=rowsum)
+        got = capi.dynamic_qlinear(x, w, ws, b, act_quant=act, post_ops=post, w_rowsum=rowsum,
+                                   algo=capi.ZT_ALGO_TCGEN05 | ((2000 + bn) << 8))
+        assert torch.equal(got, expect), f"pair tile {bn}: {(m, k, n)}"
+    m, k, n = 700, 512, 2 * bn + 8
+    x, w, ws, b = [t.cuda() for t in make_int8_case(m, k, n, seed=9)]
+    add = torch.randn(m, n, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+    expect = capi.dynamic_qlinear(x, w, ws, b, post_ops=(capi.ZT_POST_ADD,), buffers=(add,))
+    got = capi.dynamic_qlinear(x, w, ws, b, post_ops=(capi.ZT_POST_ADD,), buffers=(add,),
+                               algo=capi.ZT_ALGO_TCGEN05 | ((2000 + bn) << 8))
+    assert torch.equal(got, expect)
+    ref = O.dynamic_qlinear(x.cpu(), w.cpu(), ws.cpu(), b.cpu(), post_ops=[O.POST_ADD], buffers=[add.cpu()])
+    assert_close_bf16(got, ref, what=f"pair tile {bn} vs oracle")

@@ -333,6 +333,8 @@ int run_int8_gemm(Int8GemmArgs &g, int algo_and_tile, cudaStream_t st) {
     ZT_REQUIRE(int8_tcgen05_supported(g.M, g.N, g.K, g.q, g.w), ZT_UNSUPPORTED,
                "int8 tcgen05 kernel needs K %% 16 == 0 and 16-byte aligned operands");
     g.force_bn = tile_hint ? tile_hint : env().int8_bn;
+    // a width forced through the environment applies where that tile form exists; a hint is taken literally
+    if (!tile_hint && g.force_bn >= 2000 && (g.raw_s32 || g.M <= 256)) g.force_bn = 0;
     return int8_tcgen05_launch(g, st);
   }
   if (algo == ZT_ALGO_GENERIC) return int8_generic_launch(g, st);

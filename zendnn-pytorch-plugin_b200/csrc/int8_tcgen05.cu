@@ -106,8 +106,13 @@ int int8_tcgen05_launch(const Int8GemmArgs &a, cudaStream_t st) {
   p.post = a.post;
   p.status = device_status_ptr();
   const int epi = a.raw_s32 ? kEpiS32 : kEpiLinear;
-  // force_bn: tile width, + 1000 for 256-row tiles (e.g. 1160 = 256 x 160)
+  // force_bn: tile width, + 1000 for 256-row tiles (e.g. 1160 = 256 x 160), + 2000 for CTA pairs (512 x width)
   TileChoice tile = pick_tile(a.M, a.N, a.K);
+  if (a.force_bn >= 2000) {
+    ZT_REQUIRE(!a.raw_s32 && int8_pair_supported(a.M, a.force_bn % 1000), ZT_UNSUPPORTED,
+               "int8_tcgen05_launch: CTA-pair tiles need the linear epilogue, M > 256 and a width of 128, 160, 192 or 256");
+    return launch_pair(a.force_bn % 1000, a, p, !a.q_is_u8, st);
+  }
   if (a.force_bn > 0) tile = {a.force_bn >= 1000 ? 2 : 1, a.force_bn % 1000};
   const int bn = tile.bn;
   CUtensorMap ta, tb;

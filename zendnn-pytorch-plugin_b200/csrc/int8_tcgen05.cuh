@@ -399,6 +399,11 @@ int launch_bn(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, i
                   : launch_cfg<MH, BN, STAGES, NBUF, kEpiLinear, false>(ta, tb, p, st);
 }
 
+// CTA pairs (tcgen05.mma.cta_group::2): 512 x bn tiles, each CTA loads half of every weight block.  Linear
+// epilogue only.  Own translation unit (int8_tcgen05_pair.cu).
+bool int8_pair_supported(int64_t M, int bn);
+int launch_pair(int bn, const Int8GemmArgs &a, const TcParams &p, bool a_signed, cudaStream_t st);
+
 // 256-row tiles, instantiated in their own translation unit.
 int launch_mh2(int bn, const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, int epi, bool a_signed,
                cudaStream_t st);
