@@ -392,9 +392,11 @@ def bench_tp_layer(torch, dist, dev, stream, pk, world, rank, batches, kinds, re
     from zentorch_b200 import _capi, tp
     hidden, inter = 8192, 28672
     out = {}
+    # decode-size collectives (up to 1 MB) go through the all-reduce over peer memory, prefill through NCCL
+    peer_ar = tp.PeerAllReduce(max_bytes=1 << 20, device=dev) if world > 1 and os.environ.get("ZENTORCH_B200_PEER_AR", "1") != "0" else None
     for kind in kinds:
         fulls = [make_layer_params(torch, _capi, dev, kind, LLAMA70B, seed0=100 * (s + 1)) for s in range(2)]
-        layers = [tp.DecoderLayerLinears(kind, f, rank, world) for f in fulls]
+        layers = [tp.DecoderLayerLinears(kind, f, rank, world, peer_allreduce=peer_ar) for f in fulls]
         ref_layer = tp.DecoderLayerLinears(kind, fulls[0], 0, 1) if world > 1 else None
         if world == 1:
             fulls = None      # the shards of a single rank are the parameters themselves
@@ -436,7 +438,10 @@ def bench_tp_layer(torch, dist, dev, stream, pk, world, rank, batches, kinds, re
 
                     def coll():
                         for _ in range(2 * len(layers)):
-                            dist.all_reduce(buf)
+                            if peer_ar is not None and peer_ar.fits(buf):
+                                peer_ar(buf)
+                            else:
+                                dist.all_reduce(buf)
 
                     gc = capture_graph(torch, stream, coll)
                     gc.replay()
@@ -466,7 +471,8 @@ def bench_tp_layer(torch, dist, dev, stream, pk, world, rank, batches, kinds, re
                         "fused q/k/v and gate/up column-parallel, o and down row-parallel + NCCL all-reduce of "
                         "[M, 8192] bf16; one CUDA graph per step; two weight sets alternate (> L2)",
             "scaling": "strong", "n_gpus": world, "kinds": out,
-            "collective": "ncclAllReduce x 2 per layer (after o and after down)" if world > 1 else "none"}
+            "collective": ("2 all-reduces per layer (after o and after down): zt_allreduce_bf16 over peer memory up to "
+                           "1 MB, ncclAllReduce beyond") if world > 1 else "none"}
 
 
 def bench_e2e(torch, dev, sets, steps, world):

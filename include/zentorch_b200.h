@@ -86,7 +86,7 @@ ZT_API const char *zt_version(void);
  * is_avx512_supported, src/cpu/cpp/Utils.hpp:28-35). */
 ZT_API int zt_device_supported(void);
 /* Reads the device-side status word that a kernel sets when one of its bounded waits expires
- * (0 = none; 101..104 name the waiting role).  Synchronises with the device; `reset` clears it.
+ * (0 = none; 101..104 name the waiting role of a linear, 105 a peer that did not show up in zt_allreduce_bf16).  Synchronises with the device; `reset` clears it.
  * No counterpart in the reference (its failures are host exceptions, src/cpu/cpp/Utils.hpp:21-23). */
 ZT_API int zt_poll_device_status(int *status, int reset);
 /* Exercises that path without a fault: launches a one-thread kernel whose wait on a barrier nobody
@@ -275,6 +275,38 @@ typedef struct {
 
 ZT_API size_t zt_moe_woq_workspace_bytes(int64_t T, int64_t H, int64_t I, int32_t num_experts, int32_t top_k);
 ZT_API int zt_moe_woq(const zt_moe_woq_args_t *args, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * All-reduce of a small bf16 tensor over peer memory, for the collective that follows a row-parallel decode
+ * linear.  The reference has no communication code (it only makes its int4 tensors sliceable for vLLM's
+ * tensor-parallel loader, src/cpu/python/zentorch/vllm/_torchao_int4_opaque_patch.py:93-163); this is the
+ * B200 side of that sharding: one process per GPU, every GPU owns a symmetric buffer of
+ * zt_allreduce_symmetric_bytes(max_bytes) bytes that all peers can address (peer access enabled or an
+ * imported allocation), zero before the first call.
+ *
+ *   peer_base[r]  base address of rank r's symmetric buffer as seen from this GPU (r = rank: its own)
+ *   in, out       [numel] bf16 on this GPU, 16-byte aligned, numel a multiple of 8; may alias
+ *   epochs        two uint32 in this GPU's own memory, zero before the first call; the kernel numbers the
+ *                 calls with them (so a captured launch can be replayed)
+ *
+ * Every rank must issue the same sequence of calls with the same sizes.  Each rank adds the partial sums in
+ * rank order in fp32, so all ranks hold identical results.  A peer that does not show up within the poll
+ * limit (about a second) makes the call give up: the device status word is set (105) and `out` is left
+ * unwritten.  Tensors larger than max_bytes are refused (ZT_UNSUPPORTED): use the library collective. */
+#define ZT_AR_MAX_RANKS 8
+#define ZT_AR_MAX_SLICES 64
+typedef struct {
+  const void *in;
+  void *out;
+  int64_t numel;
+  void *peer_base[ZT_AR_MAX_RANKS];
+  int32_t rank, world;
+  size_t max_bytes; /* largest tensor, as given to zt_allreduce_symmetric_bytes */
+  uint32_t *epochs;
+} zt_allreduce_args_t;
+
+ZT_API size_t zt_allreduce_symmetric_bytes(size_t max_bytes);
+ZT_API int zt_allreduce_bf16(const zt_allreduce_args_t *args, void *stream);
 
 #ifdef __cplusplus
 }

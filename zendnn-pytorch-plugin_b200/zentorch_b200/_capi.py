@@ -29,7 +29,7 @@ EXPORTED_SYMBOLS = (
     "zt_woq_linear_workspace_bytes", "zt_woq_linear", "zt_woq_repack_weight", "zt_woq_repack_from_int4pack",
     "zt_dynamic_qlinear_workspace_bytes", "zt_dynamic_qlinear", "zt_dynamic_quantize", "zt_int8_gemm_s32",
     "zt_int8_weight_rowsum", "zt_qlinear_prequantized", "zt_dynamic_qlinear_static",
-    "zt_moe_woq_workspace_bytes", "zt_moe_woq",
+    "zt_moe_woq_workspace_bytes", "zt_moe_woq", "zt_allreduce_symmetric_bytes", "zt_allreduce_bf16",
 )
 
 
@@ -63,6 +63,16 @@ class MoeWoqArgs(C.Structure):
         ("top_k", C.c_int32), ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p), ("w13", C.c_void_p),
         ("s13", C.c_void_p), ("w2", C.c_void_p), ("s2", C.c_void_p), ("scale_dtype", C.c_int32),
         ("group_size", C.c_int64), ("y", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+ZT_AR_MAX_RANKS, ZT_AR_MAX_SLICES = 8, 64
+
+
+class AllReduceArgs(C.Structure):
+    _fields_ = [
+        ("in_", C.c_void_p), ("out", C.c_void_p), ("numel", C.c_int64), ("peer_base", C.c_void_p * ZT_AR_MAX_RANKS),
+        ("rank", C.c_int32), ("world", C.c_int32), ("max_bytes", C.c_size_t), ("epochs", C.c_void_p),
     ]
 
 
@@ -111,6 +121,9 @@ def lib() -> C.CDLL:
     L.zt_moe_woq_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32]
     L.zt_moe_woq.argtypes = [C.POINTER(MoeWoqArgs), C.c_void_p]
     L.zt_int8_weight_rowsum.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
+    L.zt_allreduce_symmetric_bytes.restype = C.c_size_t
+    L.zt_allreduce_symmetric_bytes.argtypes = [C.c_size_t]
+    L.zt_allreduce_bf16.argtypes = [C.POINTER(AllReduceArgs), C.c_void_p]
     _lib = L
     return L
 

@@ -146,6 +146,53 @@ def slice_activation_for_row_parallel(x: torch.Tensor, group=None) -> torch.Tens
     return x[..., rank * k // world:(rank + 1) * k // world].contiguous()
 
 
+# ---- all-reduce over peer memory for decode sizes -----------------------------------------------------
+class PeerAllReduce:
+    """In-place sum of a small bf16 tensor over the ranks of `group` with zt_allreduce_bf16: one kernel that
+    writes this rank's partial sums into its symmetric buffer, flags the peers and adds everybody's partial sums
+    read over NVLink.  The symmetric buffers come from torch's symmetric-memory allocator (one rendezvous at
+    construction); nothing is allocated per call and the call can be captured in a CUDA graph.  Tensors larger
+    than `max_bytes` are not accepted (`fits()`): the caller keeps the NCCL collective for those."""
+
+    def __init__(self, group=None, max_bytes=1 << 20, device=None):
+        import ctypes as C
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _capi
+        self._capi, self._C = _capi, C
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > _capi.ZT_AR_MAX_RANKS:
+            raise ValueError(f"at most {_capi.ZT_AR_MAX_RANKS} ranks")
+        self.max_bytes = int(max_bytes)
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        total = _capi.lib().zt_allreduce_symmetric_bytes(self.max_bytes)
+        self._buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
+        self._buf.zero_()
+        self._hdl = symm_mem.rendezvous(self._buf, group)
+        self._epochs = torch.zeros(_capi.ZT_AR_MAX_SLICES, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        self._hdl.barrier()          # every rank's flags are zero before anybody's first call
+        self._args = _capi.AllReduceArgs()
+        for r in range(self.world):
+            self._args.peer_base[r] = int(self._hdl.buffer_ptrs[r])
+        self._args.rank, self._args.world = self.rank, self.world
+        self._args.max_bytes = self.max_bytes
+        self._args.epochs = self._epochs.data_ptr()
+
+    def fits(self, t: torch.Tensor) -> bool:
+        return (t.dtype == torch.bfloat16 and t.is_contiguous() and t.numel() % 8 == 0
+                and t.numel() * 2 <= self.max_bytes and t.data_ptr() % 16 == 0)
+
+    def __call__(self, t: torch.Tensor) -> torch.Tensor:
+        a = self._args
+        a.in_, a.out, a.numel = t.data_ptr(), t.data_ptr(), t.numel()
+        stream = self._C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+        self._capi.check(self._capi.lib().zt_allreduce_bf16(self._C.byref(a), stream))
+        return t
+
+
 # ---- fused projections and a whole decoder layer's linears --------------------------------------------
 def fuse_woq_columns(parts):
     """Horizontal fusion of WOQ linears that share their input (q/k/v, gate/up): one linear whose output is
@@ -183,8 +230,9 @@ class DecoderLayerLinears:
     Every step is plain launches on the current stream plus NCCL calls, so a whole step can be captured
     in a CUDA graph and replayed without host code between the kernels."""
 
-    def __init__(self, kind, full, rank=0, world=1, group=None):
+    def __init__(self, kind, full, rank=0, world=1, group=None, peer_allreduce=None):
         self.kind, self.rank, self.world, self.group = kind, rank, world, group
+        self.peer_allreduce = peer_allreduce     # a PeerAllReduce for the decode-size collectives, or None
         shard = (lambda p, mode: shard_woq(*p, mode, rank, world)) if kind == "woq" else \
             (lambda p, mode: shard_int8(*p, mode, rank, world))
         fuse = fuse_woq_columns if kind == "woq" else fuse_int8_rows
@@ -200,6 +248,8 @@ class DecoderLayerLinears:
 
     def _reduce(self, y):
         if self.world > 1:
+            if self.peer_allreduce is not None and self.peer_allreduce.fits(y):
+                return self.peer_allreduce(y)
             dist.all_reduce(y, group=self.group)
         return y
 
