@@ -52,8 +52,9 @@ METRIC_TP = "dynamic int8 qlinear achieved TOP/s, Llama-3-70B decoder-layer proj
 # profiles/ (file named beside each figure); None where no capture exists for that kernel and workload.
 NCU_TRAFFIC = {
     "int8_tcgen05_kernel/config2": (47.4e6 + 11.3e6, "profiles/int8_tcgen05_kernel_config2.md"),
-    "woq_streamk_kernel/8192x28672_M1": (132.0e6, "profiles/woq_streamk_kernel_config3_layer.md"),
-    "woq_tcgen05_kernel/4096x14336_M2048": (67.6e6, "profiles/woq_tcgen05_kernel_prefill.md"),
+    "woq_stream_kernel/4096x4096_M1": (8.99e6, "profiles/woq_stream_kernel_config1_decode.md"),
+    "woq_streamk_kernel/8192x28672_M1": (131.5e6, "profiles/woq_streamk_kernel_decode_8192x28672.md"),
+    "moe_int4/config4": (503.4e6 + 27.8e6 + 285.7e6 + 5.5e6, "profiles/woq_tcgen05_kernel_moe_config4.md"),
 }
 
 # Llama-3-70B decoder layer (BASELINE config 5): name -> (K, N)
@@ -365,7 +366,8 @@ def bench_moe_config(torch, _capi, dev, pk):
             "us_per_call": round(us, 1), "weight_bytes": w_bytes, "weight_GBps": round(w_bytes / (us * 1e-6) / 1e9, 1),
             "frac_of_hbm_peak": round(w_bytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 4),
             "TFLOPps": round(flops / (us * 1e-6) / 1e12, 1),
-            "l2": "705 MB of expert weights per call exceed L2", "launch": "plain launches on the current stream"}
+            "l2": "705 MB of expert weights per call exceed L2", "launch": "plain launches on the current stream",
+            "traffic": traffic("moe_int4/config4")}
 
 
 # ---- config 5: tensor-parallel decoder layer ----------------------------------------------------------------

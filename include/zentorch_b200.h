@@ -31,7 +31,7 @@ typedef enum {
   ZT_DEVICE_TIMEOUT = 5 /* a bounded device-side wait expired; the context stays usable */
 } zt_status_t;
 
-typedef enum { ZT_BF16 = 0, ZT_F32 = 1 } zt_dtype_t;
+typedef enum { ZT_BF16 = 0, ZT_F32 = 1, ZT_U8 = 2, ZT_S8 = 3 } zt_dtype_t; /* 8-bit types: static qlinear only */
 
 /* Post-op ids; same values as UNARY_POST_OP / BINARY_POST_OP in src/cpu/cpp/Utils.hpp:56-72. */
 typedef enum {
@@ -240,6 +240,65 @@ ZT_API int zt_int8_gemm_s32(const void *q, int32_t q_is_u8, const int8_t *w, int
 
 /* rowsum[n] = sum_k W[n,k]; a one-off weight-prepack by-product used by ZT_ACT_U8_ASYM. */
 ZT_API int zt_int8_weight_rowsum(const int8_t *w, int64_t N, int64_t K, int32_t *rowsum, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * zentorch_qlinear and its _relu / _sigmoid / _mul_add / .out variants: the static-quantisation linear
+ * (zentorch_quantized_matmul_impl, src/cpu/cpp/QLinear.cpp:66-366; operators :368-591).
+ *
+ *   q   = x                                             when x is u8 / s8 already, else
+ *   q   = clamp(rint(x * (1 / s_x)) + zp_x)             u8 when x_zero_point is given, s8 (zp = 0) otherwise
+ *   acc = sum_k (q[m,k] - zp_x) * W[n,k]                exact int32
+ *   v   = post_ops( acc * (s_x * s_w[n]) + bias[n] )    fp32
+ *   y   = v                                             as fp32 / bf16 when out_scale is NULL, else
+ *   y   = clamp(rint(v * (1 / s_o)) + zp_o)             u8 when out_zero_point is given, s8 otherwise
+ *
+ * Scales and zero points are per tensor and live in device memory (they are tensors at the operator
+ * level; nothing is read back to the host): one float / one int32 each.  The weight is symmetric s8 [N, K]
+ * with one scale or one per output channel; weight zero points are not supported by the reference either
+ * (QLinear.cpp:255-270).
+ *
+ * x          [M, K] row-major: ZT_F32 / ZT_BF16 (quantised by the call) or ZT_U8 / ZT_S8.  An unsigned
+ *            input needs x_zero_point, a signed one must not have it.
+ * w_rowsum   [N] int32 (zt_int8_weight_rowsum), required when x_zero_point is given.
+ * post       chain of zt_post_op_t; binary operands are [M, N] contiguous arrays of post_buffer_dtype
+ *            (ZT_F32 / ZT_BF16), whatever the output dtype (src/cpu/cpp/MatmulUtils.hpp:418-429).
+ * y, ldy     output of y_dtype, row m at y + m * ldy elements (ldy >= N; the .out operators write into
+ *            views of wider buffers, QLinear.cpp:409-411).
+ * workspace  at least zt_static_qlinear_workspace_bytes(M, K, x_dtype) bytes, 256-byte aligned: holds the
+ *            quantised activations (nothing when x is quantised already). */
+typedef struct {
+  const void *x;
+  int32_t x_dtype;
+  int64_t M, K, N;
+  const float *x_scale;
+  const int32_t *x_zero_point; /* NULL: signed activations */
+  const int8_t *w;
+  const float *w_scales;
+  int64_t w_scales_numel;      /* 1 or N */
+  const int32_t *w_rowsum;
+  const void *bias;            /* [N] or NULL */
+  int32_t bias_dtype;
+  zt_post_ops_t post;
+  int32_t post_buffer_dtype;
+  const float *out_scale;          /* NULL: float output */
+  const int32_t *out_zero_point;   /* NULL with out_scale: s8 output */
+  void *y;
+  int32_t y_dtype;
+  int64_t ldy;
+  void *workspace;
+  size_t workspace_bytes;
+  int32_t algo;
+  int32_t flags; /* ZT_FLAG_* bits */
+} zt_static_qlinear_args_t;
+
+ZT_API size_t zt_static_qlinear_workspace_bytes(int64_t M, int64_t K, int32_t x_dtype);
+ZT_API int zt_static_qlinear(const zt_static_qlinear_args_t *args, void *stream);
+
+/* The quantisation step of zt_static_qlinear on its own (quantize_bf16_to_int8 and the
+ * at::quantize_per_tensor call of src/cpu/cpp/QLinear.cpp:14-64,140-157): numel elements of fp32 / bf16 to
+ * u8 (zero_point given) or s8. */
+ZT_API int zt_static_quantize(const void *x, int32_t x_dtype, int64_t numel, const float *scale,
+                              const int32_t *zero_point, void *q, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Mixture-of-experts FFN with int4 weight-only experts (Mixtral style, symmetric group-wise scales).

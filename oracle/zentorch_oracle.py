@@ -270,6 +270,102 @@ def dynamic_qlinear(x: torch.Tensor, weight: torch.Tensor, weight_scales: torch.
 
 
 # --------------------------------------------------------------------------------------------
+# Static-quant qlinear  (src/cpu/cpp/QLinear.cpp:66-591)
+# --------------------------------------------------------------------------------------------
+_QRANGE = {torch.uint8: (0, 255), torch.int8: (-128, 127)}
+
+
+def quantize_per_tensor(x: torch.Tensor, scale: torch.Tensor, zero_point: Optional[torch.Tensor]) -> torch.Tensor:
+    """q = clamp(rint(x * (1 / s)) + zp, lo, hi) in fp32: unsigned 8 bit when a zero point is given, signed 8
+    bit with zp = 0 otherwise (src/cpu/cpp/QLinear.cpp:14-17,120-157; the multiplication by the reciprocal is
+    what torch.fake_quantize_per_tensor_affine and quantized_decomposed.quantize_per_tensor do, which the
+    reference's tests use as the truth: test/unittests/quant_utils.py:33-36,72-79)."""
+    inv = 1.0 / scale.reshape(()).float()
+    dt = torch.uint8 if zero_point is not None else torch.int8
+    lo, hi = _QRANGE[dt]
+    zp = 0 if zero_point is None else int(zero_point.reshape(()).item())
+    return torch.clamp(torch.round(x.float() * inv) + zp, lo, hi).to(dt)
+
+
+def static_qlinear(x: torch.Tensor, weight: torch.Tensor, input_scales: torch.Tensor,
+                   input_zero_points: Optional[torch.Tensor], weight_scales: torch.Tensor,
+                   weight_zero_points: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                   output_scales: Optional[torch.Tensor] = None, output_zero_points: Optional[torch.Tensor] = None,
+                   output_dtype: Optional[torch.dtype] = None, post_ops: Sequence[int] = (),
+                   buffers: Sequence[torch.Tensor] = (), return_parts: bool = False):
+    """zentorch_qlinear and its _relu / _sigmoid / _mul_add variants.
+
+    The activations are quantised per tensor with the caller's scale and zero point (or arrive as u8 / s8
+    already), the weight is symmetric s8 [N, K] with one scale or one per output channel; with integer
+    accumulation acc = sum_k (q - zp_x) W,  y = post_ops(acc * (s_x * s_w[n]) + bias[n]) in fp32.  Without
+    output scales y is cast to float32 / bfloat16; with them it is requantised per tensor,
+    clamp(rint(y * (1 / s_o)) + zp_o), to u8 when a zero point is given and to s8 otherwise
+    (test/unittests/quant_utils.py:13-83 is the float restatement the reference's tests compare with;
+    checks and their messages: src/cpu/cpp/MatmulUtils.hpp:331-525)."""
+    if x.dtype not in (torch.float32, torch.bfloat16, torch.uint8, torch.int8):
+        raise RuntimeError("unsupported dtype for input tensor, only float32/bfloat16/uint8/int8 is supported")
+    if weight.dtype != torch.int8:
+        raise RuntimeError("unsupported dtype for weight tensor, only int8 is supported")
+    if bias is not None and bias.dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError("unsupported dtype for bias tensor, only float32 or bfloat16 is supported")
+    if input_scales.dtype != torch.float32:
+        raise RuntimeError("unsupported dtype for input_scales, only float32 is supported")
+    if input_zero_points is not None and input_zero_points.dtype != torch.int32:
+        raise RuntimeError("unsupported dtype for input_zero_points, only int32 supported")
+    if weight_scales.dtype != torch.float32:
+        raise RuntimeError("unsupported dtype for weight_scales, only float32 is supported")
+    if weight_zero_points is not None and weight_zero_points.dtype != torch.int32:
+        raise RuntimeError("unsupported dtype for weight_zero_points, only int32 is supported")
+    if output_dtype is None:
+        output_dtype = torch.float32
+    if output_dtype not in (torch.float32, torch.bfloat16, torch.uint8, torch.int8):
+        raise RuntimeError("output_dtype received is not yet supported, only float32/bfloat16/uint8/int8 is supported")
+    n, k = weight.shape
+    if x.shape[-1] != k:
+        raise RuntimeError("unsupported shapes for input and weight")
+    if input_scales.dim() > 1:
+        raise RuntimeError("unsupported dims for input_scales with respect to input tensor")
+    if input_zero_points is not None and input_zero_points.numel() != 1:
+        raise RuntimeError("only supporting per-tensor quantization for input")
+    if input_scales.numel() != 1:
+        raise RuntimeError("unsupported number of elements for input_scales with respect to input tensor")
+    if weight_scales.dim() > 1:
+        raise RuntimeError("unsupported dims for weight_scales with respect to weight tensor")
+    if weight_scales.numel() not in (1, n):
+        raise RuntimeError("unsupported number of elements for weight_scales with respect to weight tensor")
+    if output_scales is not None:
+        want = torch.uint8 if output_zero_points is not None else torch.int8
+        if output_dtype != want:
+            raise RuntimeError("unsupported dtype for result tensor when output_scales are defined")
+    elif output_dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError("unsupported dtype for result tensor, only float32/bfloat16 is supported when "
+                           "output_scales are not defined")
+    x2 = x.reshape(-1, k)
+    if x.dtype in (torch.uint8, torch.int8):
+        q = x2
+    else:
+        q = quantize_per_tensor(x2, input_scales, input_zero_points)
+    zp = 0 if input_zero_points is None else int(input_zero_points.reshape(()).item())
+    acc = int_gemm(q, weight)
+    wsum = weight.sum(dim=1, dtype=torch.int64)
+    accf = (acc.long() - zp * wsum.unsqueeze(0)).float()
+    ws = weight_scales.reshape(-1).float()
+    y = accf * (input_scales.reshape(()).float() * ws.unsqueeze(0))
+    if bias is not None:
+        y = y + bias.float()
+    y = apply_post_ops(y, post_ops, [b.reshape(-1, n) for b in buffers])
+    if output_scales is not None:
+        lo, hi = _QRANGE[output_dtype]
+        zo = 0 if output_zero_points is None else int(output_zero_points.reshape(()).item())
+        inv = 1.0 / output_scales.reshape(()).float()
+        y = torch.clamp(torch.round(y * inv) + zo, lo, hi)
+    y = y.reshape(*x.shape[:-1], n).to(output_dtype)
+    if return_parts:
+        return q, acc, y
+    return y
+
+
+# --------------------------------------------------------------------------------------------
 # Compositions without a reference counterpart (parity unpinned)
 # --------------------------------------------------------------------------------------------
 def route_top2(logits: torch.Tensor, top_k: int = 2):

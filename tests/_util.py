@@ -14,6 +14,49 @@ def bf16_from_bits(a: np.ndarray) -> torch.Tensor:
     return torch.from_numpy(np.ascontiguousarray(a)).view(torch.bfloat16)
 
 
+QLINEAR_POST = {"none": (), "relu": (1,), "sigmoid": (5,), "mul_add": (7, 8)}   # post-op ids of the oracle / C ABI
+
+
+def qlinear_golden_cases():
+    """The static-qlinear cases of tests/golden/zentorch_qlinear_golden.npz (made by the reference's qdq_linear)
+    as dictionaries of torch tensors: x, xs, xzp (None for signed activations), w, ws, bias, os / ozp (None
+    unless the output is requantised), out_dtype, post (post-op ids), buffers, y (the reference result)."""
+    g = np.load(ROOT / "tests" / "golden" / "zentorch_qlinear_golden.npz")
+    w, bias = torch.from_numpy(g["w"]), torch.from_numpy(g["bias"])
+    cases = []
+    for name in g["cases"]:
+        tag, x_kind, asym, per_channel, out_kind, eltwise = str(name).split(":")
+        x = bf16_from_bits(g[tag + "_x"]) if x_kind == "bfloat16" else torch.from_numpy(g[tag + "_x"])
+        y = bf16_from_bits(g[tag + "_y"]) if out_kind == "bfloat16" else torch.from_numpy(g[tag + "_y"])
+        c = dict(name=str(name), x=x, xs=torch.from_numpy(g[tag + "_xs"]), w=w, ws=torch.from_numpy(g[tag + "_ws"]),
+                 xzp=torch.from_numpy(g[tag + "_xzp"]) if asym == "1" else None, bias=bias, os=None, ozp=None,
+                 out_dtype=getattr(torch, out_kind), post=QLINEAR_POST[eltwise], buffers=(), y=y, eltwise=eltwise)
+        if out_kind in ("uint8", "int8"):
+            c["os"] = torch.from_numpy(g[tag + "_os"])
+            c["ozp"] = torch.from_numpy(g[tag + "_ozp"]) if out_kind == "uint8" else None
+        if eltwise == "mul_add":
+            c["buffers"] = (torch.from_numpy(g[tag + "_mul"]), torch.from_numpy(g[tag + "_add"]))
+        cases.append(c)
+    return cases
+
+
+def assert_qlinear_close(got, ref, what):
+    """Float outputs: the reference's own tolerance for zentorch_qlinear (atol = rtol = 1e-2,
+    test/unittests/op_tests/test_qlinear.py:607-609) and a hundred times tighter in the mean.  Requantised
+    outputs: the float restatement and the integer evaluation may land on different sides of a rounding
+    boundary, so at most one step apart anywhere and equal in at least 99 % of the elements."""
+    assert got.dtype == ref.dtype and got.shape == ref.shape, what
+    if ref.dtype in (torch.uint8, torch.int8):
+        d = (got.to(torch.int32) - ref.to(torch.int32)).abs()
+        assert int(d.max()) <= 1, f"{what}: requantised outputs differ by {int(d.max())} steps"
+        assert float((d == 0).float().mean()) >= 0.99, f"{what}: {float((d != 0).float().mean()):.3%} of the outputs differ"
+    else:
+        g, r = got.float(), ref.float()
+        assert torch.allclose(g, r, atol=1e-2, rtol=1e-2), f"{what}: max diff {float((g - r).abs().max()):.3e}"
+        lim = 1e-4 if ref.dtype == torch.float32 else 4e-3
+        assert float((g - r).abs().mean()) <= lim * max(1.0, float(r.abs().mean())), what
+
+
 def load_c_oracle() -> C.CDLL:
     so = ROOT / "oracle" / "_build" / "libzentorch_oracle.so"
     src = ROOT / "oracle" / "zentorch_oracle.c"

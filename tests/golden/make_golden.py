@@ -11,6 +11,9 @@ Sources of truth used here (none of them is our code):
     test/unittests/op_tests/test_woq_linear_asymmetric.py:100-142 compares the op against.
   * the formulas written out in test_woq_linear.py:71-96,107-136 and test_dynamic_qlinear.py:32-36,83-92,
     evaluated with stock torch ops exactly as those tests evaluate them.
+  * test/unittests/quant_utils.py:13-83 (``qdq_linear``), imported and called as it is: the float restatement
+    that test/unittests/op_tests/test_qlinear*.py compare zentorch_qlinear with.  Its cases go into
+    tests/golden/zentorch_qlinear_golden.npz (``python make_golden.py qlinear`` writes only that file).
 """
 import importlib.util
 import os
@@ -24,6 +27,7 @@ if "ZENTORCH_REFERENCE_ROOT" not in os.environ:
     raise SystemExit("set ZENTORCH_REFERENCE_ROOT to a checkout of amd/ZenDNN-pytorch-plugin")
 REF = Path(os.environ["ZENTORCH_REFERENCE_ROOT"])
 OUT = Path(__file__).resolve().parent / "zentorch_golden.npz"
+OUT_QLINEAR = Path(__file__).resolve().parent / "zentorch_qlinear_golden.npz"
 
 
 def _load_pack_module():
@@ -116,5 +120,81 @@ def main():
     print("wrote", OUT, OUT.stat().st_size, "bytes")
 
 
+def _load_quant_utils():
+    import torch.ao.quantization.fx._decomposed  # noqa: F401  (registers torch.ops.quantized_decomposed)
+    spec = importlib.util.spec_from_file_location("ref_quant_utils", REF / "test/unittests/quant_utils.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def main_qlinear():
+    """Static-quant qlinear cases: every combination of input dtype (fp32, bf16, already-quantised u8 / s8),
+    input zero-point kind, weight-scale granularity and output dtype that
+    test/unittests/op_tests/test_qlinear.py:540-610 runs, plus relu / sigmoid (test_qlinear_eltwise.py) and
+    mul_add (test_qlinear_mul_add.py), all evaluated by the reference's qdq_linear."""
+    torch.manual_seed(4321)
+    torch.set_num_threads(1)
+    qu = _load_quant_utils()
+    out, names = {}, []
+    m, k, n = 9, 96, 40
+    w = torch.randint(-128, 128, (n, k), dtype=torch.int8)
+    bias = torch.randn(n)
+    idx = 0
+    for x_kind in ("float32", "bfloat16", "uint8", "int8"):
+        for per_channel in (False, True):
+            for out_kind in ("float32", "bfloat16", "uint8", "int8"):
+                for eltwise in ("none", "relu", "sigmoid"):
+                    if eltwise != "none" and (x_kind in ("uint8", "int8") or per_channel is False):
+                        continue                      # the element-wise variants on the main float cases only
+                    xs = torch.rand(1) * 0.03 + 0.01
+                    asym = x_kind in ("float32", "uint8") or (x_kind == "bfloat16" and idx % 2 == 0)
+                    if x_kind == "int8":
+                        asym = False
+                    xzp = torch.randint(100, 156, (1,), dtype=torch.uint8) if asym else torch.zeros(1, dtype=torch.int8)
+                    if x_kind == "uint8":
+                        x = torch.randint(0, 256, (m, k), dtype=torch.uint8)
+                    elif x_kind == "int8":
+                        x = torch.randint(-128, 128, (m, k), dtype=torch.int8)
+                    else:
+                        x = (torch.randn(m, k) * 1.5).to(getattr(torch, x_kind))
+                    ws = torch.rand(n if per_channel else 1) * 0.004 + 0.001
+                    wzp = torch.zeros(n if per_channel else 1, dtype=torch.int8)
+                    os_, ozp = None, None
+                    if out_kind in ("uint8", "int8"):
+                        os_ = torch.rand(1) * 0.02 + 0.03
+                        ozp = (torch.randint(90, 166, (1,), dtype=torch.uint8) if out_kind == "uint8"
+                               else torch.zeros(1, dtype=torch.int8))
+                    fn = {"none": None, "relu": torch.relu, "sigmoid": torch.sigmoid}[eltwise]
+                    y = qu.qdq_linear(x, w, bias, xs, xzp, ws, wzp, fn, getattr(torch, out_kind), os_, ozp)
+                    tag = f"c{idx}"
+                    names.append(f"{tag}:{x_kind}:{int(asym)}:{int(per_channel)}:{out_kind}:{eltwise}")
+                    out[tag + "_x"], out[tag + "_xs"], out[tag + "_xzp"] = bits(x), bits(xs), bits(xzp.to(torch.int32))
+                    out[tag + "_ws"] = bits(ws)
+                    if os_ is not None:
+                        out[tag + "_os"], out[tag + "_ozp"] = bits(os_), bits(ozp.to(torch.int32))
+                    out[tag + "_y"] = bits(y)
+                    idx += 1
+    # mul_add: (linear * mul) + add, float outputs (test_qlinear_mul_add.py)
+    for x_kind in ("float32", "bfloat16"):
+        x = (torch.randn(m, k) * 1.5).to(getattr(torch, x_kind))
+        xs, xzp = torch.rand(1) * 0.03 + 0.01, torch.randint(100, 156, (1,), dtype=torch.uint8)
+        ws, wzp = torch.rand(n) * 0.004 + 0.001, torch.zeros(n, dtype=torch.int8)
+        mul, add = torch.randn(m, n), torch.randn(m, n)
+        y = qu.qdq_linear(x, w, bias, xs, xzp, ws, wzp, lambda t: t * mul + add, torch.float32)
+        tag = f"c{idx}"
+        names.append(f"{tag}:{x_kind}:1:1:float32:mul_add")
+        out[tag + "_x"], out[tag + "_xs"], out[tag + "_xzp"], out[tag + "_ws"] = (
+            bits(x), bits(xs), bits(xzp.to(torch.int32)), bits(ws))
+        out[tag + "_mul"], out[tag + "_add"], out[tag + "_y"] = bits(mul), bits(add), bits(y)
+        idx += 1
+    out["w"], out["bias"] = bits(w), bits(bias)
+    out["cases"] = np.array(names)
+    np.savez_compressed(OUT_QLINEAR, **out)
+    print("wrote", OUT_QLINEAR, OUT_QLINEAR.stat().st_size, "bytes,", idx, "cases")
+
+
 if __name__ == "__main__":
-    sys.exit(main())
+    if sys.argv[1:] != ["qlinear"]:
+        main()
+    main_qlinear()

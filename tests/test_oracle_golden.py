@@ -6,7 +6,7 @@ import numpy as np
 import torch
 
 import zentorch_oracle as O
-from _util import bf16_from_bits, make_woq_case, make_int8_case
+from _util import assert_qlinear_close, bf16_from_bits, make_woq_case, make_int8_case, qlinear_golden_cases
 
 
 def _ptr(t):
@@ -78,6 +78,46 @@ def test_dynamic_qlinear_matches_reference_formula(golden):
     assert y.shape == ref.shape
     assert torch.allclose(y, ref, atol=1e-2, rtol=1e-2)      # test_dynamic_qlinear.py:102-103
     assert torch.allclose(y, ref, atol=1e-3, rtol=1e-5)
+
+
+def test_static_qlinear_matches_reference_formula():
+    """zentorch_qlinear and its relu / sigmoid / mul_add variants against the reference's qdq_linear
+    (test/unittests/quant_utils.py:13-83) over input dtype x zero-point kind x weight granularity x output dtype."""
+    cases = qlinear_golden_cases()
+    assert len(cases) >= 48
+    seen = set()
+    for c in cases:
+        y = O.static_qlinear(c["x"], c["w"], c["xs"], c["xzp"], c["ws"], None, c["bias"], c["os"], c["ozp"],
+                             c["out_dtype"], c["post"], c["buffers"])
+        assert_qlinear_close(y, c["y"], c["name"])
+        seen.add((c["x"].dtype, c["out_dtype"], c["eltwise"]))
+    assert {d for d, _, _ in seen} == {torch.float32, torch.bfloat16, torch.uint8, torch.int8}
+    assert {e for _, _, e in seen} == {"none", "relu", "sigmoid", "mul_add"}
+
+
+def test_static_qlinear_error_messages():
+    import pytest
+    x, w = torch.zeros(2, 8), torch.zeros(4, 8, dtype=torch.int8)
+    s1, z1, sw = torch.ones(1), torch.zeros(1, dtype=torch.int32), torch.ones(4)
+    # messages of src/cpu/cpp/MatmulUtils.hpp:357-415,453-475 and src/cpu/cpp/QLinear.cpp:379-383
+    with pytest.raises(RuntimeError, match="unsupported dtype for input tensor"):
+        O.static_qlinear(x.half(), w, s1, z1, sw)
+    with pytest.raises(RuntimeError, match="unsupported dtype for weight tensor, only int8 is supported"):
+        O.static_qlinear(x, w.float(), s1, z1, sw)
+    with pytest.raises(RuntimeError, match="unsupported dtype for bias tensor"):
+        O.static_qlinear(x, w, s1, z1, sw, None, torch.zeros(4, dtype=torch.float16))
+    with pytest.raises(RuntimeError, match="unsupported dtype for input_scales"):
+        O.static_qlinear(x, w, s1.half(), z1, sw)
+    with pytest.raises(RuntimeError, match="unsupported dtype for input_zero_points"):
+        O.static_qlinear(x, w, s1, z1.float(), sw)
+    with pytest.raises(RuntimeError, match="unsupported number of elements for input_scales"):
+        O.static_qlinear(x, w, torch.ones(2), z1, sw)
+    with pytest.raises(RuntimeError, match="unsupported number of elements for weight_scales"):
+        O.static_qlinear(x, w, s1, z1, torch.ones(3))
+    with pytest.raises(RuntimeError, match="output_dtype received is not yet supported"):
+        O.static_qlinear(x, w, s1, z1, sw, output_dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="when output_scales are not defined"):
+        O.static_qlinear(x, w, s1, z1, sw, output_dtype=torch.uint8)
 
 
 def test_error_messages_follow_the_reference():

@@ -429,6 +429,98 @@ extern "C" int zt_qlinear_prequantized(const zt_dynamic_qlinear_args_t *a, const
   return run_int8_gemm(g, a->algo, (cudaStream_t)stream);
 }
 
+// ---- static-quantisation qlinear ------------------------------------------------------------------------
+extern "C" size_t zt_static_qlinear_workspace_bytes(int64_t M, int64_t K, int32_t x_dtype) {
+  if (M <= 0 || K <= 0 || x_dtype == ZT_U8 || x_dtype == ZT_S8) return 256;
+  return align_up((size_t)M * K, 256);
+}
+
+extern "C" int zt_static_quantize(const void *x, int32_t x_dtype, int64_t numel, const float *scale,
+                                  const int32_t *zero_point, void *q, void *stream) {
+  ZT_REQUIRE(numel >= 0, ZT_INVALID_ARGUMENT, "zt_static_quantize: negative size");
+  if (numel == 0) return ZT_SUCCESS;
+  ZT_REQUIRE(x && scale && q, ZT_INVALID_ARGUMENT, "zt_static_quantize: null pointer");
+  ZT_REQUIRE(valid_dtype(x_dtype), ZT_INVALID_ARGUMENT, "zt_static_quantize: input must be bfloat16 or float32");
+  return static_quantize_launch(x, x_dtype, numel, scale, zero_point, q, (cudaStream_t)stream);
+}
+
+extern "C" int zt_static_qlinear(const zt_static_qlinear_args_t *a, void *stream) {
+  ZT_REQUIRE(a != nullptr, ZT_INVALID_ARGUMENT, "zt_static_qlinear: null argument block");
+  ZT_REQUIRE(a->M >= 0 && a->N >= 0 && a->K >= 0, ZT_INVALID_ARGUMENT, "zt_static_qlinear: negative size");
+  const bool x_quantized = a->x_dtype == ZT_U8 || a->x_dtype == ZT_S8;
+  ZT_REQUIRE(valid_dtype(a->x_dtype) || x_quantized, ZT_INVALID_ARGUMENT,
+             "unsupported dtype for input tensor, only float32/bfloat16/uint8/int8 is supported");
+  ZT_REQUIRE(!a->bias || valid_dtype(a->bias_dtype), ZT_INVALID_ARGUMENT,
+             "unsupported dtype for bias tensor, only float32 or bfloat16 is supported");
+  ZT_REQUIRE(a->y_dtype == ZT_F32 || a->y_dtype == ZT_BF16 || a->y_dtype == ZT_U8 || a->y_dtype == ZT_S8,
+             ZT_INVALID_ARGUMENT, "unsupported dtype for result tensor, only float32/bfloat16/uint8/int8 is supported");
+  if (a->out_scale) {
+    ZT_REQUIRE(a->y_dtype == (a->out_zero_point ? ZT_U8 : ZT_S8), ZT_INVALID_ARGUMENT,
+               "unsupported dtype for result tensor when output_scales are defined: uint8 with output_zero_points, "
+               "int8 without");
+  } else {
+    ZT_REQUIRE(!a->out_zero_point && valid_dtype(a->y_dtype), ZT_INVALID_ARGUMENT,
+               "unsupported dtype for result tensor, only float32/bfloat16 is supported when output_scales are not "
+               "defined");
+  }
+  ZT_REQUIRE(a->x_dtype != ZT_U8 || a->x_zero_point, ZT_INVALID_ARGUMENT,
+             "zt_static_qlinear: an unsigned 8-bit input needs input_zero_points");
+  ZT_REQUIRE(a->x_dtype != ZT_S8 || !a->x_zero_point, ZT_INVALID_ARGUMENT,
+             "zt_static_qlinear: a signed 8-bit input takes no input_zero_points");
+  ZT_REQUIRE(a->w_scales_numel == 1 || a->w_scales_numel == a->N, ZT_INVALID_ARGUMENT,
+             "unsupported number of elements for weight_scales with respect to weight tensor");
+  ZT_REQUIRE(valid_dtype(a->post_buffer_dtype), ZT_INVALID_ARGUMENT,
+             "unsupported dtype for post_ops, only float32/bfloat16 is supported");
+  if (a->M == 0 || a->N == 0) return ZT_SUCCESS;
+  ZT_REQUIRE(a->K >= 1, ZT_INVALID_ARGUMENT, "zt_static_qlinear: K must be positive");
+  ZT_REQUIRE(a->x && a->x_scale && a->w && a->w_scales && a->y, ZT_INVALID_ARGUMENT,
+             "zt_static_qlinear: null tensor pointer");
+  ZT_REQUIRE(!a->x_zero_point || a->w_rowsum, ZT_INVALID_ARGUMENT,
+             "zt_static_qlinear: input_zero_points need w_rowsum (zt_int8_weight_rowsum)");
+  ZT_REQUIRE(a->ldy >= a->N, ZT_INVALID_ARGUMENT, "zt_static_qlinear: ldy (%lld) is smaller than N (%lld)",
+             (long long)a->ldy, (long long)a->N);
+  int rc = validate_post_ops(a->post);
+  if (rc != ZT_SUCCESS) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  CallOverlap overlap(!(a->flags & ZT_FLAG_WEIGHTS_VOLATILE));
+  const void *q = a->x;
+  if (!x_quantized) {
+    const size_t need = zt_static_qlinear_workspace_bytes(a->M, a->K, a->x_dtype);
+    ZT_REQUIRE(a->workspace && a->workspace_bytes >= need, ZT_WORKSPACE_TOO_SMALL,
+               "zt_static_qlinear: workspace of %zu bytes is smaller than the %zu required", a->workspace_bytes, need);
+    ZT_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, ZT_INVALID_ARGUMENT,
+               "zt_static_qlinear: workspace must be 256-byte aligned");
+    rc = static_quantize_launch(a->x, a->x_dtype, a->M * a->K, a->x_scale, a->x_zero_point, a->workspace, st);
+    if (rc != ZT_SUCCESS) return rc;
+    q = a->workspace;
+  }
+  Int8GemmArgs g{};
+  g.q = q;
+  g.q_is_u8 = a->x_zero_point != nullptr;
+  g.w = a->w;
+  g.M = a->M;
+  g.N = a->N;
+  g.K = a->K;
+  g.raw_s32 = false;
+  g.src_scale = a->x_scale;
+  g.src_zp = a->x_zero_point;
+  g.w_scale = a->w_scales;
+  g.w_scale_dtype = ZT_F32;
+  g.w_rowsum = a->x_zero_point ? a->w_rowsum : nullptr;
+  g.bias = a->bias;
+  g.bias_dtype = a->bias_dtype;
+  g.y_dtype = a->y_dtype;
+  g.y = a->y;
+  g.post = to_dev(a->post);
+  g.static_mode = true;
+  g.w_scale_per_tensor = a->w_scales_numel == 1 && a->N != 1;
+  g.post_dtype = a->post_buffer_dtype;
+  g.out_scale = a->out_scale;
+  g.out_zp = a->out_zero_point;
+  g.ldy = a->ldy;
+  return run_int8_gemm(g, a->algo, st);
+}
+
 // ---- allocation-free variant of zt_dynamic_qlinear ------------------------------------------------------
 // The scratch lives in the library's device image.  In host code the array's name is only a handle
 // for the runtime, not a device address: the address is looked up once per device with

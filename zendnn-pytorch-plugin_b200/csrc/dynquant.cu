@@ -195,7 +195,65 @@ __global__ void __launch_bounds__(kThreads) dynquant_scalar_kernel(const void *_
     q[base + k] = (uint8_t)quant_one<U8>(load_as_float(x, base + k, x_dtype), s, zp);
 }
 
+// Per-tensor quantisation with the caller's scale and zero point (the static form):
+// q = clamp(rint(x * (1 / s)) + zp).  Element-wise over the flattened tensor, eight elements per thread where
+// the alignment allows.
+template <bool U8>
+__device__ __forceinline__ uint32_t static_quant_one(float x, float inv, float zp) {
+  const float r = rintf(__fmul_rn(x, inv)) + zp;
+  if (U8) return (uint32_t)(int)fminf(fmaxf(r, 0.f), 255.f);
+  return (uint32_t)((int)fminf(fmaxf(r, -128.f), 127.f)) & 0xffu;
+}
+
+template <bool U8>
+__global__ void __launch_bounds__(kThreads) static_quant_kernel(const void *__restrict__ x, int x_dtype, int64_t numel,
+                                                                const float *__restrict__ scale,
+                                                                const int32_t *__restrict__ zero_point,
+                                                                uint8_t *__restrict__ q, bool vec) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const float inv = 1.0f / *scale;                       // IEEE division
+  const float zp = U8 ? (float)*zero_point : 0.f;
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  if (vec) {
+    for (int64_t ch = (int64_t)blockIdx.x * kThreads + threadIdx.x; ch < numel / kVec; ch += stride) {
+      float t[8];
+      load8(x, x_dtype, ch * kVec, t);
+      uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        w0 |= static_quant_one<U8>(t[i], inv, zp) << (8 * i);
+        w1 |= static_quant_one<U8>(t[4 + i], inv, zp) << (8 * i);
+      }
+      *reinterpret_cast<uint2 *>(q + ch * kVec) = make_uint2(w0, w1);
+    }
+    for (int64_t i = numel / kVec * kVec + (int64_t)blockIdx.x * kThreads + threadIdx.x; i < numel; i += stride)
+      q[i] = (uint8_t)static_quant_one<U8>(load_as_float(x, i, x_dtype), inv, zp);
+  } else {
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < numel; i += stride)
+      q[i] = (uint8_t)static_quant_one<U8>(load_as_float(x, i, x_dtype), inv, zp);
+  }
+}
+
 }  // namespace
+
+int static_quantize_launch(const void *x, int x_dtype, int64_t numel, const float *scale, const int32_t *zero_point,
+                           void *q, cudaStream_t st) {
+  if (numel == 0) return ZT_SUCCESS;
+  const bool vec = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
+  const int64_t work = vec ? (numel + kVec - 1) / kVec : numel;
+  int64_t blocks = (work + kThreads - 1) / kThreads;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  uint8_t *qq = reinterpret_cast<uint8_t *>(q);
+  if (zero_point)
+    ZT_CUDA_OK(launch_overlapped(static_quant_kernel<true>, dim3((unsigned)blocks), dim3(kThreads), (size_t)0, st, x,
+                                 x_dtype, numel, scale, zero_point, qq, vec));
+  else
+    ZT_CUDA_OK(launch_overlapped(static_quant_kernel<false>, dim3((unsigned)blocks), dim3(kThreads), (size_t)0, st, x,
+                                 x_dtype, numel, scale, zero_point, qq, vec));
+  return launch_status("static_quant_kernel");
+}
 
 int dynamic_quantize_launch(const void *x, int x_dtype, int64_t M, int64_t K, int act_quant, void *q, float *scales,
                             int32_t *zps, cudaStream_t st) {

@@ -71,16 +71,31 @@ __global__ void __launch_bounds__(256) int8_generic_kernel(const Int8GemmArgs a)
           reinterpret_cast<int32_t *>(a.y)[idx] = acc[r];
           continue;
         }
+        const int64_t ms = a.static_mode ? 0 : m;     // per-tensor activation parameters in the static form
         float af;
         if (a.src_zp) {
-          af = (float)((int64_t)acc[r] - (int64_t)a.src_zp[m] * (a.w_rowsum ? a.w_rowsum[n] : 0));
+          af = (float)((int64_t)acc[r] - (int64_t)a.src_zp[ms] * (a.w_rowsum ? a.w_rowsum[n] : 0));
         } else {
           af = (float)acc[r];
         }
-        float v = af * (a.src_scale[m] * load_as_float(a.w_scale, n, a.w_scale_dtype));
-        if (a.bias) v += load_as_float(a.bias, n, a.bias_dtype);
-        v = apply_post_ops(v, a.post, idx, a.y_dtype);
-        store_from_float(a.y, idx, a.y_dtype, v);
+        const float sw = a.src_scale[ms] * load_as_float(a.w_scale, a.w_scale_per_tensor ? 0 : n, a.w_scale_dtype);
+        float v;
+        if (a.static_mode) {
+          // separately rounded product and sum (no fused multiply-add): a requantised output sits on rounding
+          // boundaries of the float result
+          v = __fmul_rn(af, sw);
+          if (a.bias) v = __fadd_rn(v, load_as_float(a.bias, n, a.bias_dtype));
+        } else {
+          v = af * sw;
+          if (a.bias) v += load_as_float(a.bias, n, a.bias_dtype);
+        }
+        if (a.static_mode) {
+          v = apply_post_ops(v, a.post, idx, a.post_dtype);
+          store_static(a.y, m * a.ldy + n, a.y_dtype, v, load_out_quant(a.out_scale, a.out_zp, a.y_dtype));
+        } else {
+          v = apply_post_ops(v, a.post, idx, a.y_dtype);
+          store_from_float(a.y, idx, a.y_dtype, v);
+        }
       }
     }
   }

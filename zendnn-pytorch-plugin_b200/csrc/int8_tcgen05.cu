@@ -105,11 +105,20 @@ int int8_tcgen05_launch(const Int8GemmArgs &a, cudaStream_t st) {
   p.y = a.y;
   p.post = a.post;
   p.status = device_status_ptr();
-  const int epi = a.raw_s32 ? kEpiS32 : kEpiLinear;
+  {
+    static const int forced = [] { const char *e = getenv("ZENTORCH_B200_INT8_KROT"); return e ? atoi(e) : -1; }();
+    p.k_stagger = forced >= 0 ? forced : (a.M <= 64 ? 1 : 0);
+  }
+  p.w_scale_per_tensor = a.w_scale_per_tensor;
+  p.post_dtype = a.post_dtype;
+  p.out_scale = a.out_scale;
+  p.out_zp = a.out_zp;
+  p.ldy = a.ldy;
+  const int epi = a.raw_s32 ? kEpiS32 : a.static_mode ? kEpiStatic : kEpiLinear;
   // force_bn: tile width, + 1000 for 256-row tiles (e.g. 1160 = 256 x 160), + 2000 for CTA pairs (512 x width)
   TileChoice tile = pick_tile(a.M, a.N, a.K);
   if (a.force_bn >= 2000) {
-    ZT_REQUIRE(!a.raw_s32 && int8_pair_supported(a.M, a.force_bn % 1000), ZT_UNSUPPORTED,
+    ZT_REQUIRE(!a.raw_s32 && !a.static_mode && int8_pair_supported(a.M, a.force_bn % 1000), ZT_UNSUPPORTED,
                "int8_tcgen05_launch: CTA-pair tiles need the linear epilogue, M > 256 and a width of 128, 160, 192 or 256");
     return launch_pair(a.force_bn % 1000, a, p, !a.q_is_u8, st);
   }

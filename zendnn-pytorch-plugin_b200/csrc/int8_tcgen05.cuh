@@ -36,7 +36,9 @@ constexpr int kBK = 128;  // bytes (= int8 elements) of K per stage
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 64 + kEpiWarps * 32;
 
-enum EpiMode { kEpiS32 = 0, kEpiLinear = 1 };
+// kEpiStatic: the static-quantisation form (per-tensor activation parameters, optional per-tensor weight scale,
+// requantised or strided output); kept apart so that the dynamic form's epilogue carries none of it
+enum EpiMode { kEpiS32 = 0, kEpiLinear = 1, kEpiStatic = 2 };
 
 struct TcParams {
   int M, N, K;
@@ -51,6 +53,13 @@ struct TcParams {
   void *y;                 // [M,N] (y_dtype) or int32 for kEpiS32
   PostOpsDev post;
   int *status;             // device status word (bounded-wait failures)
+  int k_stagger;           // 1: column tile t starts its walk over K at block t % num_kb (see rotated_kb)
+  // kEpiStatic only
+  bool w_scale_per_tensor;
+  int post_dtype;
+  const float *out_scale;
+  const int32_t *out_zp;
+  int64_t ldy;
 };
 
 template <int MH, int BN, int STAGES>
@@ -145,6 +154,85 @@ __device__ __forceinline__ void finish_chunk(const TcParams &p, const uint32_t (
   }
 }
 
+// The same for the static-quantisation form: separately rounded product and sum (a requantised output sits
+// on rounding boundaries of the float result), post-op operands of their own dtype, and a store that
+// requantises or honours a row stride.
+__device__ __forceinline__ void finish_chunk_static(const TcParams &p, const uint32_t (&r)[32], float s_x, int zp_x,
+                                                    const float *wscale, const float *bias, const int32_t *rowsum,
+                                                    const OutQuant &oq, int m, int nb) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const float af = p.src_zp ? (float)((int64_t)(int32_t)r[j] - (int64_t)zp_x * rowsum[j]) : (float)(int32_t)r[j];
+    v[j] = __fadd_rn(__fmul_rn(af, s_x * wscale[j]), bias[j]);
+  }
+  const int64_t base = (int64_t)m * p.N + nb;
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (nb + j < p.N) v[j] = apply_post_ops(v[j], p.post, base + j, p.post_dtype);
+  const int64_t out = (int64_t)m * p.ldy + nb;
+  const bool full = nb + 32 <= p.N;
+  if (p.y_dtype == ZT_U8 || p.y_dtype == ZT_S8) {
+    uint8_t *dst = reinterpret_cast<uint8_t *>(p.y) + out;
+    if (full && ((reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 16) {
+        uint32_t w4[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          w4[q] = 0;
+#pragma unroll
+          for (int b = 0; b < 4; ++b) w4[q] |= ((uint32_t)requantize(v[j + 4 * q + b], oq) & 0xffu) << (8 * b);
+        }
+        *reinterpret_cast<uint4 *>(dst + j) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) dst[j] = (uint8_t)requantize(v[j], oq);
+    }
+  } else if (p.y_dtype == ZT_BF16) {
+    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.y) + out;
+    if (full && ((reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 o;
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+        __nv_bfloat162 t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+        __nv_bfloat162 t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        o.x = *reinterpret_cast<uint32_t *>(&t0);
+        o.y = *reinterpret_cast<uint32_t *>(&t1);
+        o.z = *reinterpret_cast<uint32_t *>(&t2);
+        o.w = *reinterpret_cast<uint32_t *>(&t3);
+        *reinterpret_cast<uint4 *>(dst + j) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else {
+    float *dst = reinterpret_cast<float *>(p.y) + out;
+    if (full && ((reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) dst[j] = v[j];
+    }
+  }
+}
+
+// With few activation rows every CTA asks for the same few 128-byte lines of the activations at every k-block;
+// integer accumulation does not depend on the order, so column tiles may start their walk over K at
+// different blocks and spread those requests over the activations' lines.
+__device__ __forceinline__ int rotated_kb(int kb, int rot, int num_kb) {
+  const int k = kb + rot;
+  return k >= num_kb ? k - num_kb : k;
+}
+
 template <int MH, int BN, int STAGES, int NBUF, int EPI, bool A_SIGNED>
 __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                    const __grid_constant__ CUtensorMap tmap_b,
@@ -200,19 +288,21 @@ __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_
       if ((int)blockIdx.x < total_tiles) {
         const int m0 = ((int)blockIdx.x % p.m_tiles) * (MH * kBM);
         const int n0 = ((int)blockIdx.x / p.m_tiles) * BN;
+        const int rot = p.k_stagger ? ((int)blockIdx.x / p.m_tiles) % num_kb : 0;
         pre = num_kb < STAGES ? num_kb : STAGES;
         for (int kb = 0; kb < pre; ++kb) {
           tc::mbar_expect_tx(&full_bar[kb], L::kStageBytes);
-          tc::tma_load_2d(smem + kb * L::kStageBytes + L::kABytes, &tmap_b, &full_bar[kb], kb * kBK, n0);
+          tc::tma_load_2d(smem + kb * L::kStageBytes + L::kABytes, &tmap_b, &full_bar[kb], rotated_kb(kb, rot, num_kb) * kBK, n0);
         }
         grid_dependency_wait();
         for (int kb = 0; kb < pre; ++kb)
-          tc::tma_load_2d(smem + kb * L::kStageBytes, &tmap_a, &full_bar[kb], kb * kBK, m0);
+          tc::tma_load_2d(smem + kb * L::kStageBytes, &tmap_a, &full_bar[kb], rotated_kb(kb, rot, num_kb) * kBK, m0);
         it = (uint32_t)pre;
       }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % p.m_tiles) * (MH * kBM);
         const int n0 = (tile / p.m_tiles) * BN;
+        const int rot = p.k_stagger ? (tile / p.m_tiles) % num_kb : 0;
         for (int kb = (tile == (int)blockIdx.x ? pre : 0); kb < num_kb; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -224,8 +314,9 @@ __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_
           unsigned char *a_dst = smem + s * L::kStageBytes;
           unsigned char *b_dst = a_dst + L::kABytes;
           tc::mbar_expect_tx(&full_bar[s], L::kStageBytes);
-          tc::tma_load_2d(a_dst, &tmap_a, &full_bar[s], kb * kBK, m0);
-          tc::tma_load_2d(b_dst, &tmap_b, &full_bar[s], kb * kBK, n0);
+          const int kx = rotated_kb(kb, rot, num_kb) * kBK;
+          tc::tma_load_2d(a_dst, &tmap_a, &full_bar[s], kx, m0);
+          tc::tma_load_2d(b_dst, &tmap_b, &full_bar[s], kx, n0);
         }
       }
     }
@@ -285,6 +376,8 @@ __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_
     int unary = -1;
     if (p.post.n_ops == 0) unary = ZT_POST_NONE;
     else if (p.post.n_ops == 1 && p.post.ids[0] < ZT_POST_MUL) unary = p.post.ids[0];
+    OutQuant out_quant{0.f, 0.f, 0.f, 0.f};
+    if (EPI == kEpiStatic) out_quant = load_out_quant(p.out_scale, p.out_zp, p.y_dtype);
     int local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
@@ -295,11 +388,11 @@ __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_
       float *v_wscale = s_vec + (local & 1) * 3 * BN;
       float *v_bias = v_wscale + BN;
       int32_t *v_rowsum = reinterpret_cast<int32_t *>(v_bias + BN);
-      if (EPI == kEpiLinear) {
+      if (EPI != kEpiS32) {
         for (int j = et; j < BN; j += kEpiWarps * 32) {
           const int n = n0 + j;
           const bool in = n < p.N;
-          v_wscale[j] = in ? load_as_float(p.w_scale, n, p.w_scale_dtype) : 0.f;
+          v_wscale[j] = in ? load_as_float(p.w_scale, (EPI == kEpiStatic && p.w_scale_per_tensor) ? 0 : n, p.w_scale_dtype) : 0.f;
           v_bias[j] = (in && p.bias) ? load_as_float(p.bias, n, p.bias_dtype) : 0.f;
           v_rowsum[j] = (in && p.w_rowsum) ? p.w_rowsum[n] : 0;
         }
@@ -322,6 +415,10 @@ __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_
           s_m = p.src_scale[m];
           if (p.src_zp) zp_m = p.src_zp[m];
         }
+        if (EPI == kEpiStatic) {                     // one scale and zero point for the whole tensor
+          s_m = p.src_scale[0];
+          if (p.src_zp) zp_m = p.src_zp[0];
+        }
         const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (buf * MH + h) * BN;
 #pragma unroll 1
         for (int c = parity * 32; c < BN; c += 64) {
@@ -341,6 +438,8 @@ __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_
                 for (int j = 0; j < 32; ++j)
                   if (nb + j < p.N) dst[j] = (int32_t)r[j];
               }
+            } else if (EPI == kEpiStatic) {
+              finish_chunk_static(p, r, s_m, zp_m, v_wscale + c, v_bias + c, v_rowsum + c, out_quant, m, nb);
             } else {
               const float *ws = v_wscale + c, *bs = v_bias + c;
               const int32_t *rs = v_rowsum + c;
@@ -395,6 +494,9 @@ int launch_bn(const CUtensorMap &ta, const CUtensorMap &tb, const TcParams &p, i
   if (epi == kEpiS32)
     return a_signed ? launch_cfg<MH, BN, STAGES, NBUF, kEpiS32, true>(ta, tb, p, st)
                     : launch_cfg<MH, BN, STAGES, NBUF, kEpiS32, false>(ta, tb, p, st);
+  if (epi == kEpiStatic)
+    return a_signed ? launch_cfg<MH, BN, STAGES, NBUF, kEpiStatic, true>(ta, tb, p, st)
+                    : launch_cfg<MH, BN, STAGES, NBUF, kEpiStatic, false>(ta, tb, p, st);
   return a_signed ? launch_cfg<MH, BN, STAGES, NBUF, kEpiLinear, true>(ta, tb, p, st)
                   : launch_cfg<MH, BN, STAGES, NBUF, kEpiLinear, false>(ta, tb, p, st);
 }

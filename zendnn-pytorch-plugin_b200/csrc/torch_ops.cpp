@@ -423,6 +423,248 @@ at::Tensor dynamic_qlinear_ext(const at::Tensor &input, const at::Tensor &weight
                               post_id_from_name(post_op), weight_rowsum, zentorch_op_name);
 }
 
+// ---- static-quantisation qlinear (src/cpu/cpp/QLinear.cpp:66-591) ------------------------------------------
+int to_zt_dtype8(c10::ScalarType t) {
+  switch (t) {
+    case at::kBFloat16: return ZT_BF16;
+    case at::kFloat: return ZT_F32;
+    case at::kByte: return ZT_U8;
+    case at::kChar: return ZT_S8;
+    default: return -1;
+  }
+}
+
+// Checks of check_valid_dtypes_for_quantized_matmul / check_valid_sizes_for_quantized_matmul
+// (src/cpu/cpp/MatmulUtils.hpp:331-525) with their messages, then one zt_static_qlinear call that writes
+// `result` (any float / 8-bit dtype; a 2-D view may have a row stride).
+void qlinear_into(at::Tensor &result, const at::Tensor &input, const at::Tensor &weight, const at::Tensor &input_scales,
+                  const at::Tensor &input_zero_points, const at::Tensor &weight_scales,
+                  const at::Tensor &weight_zero_points, const std::optional<at::Tensor> &bias,
+                  const std::optional<at::Tensor> &output_scales, const std::optional<at::Tensor> &output_zero_points,
+                  const std::vector<int> &post_ops, const std::vector<at::Tensor> &post_buffers,
+                  const std::string &op_name) {
+  RECORD_FUNCTION(op_name, std::vector<c10::IValue>({input, weight}));
+  const bool has_bias = bias.has_value() && bias->defined();
+  const bool has_oscale = output_scales.has_value() && output_scales->defined();
+  const bool has_ozp = output_zero_points.has_value() && output_zero_points->defined();
+  const bool has_xzp = input_zero_points.defined();
+  const int x_dtype = to_zt_dtype8(input.scalar_type());
+  const int y_dtype = to_zt_dtype8(result.scalar_type());
+  TORCH_CHECK(x_dtype >= 0, "unsupported dtype for input tensor, only float32/bfloat16/uint8/int8 is supported");
+  TORCH_CHECK(weight.scalar_type() == at::kChar, "unsupported dtype for weight tensor, only int8 is supported");
+  TORCH_CHECK(y_dtype >= 0, "unsupported dtype for result tensor, only float32/bfloat16/uint8/int8 is supported");
+  if (has_bias)
+    TORCH_CHECK(bias->scalar_type() == at::kFloat || bias->scalar_type() == at::kBFloat16,
+                "unsupported dtype for bias tensor, only float32 or bfloat16 is supported");
+  TORCH_CHECK(input_scales.scalar_type() == at::kFloat, "unsupported dtype for input_scales, only float32 is supported");
+  if (has_xzp)
+    TORCH_CHECK(input_zero_points.scalar_type() == at::kInt, "unsupported dtype for input_zero_points, only int32 supported");
+  TORCH_CHECK(weight_scales.scalar_type() == at::kFloat, "unsupported dtype for weight_scales, only float32 is supported");
+  if (weight_zero_points.defined())
+    TORCH_CHECK(weight_zero_points.scalar_type() == at::kInt,
+                "unsupported dtype for weight_zero_points, only int32 is supported");
+  if (has_oscale) {
+    TORCH_CHECK(output_scales->scalar_type() == at::kFloat, "unsupported dtype for output_scales, only float32 is supported");
+    if (has_ozp) {
+      TORCH_CHECK(output_zero_points->scalar_type() == at::kInt,
+                  "unsupported dtype for output_zero_points, only int32 is supported");
+      TORCH_CHECK(result.scalar_type() == at::kByte,
+                  "unsupported dtype for result tensor when output_zero_points are defined, uint8 are supported dtype");
+    } else {
+      TORCH_CHECK(result.scalar_type() == at::kChar,
+                  "unsupported dtype for result tensor when output_zero_points are not defined while output_scales are "
+                  "defined, int8 are supported dtype");
+    }
+  } else {
+    TORCH_CHECK(result.scalar_type() == at::kFloat || result.scalar_type() == at::kBFloat16,
+                "unsupported dtype for result tensor, only float32/bfloat16 is supported when output_scales are not "
+                "defined");
+  }
+  for (const at::Tensor &b : post_buffers)
+    TORCH_CHECK(b.scalar_type() == at::kFloat || b.scalar_type() == at::kBFloat16,
+                "unsupported dtype for post_ops, only float32/bfloat16 is supported");
+  if (post_buffers.size() == 2)
+    TORCH_CHECK(post_buffers[0].scalar_type() == post_buffers[1].scalar_type(),
+                "unsupported dtype for post_ops, only float32/bfloat16 is supported");
+  // sizes
+  TORCH_CHECK(input.dim() >= 2 && weight.dim() == 2, "unsupported dims for input and weight");
+  const int64_t N = weight.size(0), K = weight.size(1);
+  TORCH_CHECK(input.size(input.dim() - 1) == K, "unsupported shapes for input and weight");
+  if (has_bias) TORCH_CHECK(bias->dim() == 1 && bias->size(0) == N, "unsupported shapes for input, weight and bias");
+  TORCH_CHECK(input_scales.dim() <= 1, "unsupported dims for input_scales with respect to input tensor");
+  if (has_xzp) {
+    TORCH_CHECK(input_zero_points.dim() <= 1, "only scalar and 1-d input_zero_points are supported");
+    TORCH_CHECK(input_zero_points.numel() == 1, "only supporting per-tensor quantization for input");
+  }
+  TORCH_CHECK(input_scales.numel() == 1, "unsupported number of elements for input_scales with respect to input tensor");
+  TORCH_CHECK(weight_scales.dim() <= 1, "unsupported dims for weight_scales with respect to weight tensor");
+  TORCH_CHECK(weight_scales.numel() == 1 || weight_scales.numel() == N,
+              "unsupported number of elements for weight_scales with respect to weight tensor");
+  if (weight_zero_points.defined()) {
+    TORCH_CHECK(weight_zero_points.dim() <= 1, "only scalar and 1-d weight_zero_points are supported");
+    TORCH_CHECK(weight_zero_points.numel() == 1 || weight_zero_points.numel() == N,
+                "only supporting per-tensor and per-channel quantization for weight");
+  }
+  if (has_oscale && has_ozp) {
+    TORCH_CHECK(output_scales->dim() <= 1, "unsupported dims for output_scales with respect to output tensor");
+    TORCH_CHECK(output_zero_points->dim() <= 1, "unsupported dims for output_zero_points with respect to output tensor");
+    TORCH_CHECK(output_scales->numel() == 1, "unsupported number of elements for output_scales with respect to output tensor");
+    TORCH_CHECK(output_zero_points->numel() == 1,
+                "unsupported number of elements for output_zero_points with respect to output tensor");
+  } else if (has_oscale) {
+    TORCH_CHECK(output_scales->numel() == 1, "unsupported number of elements for output_scales with respect to output tensor");
+  }
+  std::vector<int64_t> out_sizes = input.sizes().vec();
+  out_sizes.back() = N;
+  TORCH_CHECK(result.sizes() == c10::IntArrayRef(out_sizes), "unsupported shapes for input, weight and result");
+  for (const at::Tensor &b : post_buffers) {
+    TORCH_CHECK(b.dim() == input.dim(), "unsupported dims for post op buffers for input and weight");
+    TORCH_CHECK(b.sizes() == c10::IntArrayRef(out_sizes), "unsupported shapes for post op buffers for input and weight");
+  }
+  // the unsigned / signed form of the activations follows from the zero points, as in the reference
+  // (QLinear.cpp:17,379-383): an unsigned input needs them, a signed one has none
+  if (input.scalar_type() == at::kByte)
+    TORCH_CHECK(has_xzp, "zentorch_qlinear: a uint8 input needs input_zero_points");
+  if (input.scalar_type() == at::kChar)
+    TORCH_CHECK(!has_xzp, "zentorch_qlinear: an int8 input takes no input_zero_points");
+  TORCH_CHECK(input.is_cuda(), "zentorch_qlinear (CUDA): input must be a CUDA tensor");
+  check_on_device(weight, input, "zentorch_qlinear", "weight");
+  check_on_device(input_scales, input, "zentorch_qlinear", "input_scales");
+  if (has_xzp) check_on_device(input_zero_points, input, "zentorch_qlinear", "input_zero_points");
+  check_on_device(weight_scales, input, "zentorch_qlinear", "weight_scales");
+  check_on_device(bias, input, "zentorch_qlinear", "bias");
+  check_on_device(output_scales, input, "zentorch_qlinear", "output_scales");
+  check_on_device(output_zero_points, input, "zentorch_qlinear", "output_zero_points");
+  check_on_device(result, input, "zentorch_qlinear", "out");
+  for (const at::Tensor &b : post_buffers) check_on_device(b, input, "zentorch_qlinear", "post-op operand");
+  c10::cuda::CUDAGuard device_guard(input.device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+
+  at::Tensor x2 = as_2d(input);
+  const int64_t M = x2.size(0);
+  if (M == 0 || N == 0) return;
+  // the result as rows of N elements `ldy` apart: contiguous tensors of any rank, or a 2-D view of a wider buffer
+  int64_t ldy = N;
+  if (result.dim() == 2 && result.stride(1) == 1 && result.stride(0) >= N) {
+    ldy = M > 1 ? result.stride(0) : N;
+  } else {
+    TORCH_CHECK(result.is_contiguous(), "zentorch_qlinear: out must be contiguous or a 2-D view with unit inner stride");
+  }
+  at::Tensor w = weight.contiguous();
+  at::Tensor ws = weight_scales.contiguous();
+  at::Tensor b = has_bias ? bias->contiguous() : at::Tensor();
+  std::vector<at::Tensor> bufs;
+  for (const at::Tensor &t : post_buffers) bufs.push_back(t.contiguous());
+  at::Tensor rowsum;
+  bool weights_const;
+  if (has_xzp) {
+    bool computed_now = false;
+    const std::function<at::Tensor()> make = [&]() {
+      at::Tensor r = at::empty({N}, w.options().dtype(at::kInt));
+      const int rc = zt_int8_weight_rowsum(w.data_ptr<int8_t>(), N, K, r.data_ptr<int32_t>(), stream);
+      TORCH_CHECK(rc == ZT_SUCCESS, zt_last_error());
+      computed_now = true;
+      return r;
+    };
+    weights_const = seen_weights().lookup(weight, &make, &rowsum) && !computed_now;
+  } else {
+    weights_const = seen_weights().seen_before(weight);
+  }
+  weights_const = seen_weights().seen_before(weight_scales) && w.is_same(weight) && ws.is_same(weight_scales) && weights_const;
+  const size_t ws_bytes = zt_static_qlinear_workspace_bytes(M, K, x_dtype);
+  at::Tensor scratch = at::empty({(int64_t)ws_bytes}, w.options().dtype(at::kByte));
+
+  zt_static_qlinear_args_t a{};
+  a.x = x2.data_ptr();
+  a.x_dtype = x_dtype;
+  a.M = M;
+  a.K = K;
+  a.N = N;
+  a.x_scale = input_scales.data_ptr<float>();
+  a.x_zero_point = has_xzp ? input_zero_points.data_ptr<int32_t>() : nullptr;
+  a.w = w.data_ptr<int8_t>();
+  a.w_scales = ws.data_ptr<float>();
+  a.w_scales_numel = ws.numel();
+  a.w_rowsum = rowsum.defined() ? rowsum.data_ptr<int32_t>() : nullptr;
+  a.bias = b.defined() ? b.data_ptr() : nullptr;
+  a.bias_dtype = b.defined() ? to_zt_dtype(b, "bias") : ZT_F32;
+  int nb = 0;
+  for (int id : post_ops) {
+    if (id == ZT_POST_NONE) continue;
+    a.post.ids[a.post.n_ops++] = id;
+    if (id == ZT_POST_MUL || id == ZT_POST_ADD) {
+      a.post.buffers[nb] = bufs[nb].data_ptr();
+      ++nb;
+    }
+  }
+  a.post_buffer_dtype = bufs.empty() ? ZT_F32 : to_zt_dtype(bufs[0], "post-op operand");
+  a.out_scale = has_oscale ? output_scales->data_ptr<float>() : nullptr;
+  a.out_zero_point = has_ozp ? output_zero_points->data_ptr<int32_t>() : nullptr;
+  a.y = result.data_ptr();
+  a.y_dtype = y_dtype;
+  a.ldy = ldy;
+  a.workspace = scratch.data_ptr();
+  a.workspace_bytes = ws_bytes;
+  a.algo = ZT_ALGO_AUTO;
+  a.flags = weights_const ? 0 : ZT_FLAG_WEIGHTS_VOLATILE;
+  ZT_TORCH_CALL(zt_static_qlinear(&a, stream));
+}
+
+c10::ScalarType qlinear_output_dtype(std::optional<c10::ScalarType> output_dtype) {
+  const c10::ScalarType t = output_dtype.value_or(at::kFloat);
+  TORCH_CHECK(t == at::kFloat || t == at::kBFloat16 || t == at::kByte || t == at::kChar,
+              "output_dtype received is not yet supported, only float32/bfloat16/uint8/int8 is supported");
+  return t;
+}
+
+at::Tensor qlinear_result(const at::Tensor &input, const at::Tensor &weight, c10::ScalarType dtype) {
+  TORCH_CHECK(input.dim() >= 1 && weight.dim() == 2, "unsupported dims for input and weight");
+  std::vector<int64_t> out_sizes = input.sizes().vec();
+  out_sizes.back() = weight.size(0);
+  return at::empty(out_sizes, input.options().dtype(dtype));
+}
+
+// zentorch_qlinear / _relu / _sigmoid (zentorch_qlinear_unary, QLinear.cpp:420-454)
+template <int POST>
+at::Tensor qlinear_unary(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &input_scales,
+                         const at::Tensor &input_zero_points, const at::Tensor &weight_scales,
+                         const at::Tensor &weight_zero_points, std::optional<at::Tensor> bias,
+                         std::optional<at::Tensor> output_scales, std::optional<at::Tensor> output_zero_points,
+                         std::optional<c10::ScalarType> output_dtype, std::string zentorch_op_name) {
+  at::Tensor result = qlinear_result(input, weight, qlinear_output_dtype(output_dtype));
+  qlinear_into(result, input, weight, input_scales, input_zero_points, weight_scales, weight_zero_points, bias,
+               output_scales, output_zero_points, {POST}, {}, zentorch_op_name);
+  return result;
+}
+
+// zentorch_qlinear.out / zentorch_qlinear_relu.out (zentorch_qlinear_out_unary, QLinear.cpp:368-418)
+template <int POST>
+void qlinear_out_unary(at::Tensor &out, const at::Tensor &input, const at::Tensor &weight,
+                       const at::Tensor &input_scales, const at::Tensor &input_zero_points,
+                       const at::Tensor &weight_scales, const at::Tensor &weight_zero_points,
+                       std::optional<at::Tensor> bias, std::optional<at::Tensor> output_scales,
+                       std::optional<at::Tensor> output_zero_points, std::optional<c10::ScalarType> output_dtype,
+                       std::string zentorch_op_name) {
+  TORCH_CHECK(output_dtype.has_value() && *output_dtype == out.scalar_type(),
+              "output_dtype received does not match the dtype of the output tensor");
+  qlinear_output_dtype(output_dtype);
+  qlinear_into(out, input, weight, input_scales, input_zero_points, weight_scales, weight_zero_points, bias,
+               output_scales, output_zero_points, {POST}, {}, zentorch_op_name);
+}
+
+// zentorch_qlinear_mul_add (zentorch_qlinear_binary_binary<MUL, ADD>, QLinear.cpp:456-531)
+at::Tensor qlinear_mul_add(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &input_scales,
+                           const at::Tensor &input_zero_points, const at::Tensor &weight_scales,
+                           const at::Tensor &weight_zero_points, const at::Tensor &mul_input,
+                           const at::Tensor &add_input, std::optional<at::Tensor> bias,
+                           std::optional<at::Tensor> output_scales, std::optional<at::Tensor> output_zero_points,
+                           std::optional<c10::ScalarType> output_dtype, std::string zentorch_op_name) {
+  at::Tensor result = qlinear_result(input, weight, qlinear_output_dtype(output_dtype));
+  qlinear_into(result, input, weight, input_scales, input_zero_points, weight_scales, weight_zero_points, bias,
+               output_scales, output_zero_points, {ZT_POST_MUL, ZT_POST_ADD}, {mul_input, add_input}, zentorch_op_name);
+  return result;
+}
+
 // ---- meta kernels (src/cpu/python/zentorch/_meta_registrations.py:552-714, 755-797) --------------------
 at::Tensor meta_woq(const at::Tensor &input, const at::Tensor &weight) {
   std::vector<c10::SymInt> sizes = input.sym_sizes().vec();
@@ -463,8 +705,29 @@ at::Tensor meta_dynamic_qlinear_ext(const at::Tensor &input, const at::Tensor &w
   return at::empty_symint(sizes, input.options());
 }
 
-bool has_schema(const char *name) {
-  return c10::Dispatcher::singleton().findSchema({std::string("zentorch::") + name, ""}).has_value();
+// static qlinear (src/cpu/python/zentorch/_meta_registrations.py:424-550)
+at::Tensor meta_qlinear_shape(const at::Tensor &input, const at::Tensor &weight, std::optional<c10::ScalarType> dtype) {
+  std::vector<c10::SymInt> sizes = input.sym_sizes().vec();
+  sizes.back() = weight.sym_size(0);
+  return at::empty_symint(sizes, input.options().dtype(dtype.value_or(at::kFloat)));
+}
+at::Tensor meta_qlinear(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &, const at::Tensor &,
+                        const at::Tensor &, const at::Tensor &, std::optional<at::Tensor>, std::optional<at::Tensor>,
+                        std::optional<at::Tensor>, std::optional<c10::ScalarType> output_dtype, std::string) {
+  return meta_qlinear_shape(input, weight, output_dtype);
+}
+at::Tensor meta_qlinear_mul_add(const at::Tensor &input, const at::Tensor &weight, const at::Tensor &, const at::Tensor &,
+                                const at::Tensor &, const at::Tensor &, const at::Tensor &, const at::Tensor &,
+                                std::optional<at::Tensor>, std::optional<at::Tensor>, std::optional<at::Tensor>,
+                                std::optional<c10::ScalarType> output_dtype, std::string) {
+  return meta_qlinear_shape(input, weight, output_dtype);
+}
+void meta_qlinear_out(at::Tensor &, const at::Tensor &, const at::Tensor &, const at::Tensor &, const at::Tensor &,
+                      const at::Tensor &, const at::Tensor &, std::optional<at::Tensor>, std::optional<at::Tensor>,
+                      std::optional<at::Tensor>, std::optional<c10::ScalarType>, std::string) {}
+
+bool has_schema(const char *name, const char *overload = "") {
+  return c10::Dispatcher::singleton().findSchema({std::string("zentorch::") + name, overload}).has_value();
 }
 
 struct Registrar {
@@ -512,6 +775,27 @@ struct Registrar {
         "zentorch_dynamic_qlinear_ext(Tensor input, Tensor weight, Tensor weight_scales, Tensor? bias=None, "
         "Tensor? weight_rowsum=None, *, str act_quant='s8_sym', str post_op='none', "
         "str zentorch_op_name='zentorch::zentorch_dynamic_qlinear_ext') -> Tensor");
+    // static-quantisation family, schema strings of src/cpu/cpp/QLinear.cpp:535-575
+#define ZT_QLINEAR_ARGS                                                                                           \
+  "Tensor input, Tensor weight, Tensor input_scales, Tensor input_zero_points, Tensor weight_scales, "            \
+  "Tensor weight_zero_points, "
+#define ZT_QLINEAR_TAIL "Tensor? bias, Tensor? output_scales, Tensor? output_zero_points, ScalarType? output_dtype=None, "
+    def("zentorch_qlinear", "zentorch_qlinear(" ZT_QLINEAR_ARGS ZT_QLINEAR_TAIL
+        "str zentorch_op_name='zentorch::zentorch_qlinear') -> Tensor");
+    def("zentorch_qlinear_relu", "zentorch_qlinear_relu(" ZT_QLINEAR_ARGS ZT_QLINEAR_TAIL
+        "str zentorch_op_name='zentorch::zentorch_qlinear_relu') -> Tensor");
+    def("zentorch_qlinear_sigmoid", "zentorch_qlinear_sigmoid(" ZT_QLINEAR_ARGS ZT_QLINEAR_TAIL
+        "str zentorch_op_name='zentorch::zentorch_qlinear_sigmoid') -> Tensor");
+    def("zentorch_qlinear_mul_add", "zentorch_qlinear_mul_add(" ZT_QLINEAR_ARGS "Tensor mul_input, Tensor add_input, "
+        ZT_QLINEAR_TAIL "str zentorch_op_name='zentorch::zentorch_qlinear_mul_add') -> Tensor");
+    if (!has_schema("zentorch_qlinear", "out"))
+      frag->def("zentorch_qlinear.out(Tensor(a!) out, " ZT_QLINEAR_ARGS ZT_QLINEAR_TAIL
+                "str zentorch_op_name='zentorch::zentorch_qlinear.out') -> ()");
+    if (!has_schema("zentorch_qlinear_relu", "out"))
+      frag->def("zentorch_qlinear_relu.out(Tensor(a!) out, " ZT_QLINEAR_ARGS ZT_QLINEAR_TAIL
+                "str zentorch_op_name='zentorch::zentorch_qlinear_relu.out') -> ()");
+#undef ZT_QLINEAR_ARGS
+#undef ZT_QLINEAR_TAIL
     libs.push_back(std::move(frag));
 
     auto cuda = std::make_unique<torch::Library>(torch::Library::IMPL, "zentorch", c10::DispatchKey::CUDA, __FILE__, __LINE__);
@@ -527,12 +811,18 @@ struct Registrar {
     cuda->impl("zentorch_woq_repack_from_int4pack", woq_repack_from_int4pack);
     cuda->impl("zentorch_dynamic_qlinear", dynamic_qlinear);
     cuda->impl("zentorch_dynamic_qlinear_ext", dynamic_qlinear_ext);
+    cuda->impl("zentorch_qlinear", qlinear_unary<ZT_POST_NONE>);
+    cuda->impl("zentorch_qlinear_relu", qlinear_unary<ZT_POST_RELU>);
+    cuda->impl("zentorch_qlinear_sigmoid", qlinear_unary<ZT_POST_SIGMOID>);
+    cuda->impl("zentorch_qlinear_mul_add", qlinear_mul_add);
+    cuda->impl("zentorch_qlinear.out", qlinear_out_unary<ZT_POST_NONE>);
+    cuda->impl("zentorch_qlinear_relu.out", qlinear_out_unary<ZT_POST_RELU>);
     libs.push_back(std::move(cuda));
 
     // A real zentorch registers its own Meta kernels from Python; only fill the gap when absent.
     auto meta = std::make_unique<torch::Library>(torch::Library::IMPL, "zentorch", c10::DispatchKey::Meta, __FILE__, __LINE__);
-    auto has_meta = [](const char *name) {
-      auto op = c10::Dispatcher::singleton().findOp({std::string("zentorch::") + name, ""});
+    auto has_meta = [](const char *name, const char *overload = "") {
+      auto op = c10::Dispatcher::singleton().findOp({std::string("zentorch::") + name, overload});
       return op.has_value() && op->hasKernelForDispatchKey(c10::DispatchKey::Meta);
     };
 #define ZT_META(name, fn) \
@@ -549,6 +839,12 @@ struct Registrar {
     ZT_META("zentorch_woq_repack_from_int4pack", meta_repack_from_int4pack);
     ZT_META("zentorch_dynamic_qlinear", meta_dynamic_qlinear);
     ZT_META("zentorch_dynamic_qlinear_ext", meta_dynamic_qlinear_ext);
+    ZT_META("zentorch_qlinear", meta_qlinear);
+    ZT_META("zentorch_qlinear_relu", meta_qlinear);
+    ZT_META("zentorch_qlinear_sigmoid", meta_qlinear);
+    ZT_META("zentorch_qlinear_mul_add", meta_qlinear_mul_add);
+    if (!has_meta("zentorch_qlinear", "out")) meta->impl("zentorch_qlinear.out", meta_qlinear_out);
+    if (!has_meta("zentorch_qlinear_relu", "out")) meta->impl("zentorch_qlinear_relu.out", meta_qlinear_out);
 #undef ZT_META
     libs.push_back(std::move(meta));
   }
@@ -647,4 +943,52 @@ extern "C" ZT_API AOTITorchError aoti_torch_cuda_zentorch_dynamic_qlinear(AtenTe
                                zentorch_op_name);
     *ret0 = new_tensor_handle(std::move(tmp));
   });
+}
+
+// Static-quantisation family (src/cpu/cpp/shim_cpu_zentorch.hpp:28-75, shim_cpu_zentorch.cpp:72-230).
+#define ZT_QL_ARGS                                                                                       \
+  AtenTensorHandle X, AtenTensorHandle W, AtenTensorHandle X_scales, AtenTensorHandle X_zero_points,     \
+      AtenTensorHandle W_scales, AtenTensorHandle W_zero_points
+#define ZT_QL_TAIL                                                                                       \
+  AtenTensorHandle *B, AtenTensorHandle *output_scales, AtenTensorHandle *output_zero_points,            \
+      const int32_t *output_dtype, const char *zentorch_op_name
+#define ZT_QL_PASS                                                                                       \
+  *tensor_handle_to_tensor_pointer(X), *tensor_handle_to_tensor_pointer(W),                              \
+      *tensor_handle_to_tensor_pointer(X_scales), *tensor_handle_to_tensor_pointer(X_zero_points),       \
+      *tensor_handle_to_tensor_pointer(W_scales), *tensor_handle_to_tensor_pointer(W_zero_points)
+#define ZT_QL_PASS_TAIL                                                                                  \
+  pointer_to_optional<at::Tensor>(B), pointer_to_optional<at::Tensor>(output_scales),                    \
+      pointer_to_optional<at::Tensor>(output_zero_points), pointer_to_optional<c10::ScalarType>(output_dtype), \
+      zentorch_op_name
+
+#define ZT_SHIM_QLINEAR(suffix, POST)                                                                    \
+  extern "C" ZT_API AOTITorchError aoti_torch_cuda_zentorch_qlinear##suffix(ZT_QL_ARGS, ZT_QL_TAIL,      \
+                                                                            AtenTensorHandle *ret0) {    \
+    AOTI_TORCH_CONVERT_EXCEPTION_TO_ERROR_CODE({                                                         \
+      auto tmp = qlinear_unary<POST>(ZT_QL_PASS, ZT_QL_PASS_TAIL);                                       \
+      *ret0 = new_tensor_handle(std::move(tmp));                                                         \
+    });                                                                                                  \
+  }
+ZT_SHIM_QLINEAR(, ZT_POST_NONE)
+ZT_SHIM_QLINEAR(_relu, ZT_POST_RELU)
+ZT_SHIM_QLINEAR(_sigmoid, ZT_POST_SIGMOID)
+
+extern "C" ZT_API AOTITorchError aoti_torch_cuda_zentorch_qlinear_mul_add(ZT_QL_ARGS, AtenTensorHandle mul_input,
+                                                                         AtenTensorHandle add_input, ZT_QL_TAIL,
+                                                                         AtenTensorHandle *ret0) {
+  AOTI_TORCH_CONVERT_EXCEPTION_TO_ERROR_CODE({
+    auto tmp = qlinear_mul_add(ZT_QL_PASS, *tensor_handle_to_tensor_pointer(mul_input),
+                               *tensor_handle_to_tensor_pointer(add_input), ZT_QL_PASS_TAIL);
+    *ret0 = new_tensor_handle(std::move(tmp));
+  });
+}
+
+extern "C" ZT_API AOTITorchError aoti_torch_cuda_zentorch_qlinear_out(AtenTensorHandle out, ZT_QL_ARGS, ZT_QL_TAIL) {
+  AOTI_TORCH_CONVERT_EXCEPTION_TO_ERROR_CODE(
+      { qlinear_out_unary<ZT_POST_NONE>(*tensor_handle_to_tensor_pointer(out), ZT_QL_PASS, ZT_QL_PASS_TAIL); });
+}
+
+extern "C" ZT_API AOTITorchError aoti_torch_cuda_zentorch_qlinear_relu_out(AtenTensorHandle out, ZT_QL_ARGS, ZT_QL_TAIL) {
+  AOTI_TORCH_CONVERT_EXCEPTION_TO_ERROR_CODE(
+      { qlinear_out_unary<ZT_POST_RELU>(*tensor_handle_to_tensor_pointer(out), ZT_QL_PASS, ZT_QL_PASS_TAIL); });
 }

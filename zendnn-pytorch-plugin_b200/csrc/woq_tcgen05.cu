@@ -63,6 +63,9 @@ constexpr int kThreads = 64 + 32 * (kDqWarps + kEpiWarps);
 constexpr int kEpiRowStride = 36;  // floats; 144 bytes keeps 16-byte alignment and spreads banks
 constexpr int kChunkKB = 4;        // k-blocks per packed-weight chunk: 4 x 32 B = one 128-byte row
 constexpr int kChunkBytes = kBN * 128;
+// per packed chunk: up to two groups x 128 columns of fp32 scales (1 KB), then the same for zero points
+constexpr int kScaleSlotBytes = 2048;
+constexpr int kZeroSlotOffset = 1024;
 
 struct TcParams {
   int M, N, K;
@@ -86,6 +89,9 @@ struct TcParams {
   // sums [ksplit][M][N] that a second kernel adds.  ksplit = 1: kps = K / 64, partial unused.
   int ksplit, kps;
   float *partial;
+  // Scales (and zero points) staged in shared memory with every packed chunk: groups per chunk (1 or 2; 0 = the
+  // conversion threads fetch them from global memory), log2 of the group size, groups per expert.
+  int staged_gpc, gs_log2, groups;
 };
 
 struct TileInfo {
@@ -124,9 +130,10 @@ struct SmemLayout {
   static constexpr int kWRingBytes = STAGES * kWBytes;
   static constexpr int kTileBytes = kWRingBytes + XSTAGES * kXBytes;
   static constexpr int kPackedBytes = PSTAGES * kChunkBytes;
+  static constexpr int kScaleBytes = PSTAGES * kScaleSlotBytes;   // scales / zero points of every packed chunk
   static constexpr int kEpiBytes = kEpiWarps * 32 * kEpiRowStride * 4;
   static constexpr int kBarBytes = (2 * STAGES + 2 * XSTAGES + 2 * PSTAGES + 4) * 8 + 8;
-  static constexpr int kTotal = kTileBytes + kPackedBytes + kEpiBytes + kBarBytes + 1024;
+  static constexpr int kTotal = kTileBytes + kPackedBytes + kScaleBytes + kEpiBytes + kBarBytes + 1024;
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -209,13 +216,16 @@ constexpr int kTeamWarps = kDqWarps / kTeams;  // 4 warps = 128 threads = one we
 template <int BT, int STAGES, int XSTAGES, int PSTAGES, bool ASYM>
 __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                   const __grid_constant__ CUtensorMap tmap_w,
+                                                                  const __grid_constant__ CUtensorMap tmap_s,
+                                                                  const __grid_constant__ CUtensorMap tmap_z,
                                                                   const TcParams p) {
   using L = SmemLayout<BT, STAGES, XSTAGES, PSTAGES>;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char *smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
   unsigned char *packed = smem + L::kTileBytes;  // ring of packed-weight chunks (1024-byte aligned)
-  float *epi_scratch = reinterpret_cast<float *>(smem + L::kTileBytes + L::kPackedBytes);
-  uint64_t *full_x = reinterpret_cast<uint64_t *>(smem + L::kTileBytes + L::kPackedBytes + L::kEpiBytes);
+  unsigned char *sc_ring = smem + L::kTileBytes + L::kPackedBytes;   // scales / zero points of the packed chunks
+  float *epi_scratch = reinterpret_cast<float *>(sc_ring + L::kScaleBytes);
+  uint64_t *full_x = reinterpret_cast<uint64_t *>(sc_ring + L::kScaleBytes + L::kEpiBytes);
   uint64_t *empty_x = full_x + XSTAGES;      // activation slot read by the MMAs of its k-block
   uint64_t *full_w = empty_x + XSTAGES;      // converted weight block written
   uint64_t *empty_bar = full_w + STAGES;     // converted weight block read by the MMAs of its k-block
@@ -240,6 +250,10 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
   if (threadIdx.x == 0) {
     tc::prefetch_tensormap(&tmap_x);
     tc::prefetch_tensormap(&tmap_w);
+    if (p.staged_gpc) {
+      tc::prefetch_tensormap(&tmap_s);
+      if (ASYM) tc::prefetch_tensormap(&tmap_z);
+    }
     for (int s = 0; s < XSTAGES; ++s) {
       tc::mbar_init(&full_x[s], 1);
       tc::mbar_init(&empty_x[s], 1);
@@ -293,10 +307,17 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
           if (!done) return false;
         }
         const TileInfo t = decode_tile(p, ptile, n_mt, BT);
-        tc::mbar_expect_tx(&full_p[ps], kChunkBytes);
+        const int chunk = t.kb0 / kChunkKB + pchunk;            // chunk of 256 k within K
+        const uint32_t sc_bytes = (uint32_t)p.staged_gpc * kBN * (p.scale_dtype == ZT_F32 ? 4u : 2u);
+        tc::mbar_expect_tx(&full_p[ps], kChunkBytes + (ASYM ? 2u : 1u) * sc_bytes);
         // rows of the stacked weight: expert * N + n0 ; 32 words (four k-blocks) per row
-        tc::tma_load_2d(packed + ps * kChunkBytes, &tmap_w, &full_p[ps], (t.kb0 / kChunkKB + pchunk) * (kChunkKB * 8),
-                        t.expert * p.N + t.n0);
+        tc::tma_load_2d(packed + ps * kChunkBytes, &tmap_w, &full_p[ps], chunk * (kChunkKB * 8), t.expert * p.N + t.n0);
+        if (p.staged_gpc) {
+          // the chunk's groups x 128 columns of the scale table (rows = expert * groups + group)
+          const int g0 = t.expert * p.groups + ((chunk * (kChunkKB * kBK)) >> p.gs_log2);
+          tc::tma_load_2d(sc_ring + ps * kScaleSlotBytes, &tmap_s, &full_p[ps], t.n0, g0);
+          if (ASYM) tc::tma_load_2d(sc_ring + ps * kScaleSlotBytes + kZeroSlotOffset, &tmap_z, &full_p[ps], t.n0, g0);
+        }
         ++pit;
         if (++pchunk == num_chunks) {
           pchunk = 0;
@@ -399,19 +420,30 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
       }
     };
     Sc nxt{0.f, 0.f, 0.f, 0.f};
-    fetch(0, 0, nxt);
+    const bool staged = p.staged_gpc != 0;
+    if (!staged) fetch(0, 0, nxt);
     uint32_t pit = 0;   // packed chunks walked so far (every team walks every chunk)
     bool ok = true;
     for (int local = 0; local < my_tiles; ++local) {
       const uint32_t it0 = (uint32_t)local * (uint32_t)num_kb;   // ring position of the tile's first k-block
       const uint32_t jt = (team - it0) & 3u;
       for (int chunk = 0; chunk < num_chunks; ++chunk, ++pit) {
-        const Sc cur = nxt;
-        if (chunk + 1 < num_chunks) fetch(local, chunk + 1, nxt); else fetch(local + 1, 0, nxt);
+        Sc cur = nxt;
+        if (!staged) {
+          if (chunk + 1 < num_chunks) fetch(local, chunk + 1, nxt); else fetch(local + 1, 0, nxt);
+        }
         const uint32_t ps = pit % PSTAGES;
         if (ok && !tc::mbar_wait(&full_p[ps], (pit / PSTAGES) & 1)) {
           tc::report_timeout(p.status, kStatusConvertTimeout);
           ok = false;
+        }
+        if (staged && ok) {
+          // groups are at least 128 k wide here, so both halves of a k-block share one; with two groups per chunk
+          // the k-blocks 0, 1 take the first and 2, 3 the second
+          const int gl = p.staged_gpc == 2 ? (int)(jt >> 1) : 0;
+          const unsigned char *slot = sc_ring + ps * kScaleSlotBytes;
+          cur.s0 = cur.s1 = load_as_float(slot, gl * kBN + row, p.scale_dtype);
+          if (ASYM) cur.z0 = cur.z1 = load_as_float(slot + kZeroSlotOffset, gl * kBN + row, p.scale_dtype);
         }
         const int kb = chunk * kChunkKB + (int)jt;
         if (kb < num_kb) {
@@ -732,17 +764,19 @@ struct MapKeyHash {
 // Tensor maps: activations [rows, K] bf16 with a (64 x BT) box; packed weights [rows, K/8] u32 with a
 // (32 words x 128 rows) box; both 128-byte swizzled.  Memoised per process.
 int cached_map(CUtensorMap *out, const void *ptr, CUtensorMapDataType dt, uint64_t inner, uint64_t rows,
-               uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows) {
+               uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle = true) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  const MapKey key{ptr, inner * 4 + (uint64_t)dt % 4, rows, box_rows * 1024 + box_inner};
+  const MapKey key{ptr, inner * 4 + (uint64_t)dt % 4, rows, (box_rows * 1024 + box_inner) * 2 + (swizzle ? 1u : 0u)};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
     *out = it->second;
     return ZT_SUCCESS;
   }
-  int rc = make_tensor_map_2d(out, ptr, dt, 0, inner, rows, pitch_bytes, box_inner, box_rows);
+  const uint64_t dims[2] = {inner, rows}, strides[1] = {pitch_bytes};
+  const uint32_t box[2] = {box_inner, box_rows};
+  int rc = make_tensor_map(out, ptr, dt, 2, dims, strides, box, swizzle);
   if (rc != ZT_SUCCESS) return rc;
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, *out);
@@ -763,6 +797,32 @@ int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows,
   rc = cached_map(&tw, p.wq, CU_TENSOR_MAP_DATA_TYPE_UINT32, (uint64_t)p.K / 8, (uint64_t)w_rows, (uint64_t)p.K / 2,
                   kChunkKB * 8, kBN);
   if (rc != ZT_SUCCESS) return rc;
+  // Scales and zero points travel with the packed chunks (one or two groups x 128 columns per chunk) when a
+  // group is a power of two of at least 128 k and the tables can be addressed by TMA; otherwise the conversion
+  // threads fetch them from global memory.
+  CUtensorMap ts = tw, tz = tw;
+  p.staged_gpc = 0;
+  {
+    const uint64_t esz = p.scale_dtype == ZT_F32 ? 4 : 2;
+    const bool pow2 = (p.gs & (p.gs - 1)) == 0;
+    const bool aligned = ((uint64_t)p.N * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.scales) & 15) == 0 &&
+                         (!asym || (reinterpret_cast<uintptr_t>(p.zeros) & 15) == 0);
+    if (pow2 && p.gs >= 128 && aligned) {
+      int lg = 0;
+      while ((1 << lg) < p.gs) ++lg;
+      p.gs_log2 = lg;
+      p.groups = p.K / p.gs;
+      p.staged_gpc = p.gs == 128 ? 2 : 1;
+      const uint64_t table_rows = (uint64_t)(w_rows / p.N) * (uint64_t)p.groups;   // experts x groups
+      const CUtensorMapDataType sdt = p.scale_dtype == ZT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+      rc = cached_map(&ts, p.scales, sdt, (uint64_t)p.N, table_rows, (uint64_t)p.N * esz, kBN, (uint32_t)p.staged_gpc, false);
+      if (rc != ZT_SUCCESS) return rc;
+      if (asym) {
+        rc = cached_map(&tz, p.zeros, sdt, (uint64_t)p.N, table_rows, (uint64_t)p.N * esz, kBN, (uint32_t)p.staged_gpc, false);
+        if (rc != ZT_SUCCESS) return rc;
+      }
+    }
+  }
   const long long tiles = (long long)(p.g_count ? max_row_tiles : p.m_tiles) * p.n_tiles * p.ksplit;
   const int sms = sm_count();
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));
@@ -770,12 +830,12 @@ int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows,
     auto kern = woq_tcgen05_kernel<BT, STAGES, XSTAGES, PSTAGES, true>;
     static PerDeviceOnce configured;
     if (int rc_cfg = allow_dynamic_smem(configured, kern, L::kTotal)) return rc_cfg;
-    ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, p));
+    ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, ts, tz, p));
   } else {
     auto kern = woq_tcgen05_kernel<BT, STAGES, XSTAGES, PSTAGES, false>;
     static PerDeviceOnce configured;
     if (int rc_cfg = allow_dynamic_smem(configured, kern, L::kTotal)) return rc_cfg;
-    ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, p));
+    ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, ts, tz, p));
   }
   return launch_status("woq_tcgen05_kernel");
 }
@@ -785,7 +845,7 @@ int launch_any(int bt, const TcParams &p, const void *x, int64_t x_rows, int64_t
   switch (bt) {
     // <token tile, converted-weight stages, activation slots, packed chunks>
     case 32: return launch_bt<32, 4, 12, 5>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
-    case 64: return launch_bt<64, 4, 7, 5>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+    case 64: return launch_bt<64, 4, 6, 5>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
     case 128: return launch_bt<128, 4, 4, 4>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
     case 256: return launch_bt<256, 4, 3, 2>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
     default: break;

@@ -13,7 +13,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libzentorch_b200.so"
 
 ZT_SUCCESS = 0
-ZT_BF16, ZT_F32 = 0, 1
+ZT_BF16, ZT_F32, ZT_U8, ZT_S8 = 0, 1, 2, 3
 ZT_MAX_POST_OPS = 4
 ZT_WOQ_COUNTER_BYTES = 16384
 ZT_ALGO_AUTO, ZT_ALGO_GENERIC, ZT_ALGO_SKINNY, ZT_ALGO_TCGEN05 = 0, 1, 2, 3
@@ -29,6 +29,7 @@ EXPORTED_SYMBOLS = (
     "zt_woq_linear_workspace_bytes", "zt_woq_linear", "zt_woq_repack_weight", "zt_woq_repack_from_int4pack",
     "zt_dynamic_qlinear_workspace_bytes", "zt_dynamic_qlinear", "zt_dynamic_quantize", "zt_int8_gemm_s32",
     "zt_int8_weight_rowsum", "zt_qlinear_prequantized", "zt_dynamic_qlinear_static",
+    "zt_static_qlinear_workspace_bytes", "zt_static_qlinear", "zt_static_quantize",
     "zt_moe_woq_workspace_bytes", "zt_moe_woq", "zt_allreduce_symmetric_bytes", "zt_allreduce_bf16",
 )
 
@@ -54,6 +55,17 @@ class DynamicQLinearArgs(C.Structure):
         ("bias_dtype", C.c_int32), ("act_quant", C.c_int32), ("w_rowsum", C.c_void_p), ("post", PostOps),
         ("y", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("algo", C.c_int32),
         ("flags", C.c_int32),
+    ]
+
+
+class StaticQLinearArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("x_dtype", C.c_int32), ("M", C.c_int64), ("K", C.c_int64), ("N", C.c_int64),
+        ("x_scale", C.c_void_p), ("x_zero_point", C.c_void_p), ("w", C.c_void_p), ("w_scales", C.c_void_p),
+        ("w_scales_numel", C.c_int64), ("w_rowsum", C.c_void_p), ("bias", C.c_void_p), ("bias_dtype", C.c_int32),
+        ("post", PostOps), ("post_buffer_dtype", C.c_int32), ("out_scale", C.c_void_p),
+        ("out_zero_point", C.c_void_p), ("y", C.c_void_p), ("y_dtype", C.c_int32), ("ldy", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("algo", C.c_int32), ("flags", C.c_int32),
     ]
 
 
@@ -117,6 +129,10 @@ def lib() -> C.CDLL:
     L.zt_int8_gemm_s32.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                    C.c_int32, C.c_void_p]
     L.zt_qlinear_prequantized.argtypes = [C.POINTER(DynamicQLinearArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.zt_static_qlinear_workspace_bytes.restype = C.c_size_t
+    L.zt_static_qlinear_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int32]
+    L.zt_static_qlinear.argtypes = [C.POINTER(StaticQLinearArgs), C.c_void_p]
+    L.zt_static_quantize.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.zt_moe_woq_workspace_bytes.restype = C.c_size_t
     L.zt_moe_woq_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32]
     L.zt_moe_woq.argtypes = [C.POINTER(MoeWoqArgs), C.c_void_p]
@@ -165,6 +181,12 @@ def _dtype_code(t) -> int:
     if t.dtype == torch.float32:
         return ZT_F32
     raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _dtype_code8(dtype) -> int:
+    """Codes of the four tensor dtypes of the static qlinear."""
+    import torch
+    return {torch.bfloat16: ZT_BF16, torch.float32: ZT_F32, torch.uint8: ZT_U8, torch.int8: ZT_S8}[dtype]
 
 
 def _stream_ptr():
@@ -319,6 +341,49 @@ def dynamic_qlinear_static(x, w, w_scales, bias=None, act_quant=ZT_ACT_S8_SYM, p
     y = torch.empty(m, n, dtype=x.dtype, device=x.device)
     a = dynamic_qlinear_args(x, w, w_scales, bias, act_quant, post_ops, buffers, w_rowsum, y, None, algo)
     check(lib().zt_dynamic_qlinear_static(C.byref(a), _stream_ptr()))
+    return y
+
+
+def static_quantize(x, scale, zero_point=None):
+    """zt_static_quantize: per-tensor quantisation of x (fp32 / bf16) to u8 (zero point given) or s8."""
+    import torch
+    q = torch.empty(x.shape, dtype=torch.uint8 if zero_point is not None else torch.int8, device=x.device)
+    check(lib().zt_static_quantize(x.data_ptr(), _dtype_code(x), x.numel(), scale.data_ptr(),
+                                   zero_point.data_ptr() if zero_point is not None else None, q.data_ptr(),
+                                   _stream_ptr()))
+    return q
+
+
+def static_qlinear(x, w, x_scale, x_zero_point, w_scales, bias=None, out_scale=None, out_zero_point=None,
+                   out_dtype=None, post_ops=(), buffers=(), w_rowsum=None, algo=ZT_ALGO_AUTO, out=None, flags=0):
+    """zt_static_qlinear on 2-D operands: x [M, K] fp32 / bf16 / u8 / s8, w [N, K] int8, one-element x_scale
+    (fp32) and x_zero_point (int32 or None), w_scales fp32 with 1 or N elements, optional requantisation.
+    `out` may be a view with a row stride (its last dimension contiguous)."""
+    import torch
+    m, k = x.shape
+    n = w.shape[0]
+    if out_dtype is None:
+        out_dtype = torch.float32
+    y = out if out is not None else torch.empty(m, n, dtype=out_dtype, device=x.device)
+    nbytes = lib().zt_static_qlinear_workspace_bytes(m, k, _dtype_code8(x.dtype))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    if x_zero_point is not None and w_rowsum is None:
+        w_rowsum = int8_weight_rowsum(w)
+    a = StaticQLinearArgs()
+    a.x, a.x_dtype, a.M, a.K, a.N = x.data_ptr(), _dtype_code8(x.dtype), m, k, n
+    a.x_scale = x_scale.data_ptr()
+    a.x_zero_point = x_zero_point.data_ptr() if x_zero_point is not None else None
+    a.w, a.w_scales, a.w_scales_numel = w.data_ptr(), w_scales.data_ptr(), w_scales.numel()
+    a.w_rowsum = w_rowsum.data_ptr() if w_rowsum is not None else None
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.bias_dtype = _dtype_code(bias) if bias is not None else ZT_F32
+    a.post = _post(post_ops, buffers)
+    a.post_buffer_dtype = _dtype_code(buffers[0]) if buffers else ZT_F32
+    a.out_scale = out_scale.data_ptr() if out_scale is not None else None
+    a.out_zero_point = out_zero_point.data_ptr() if out_zero_point is not None else None
+    a.y, a.y_dtype, a.ldy = y.data_ptr(), _dtype_code8(y.dtype), y.stride(0) if m > 1 or out is not None else n
+    a.workspace, a.workspace_bytes, a.algo, a.flags = ws.data_ptr(), nbytes, algo, flags
+    check(lib().zt_static_qlinear(C.byref(a), _stream_ptr()))
     return y
 
 
