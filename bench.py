@@ -741,7 +741,8 @@ def run_profile_case(name):
     """A few plain launches (no CUDA graph) of one kernel on a case that is small enough to profile
     with `ncu --set full` and still larger than L2:
         python bench.py --profile int8_gemm|dynquant|woq_decode|woq_decode_small|woq_mid|woq_prefill|moe
-    and `--profile woq_timeline`, which prints where the time of the small-layer decode kernel goes."""
+    and `--profile woq_timeline[_large]`, which prints where the time of the decode kernels goes, and
+    `--profile woq_roles` (per-role cycle counters of the tensor-core weight-only kernel, diagnostic build)."""
     import ctypes as C
     import torch
     import zentorch_b200  # noqa: F401
@@ -785,6 +786,10 @@ def run_profile_case(name):
     elif name == "woq_timeline":          # config 1 (small layer)
         print(json.dumps(woq_timeline(torch, _capi, lib, dev)))
         return
+    elif name == "woq_roles":             # needs a build with ZENTORCH_B200_NVCC_DEFINES=-DZT_TCPROF
+        for m, k, n in ((32, 4096, 14336), (2048, 4096, 4096), (128, 8192, 8192)):
+            print(json.dumps(woq_roles(torch, _capi, lib, dev, m, k, n)))
+        return
     elif name == "woq_timeline_large":    # 117 MB layer
         print(json.dumps(woq_timeline(torch, _capi, lib, dev, k=8192, n=28672, chain=12, copies=3)))
         return
@@ -793,6 +798,47 @@ def run_profile_case(name):
     torch.cuda.synchronize()
     assert _capi.poll_device_status() == 0
     print(json.dumps({"profile_case": name, "status": "ok"}))
+
+
+def woq_roles(torch, _capi, lib, dev, m, k, n, launches=6):
+    """Where the warps of woq_tcgen05_kernel spend their cycles, per 128 x 64 weight block in steady state (the
+    first blocks of a CTA are left out): the MMA issuer, the TMA producer and conversion team 0.  The counters
+    exist only in a library built with ZENTORCH_B200_NVCC_DEFINES=-DZT_TCPROF (python -m zentorch_b200._build);
+    launches are separated by a synchronisation so that no launch waits for its predecessor."""
+    x = seeded_x(torch, dev, m, k, seed=1)
+    bias = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+    sets = [device_woq_weights(torch, _capi, dev, k, n, seed=s) for s in range(launches)]
+    for wq, sc in sets:
+        _capi.woq_linear(x, wq, sc, None, bias)
+    torch.cuda.synchronize()
+    buf = torch.zeros(launches * 148 * 4 * 8 * 2, dtype=torch.int64, device=dev)
+    _capi.check(lib.zt_debug_set_timeline(buf.data_ptr(), buf.numel() * 8))
+    for wq, sc in sets:
+        _capi.woq_linear(x, wq, sc, None, bias)
+        torch.cuda.synchronize()
+    _capi.check(lib.zt_debug_set_timeline(None, 0))
+    rec = buf.cpu().view(-1, 4, 8).double()
+    rec = rec[rec[:, 1, 0] > 0]
+    if rec.shape[0] == 0:
+        return {"profile_case": "woq_roles", "error": "no counters: build with ZENTORCH_B200_NVCC_DEFINES=-DZT_TCPROF"}
+    rec = rec[rec.shape[0] // 2:]
+
+    def role(r, labels, blocks_at):
+        nb = float(r[:, blocks_at].mean())
+        out = {"cycles_per_block": round(float(r[:, 0].mean()) / nb)}
+        out.update({lab: round(float(r[:, i + 1].mean()) / nb) for i, lab in enumerate(labels)})
+        return out
+    return {"profile_case": "woq_roles", "workload": f"WOQ int4 M={m} K={k} N={n}", "unit": "SM cycles per weight block",
+            "mma_issuer": role(rec[:, 1], ["wait_activations", "wait_converted_weights", "issue_and_commit",
+                                           "wait_accumulator", "of_which_commit"], 6),
+            "tma_producer": role(rec[:, 2], ["wait_activation_slot", "wait_packed_slot"], 3),
+            "conversion_team0_per_own_block": role(rec[:, 0], ["wait_packed_chunk", "wait_stage_free",
+                                                              "convert_and_arrive"], 4),
+            # one stage's round trip, block 16 of every CTA (cycles after team 0 announced the converted block)
+            "stage_round_trip": {"issuer_saw_block": round(float((rec[:, 3, 1] - rec[:, 3, 0]).median())),
+                                 "mmas_issued": round(float((rec[:, 3, 2] - rec[:, 3, 0]).median())),
+                                 "team_saw_stage_free": round(float((rec[:, 3, 3] - rec[:, 3, 0]).median())),
+                                 "next_block_announced": round(float((rec[:, 3, 4] - rec[:, 3, 0]).median()))}}
 
 
 def woq_timeline(torch, _capi, lib, dev, m=1, k=4096, n=4096, chain=24, copies=32):

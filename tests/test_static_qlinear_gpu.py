@@ -279,7 +279,8 @@ def test_aoti_shim(capi):
     lib = _capi._torch_boundary()
     m, k, n = 40, 256, 64
     c = _case(m, k, n, "bfloat16", True, "bfloat16", seed=6)
-    tensors = [c["x"].cuda(), c["w"].cuda(), c["xs"].cuda(), c["xzp"].cuda(), c["ws"].cuda(), torch.Tensor(),
+    w_zero_points = torch.zeros(1, dtype=torch.int32, device="cuda")   # symmetric weights, as the reference expects
+    tensors = [c["x"].cuda(), c["w"].cuda(), c["xs"].cuda(), c["xzp"].cuda(), c["ws"].cuda(), w_zero_points,
                c["bias"].cuda()]
     handles = [aoti_handle(t) for t in tensors]                  # (capsule, address) pairs
     vp = C.c_void_p

@@ -307,7 +307,8 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 extern "C" size_t zt_dynamic_qlinear_workspace_bytes(int64_t M, int64_t K) {
   if (M <= 0 || K <= 0) return 256;
-  return align_up((size_t)M * K, 256) + 2 * align_up((size_t)M * 4, 256);
+  const int64_t rows = M < kMinQRows ? kMinQRows : M;   // the quantised activations are padded to kMinQRows rows
+  return align_up((size_t)rows * K, 256) + 2 * align_up((size_t)M * 4, 256);
 }
 
 extern "C" int zt_dynamic_quantize(const void *x, int32_t x_dtype, int64_t M, int64_t K, int32_t act_quant, void *q,
@@ -360,6 +361,9 @@ extern "C" int zt_int8_gemm_s32(const void *q, int32_t q_is_u8, const int8_t *w,
   return run_int8_gemm(g, algo, (cudaStream_t)stream);
 }
 
+static int qlinear_prequantized_impl(const zt_dynamic_qlinear_args_t *a, const void *q, int64_t q_rows,
+                                     const float *src_scales, const int32_t *src_zero_points, void *stream);
+
 extern "C" int zt_dynamic_qlinear(const zt_dynamic_qlinear_args_t *a, void *stream) {
   ZT_REQUIRE(a != nullptr, ZT_INVALID_ARGUMENT, "zt_dynamic_qlinear: null argument block");
   ZT_REQUIRE(a->M >= 0 && a->N >= 0 && a->K >= 0, ZT_INVALID_ARGUMENT, "zt_dynamic_qlinear: negative size");
@@ -377,7 +381,10 @@ extern "C" int zt_dynamic_qlinear(const zt_dynamic_qlinear_args_t *a, void *stre
              "zt_dynamic_qlinear: the u8 mode needs w_rowsum (zt_int8_weight_rowsum)");
   int rc = validate_post_ops(a->post);
   if (rc != ZT_SUCCESS) return rc;
-  const size_t need = zt_dynamic_qlinear_workspace_bytes(a->M, a->K);
+  // the size asked for includes the padding of the quantised activations to kMinQRows rows; a workspace
+  // that only holds the M rows is accepted and used without the padding
+  const size_t padded = zt_dynamic_qlinear_workspace_bytes(a->M, a->K);
+  const size_t need = align_up((size_t)a->M * a->K, 256) + 2 * align_up((size_t)a->M * 4, 256);
   ZT_REQUIRE(a->workspace && a->workspace_bytes >= need, ZT_WORKSPACE_TOO_SMALL,
              "zt_dynamic_qlinear: workspace of %zu bytes is smaller than the %zu required", a->workspace_bytes, need);
   ZT_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, ZT_INVALID_ARGUMENT,
@@ -386,15 +393,22 @@ extern "C" int zt_dynamic_qlinear(const zt_dynamic_qlinear_args_t *a, void *stre
   CallOverlap overlap(!(a->flags & ZT_FLAG_WEIGHTS_VOLATILE));
   char *ws = reinterpret_cast<char *>(a->workspace);
   void *q = ws;
-  float *scales = reinterpret_cast<float *>(ws + align_up((size_t)a->M * a->K, 256));
+  const int64_t q_rows = (a->M < kMinQRows && a->workspace_bytes >= padded) ? kMinQRows : a->M;
+  float *scales = reinterpret_cast<float *>(ws + align_up((size_t)q_rows * a->K, 256));
   int32_t *zps = reinterpret_cast<int32_t *>(reinterpret_cast<char *>(scales) + align_up((size_t)a->M * 4, 256));
   rc = dynamic_quantize_launch(a->x, a->x_dtype, a->M, a->K, a->act_quant, q, scales, zps, st);
   if (rc != ZT_SUCCESS) return rc;
-  return zt_qlinear_prequantized(a, q, scales, zps, stream);
+  return qlinear_prequantized_impl(a, q, q_rows, scales, zps, stream);
 }
 
 extern "C" int zt_qlinear_prequantized(const zt_dynamic_qlinear_args_t *a, const void *q, const float *src_scales,
                                        const int32_t *src_zero_points, void *stream) {
+  return qlinear_prequantized_impl(a, q, 0, src_scales, src_zero_points, stream);
+}
+
+// q_rows: rows addressable behind q (0: exactly M)
+static int qlinear_prequantized_impl(const zt_dynamic_qlinear_args_t *a, const void *q, int64_t q_rows,
+                                     const float *src_scales, const int32_t *src_zero_points, void *stream) {
   ZT_REQUIRE(a != nullptr, ZT_INVALID_ARGUMENT, "zt_qlinear_prequantized: null argument block");
   ZT_REQUIRE(a->M >= 0 && a->N >= 0 && a->K >= 0, ZT_INVALID_ARGUMENT, "zt_qlinear_prequantized: negative size");
   ZT_REQUIRE(valid_dtype(a->x_dtype) && valid_dtype(a->w_scale_dtype) && (!a->bias || valid_dtype(a->bias_dtype)),
@@ -416,6 +430,7 @@ extern "C" int zt_qlinear_prequantized(const zt_dynamic_qlinear_args_t *a, const
   g.N = a->N;
   g.K = a->K;
   g.raw_s32 = false;
+  g.q_rows = q_rows;
   g.src_scale = src_scales;
   g.src_zp = u8 ? src_zero_points : nullptr;
   g.w_scale = a->w_scales;

@@ -23,6 +23,7 @@ struct Int8GemmArgs {
   void *y;
   PostOpsDev post;
   int force_bn;            // 0 = choose
+  int64_t q_rows;          // rows addressable behind q when more than M (scratch padded by the caller), else 0
   // Static-quantisation form (zt_static_qlinear): src_scale / src_zp hold one element for the whole tensor,
   // w_scale is fp32 and may be one element, binary post-op operands have their own dtype, rows of y are ldy
   // elements apart, and with out_scale the result is requantised to y_dtype (ZT_U8 with out_zp, else ZT_S8).
@@ -61,6 +62,9 @@ __device__ __forceinline__ void store_static(void *y, int64_t i, int y_dtype, fl
   else
     store_from_float(y, i, y_dtype, v);
 }
+
+// The quantised activations of a call with fewer rows live in scratch padded to this many rows.
+constexpr int64_t kMinQRows = 16;
 
 bool int8_tcgen05_supported(int64_t M, int64_t N, int64_t K, const void *q, const void *w);
 int int8_tcgen05_launch(const Int8GemmArgs &a, cudaStream_t st);

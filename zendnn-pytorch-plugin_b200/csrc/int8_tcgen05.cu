@@ -105,10 +105,6 @@ int int8_tcgen05_launch(const Int8GemmArgs &a, cudaStream_t st) {
   p.y = a.y;
   p.post = a.post;
   p.status = device_status_ptr();
-  {
-    static const int forced = [] { const char *e = getenv("ZENTORCH_B200_INT8_KROT"); return e ? atoi(e) : -1; }();
-    p.k_stagger = forced >= 0 ? forced : (a.M <= 64 ? 1 : 0);
-  }
   p.w_scale_per_tensor = a.w_scale_per_tensor;
   p.post_dtype = a.post_dtype;
   p.out_scale = a.out_scale;
@@ -125,7 +121,10 @@ int int8_tcgen05_launch(const Int8GemmArgs &a, cudaStream_t st) {
   if (a.force_bn > 0) tile = {a.force_bn >= 1000 ? 2 : 1, a.force_bn % 1000};
   const int bn = tile.bn;
   CUtensorMap ta, tb;
-  int rc = cached_map(&ta, a.q, (uint64_t)a.K, (uint64_t)a.M, (uint32_t)(tile.mh * kBM));
+  // q_rows: rows that may be addressed behind q (the caller's scratch is padded to kMinQRows rows so that the
+  // activation map never has fewer; rows beyond M hold stale bytes whose products are never stored)
+  const uint64_t q_rows = a.q_rows > a.M ? (uint64_t)a.q_rows : (uint64_t)a.M;
+  int rc = cached_map(&ta, a.q, (uint64_t)a.K, q_rows, (uint32_t)(tile.mh * kBM));
   if (rc != ZT_SUCCESS) return rc;
   rc = cached_map(&tb, a.w, (uint64_t)a.K, (uint64_t)a.N, (uint32_t)bn);
   if (rc != ZT_SUCCESS) return rc;

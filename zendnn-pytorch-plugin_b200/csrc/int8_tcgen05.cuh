@@ -53,7 +53,6 @@ struct TcParams {
   void *y;                 // [M,N] (y_dtype) or int32 for kEpiS32
   PostOpsDev post;
   int *status;             // device status word (bounded-wait failures)
-  int k_stagger;           // 1: column tile t starts its walk over K at block t % num_kb (see rotated_kb)
   // kEpiStatic only
   bool w_scale_per_tensor;
   int post_dtype;
@@ -225,14 +224,6 @@ __device__ __forceinline__ void finish_chunk_static(const TcParams &p, const uin
   }
 }
 
-// With few activation rows every CTA asks for the same few 128-byte lines of the activations at every k-block;
-// integer accumulation does not depend on the order, so column tiles may start their walk over K at
-// different blocks and spread those requests over the activations' lines.
-__device__ __forceinline__ int rotated_kb(int kb, int rot, int num_kb) {
-  const int k = kb + rot;
-  return k >= num_kb ? k - num_kb : k;
-}
-
 template <int MH, int BN, int STAGES, int NBUF, int EPI, bool A_SIGNED>
 __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                    const __grid_constant__ CUtensorMap tmap_b,
@@ -288,21 +279,19 @@ __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_
       if ((int)blockIdx.x < total_tiles) {
         const int m0 = ((int)blockIdx.x % p.m_tiles) * (MH * kBM);
         const int n0 = ((int)blockIdx.x / p.m_tiles) * BN;
-        const int rot = p.k_stagger ? ((int)blockIdx.x / p.m_tiles) % num_kb : 0;
         pre = num_kb < STAGES ? num_kb : STAGES;
         for (int kb = 0; kb < pre; ++kb) {
           tc::mbar_expect_tx(&full_bar[kb], L::kStageBytes);
-          tc::tma_load_2d(smem + kb * L::kStageBytes + L::kABytes, &tmap_b, &full_bar[kb], rotated_kb(kb, rot, num_kb) * kBK, n0);
+          tc::tma_load_2d(smem + kb * L::kStageBytes + L::kABytes, &tmap_b, &full_bar[kb], kb * kBK, n0);
         }
         grid_dependency_wait();
         for (int kb = 0; kb < pre; ++kb)
-          tc::tma_load_2d(smem + kb * L::kStageBytes, &tmap_a, &full_bar[kb], rotated_kb(kb, rot, num_kb) * kBK, m0);
+          tc::tma_load_2d(smem + kb * L::kStageBytes, &tmap_a, &full_bar[kb], kb * kBK, m0);
         it = (uint32_t)pre;
       }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % p.m_tiles) * (MH * kBM);
         const int n0 = (tile / p.m_tiles) * BN;
-        const int rot = p.k_stagger ? (tile / p.m_tiles) % num_kb : 0;
         for (int kb = (tile == (int)blockIdx.x ? pre : 0); kb < num_kb; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -314,9 +303,8 @@ __global__ void __launch_bounds__(kThreads, 1) int8_tcgen05_kernel(const __grid_
           unsigned char *a_dst = smem + s * L::kStageBytes;
           unsigned char *b_dst = a_dst + L::kABytes;
           tc::mbar_expect_tx(&full_bar[s], L::kStageBytes);
-          const int kx = rotated_kb(kb, rot, num_kb) * kBK;
-          tc::tma_load_2d(a_dst, &tmap_a, &full_bar[s], kx, m0);
-          tc::tma_load_2d(b_dst, &tmap_b, &full_bar[s], kx, n0);
+          tc::tma_load_2d(a_dst, &tmap_a, &full_bar[s], kb * kBK, m0);
+          tc::tma_load_2d(b_dst, &tmap_b, &full_bar[s], kb * kBK, n0);
         }
       }
     }

@@ -92,6 +92,10 @@ struct TcParams {
   // Scales (and zero points) staged in shared memory with every packed chunk: groups per chunk (1 or 2; 0 = the
   // conversion threads fetch them from global memory), log2 of the group size, groups per expert.
   int staged_gpc, gs_log2, groups;
+#ifdef ZT_TCPROF
+  TimelineSink prof;   // 4 records of 8 counters per CTA: conversion team 0, MMA issuer, producer, epilogue warp 0
+  int dbg;             // ZENTORCH_B200_TCDBG: 1 no MMA issue, 2 no activation loads, 4 no conversion arithmetic (timing only, results are garbage)
+#endif
 };
 
 struct TileInfo {
@@ -210,6 +214,19 @@ __global__ void __launch_bounds__(256) woq_splitk_reduce_kernel(const float *__r
   *reinterpret_cast<uint2 *>(y + base) = o;
 }
 
+#ifdef ZT_TCPROF
+#define TCP_T0() const long long tcp_t0 = clock64()
+#define TCP_ADD(acc) acc += (tcp_warm ? clock64() - tcp_t0 : 0)
+#define TCP_DBG(bit) ((p.dbg & (bit)) != 0)
+#else
+#define TCP_T0()
+#define TCP_ADD(acc)
+#define TCP_DBG(bit) false
+#endif
+// Waits of the two pacing threads poll; the conversion teams and the epilogue warps, which wait most of the time,
+// let the hardware suspend them between polls (fewer barrier reads competing with the pacing threads).
+#define TC_WAIT1(bar, par) tc::mbar_wait(bar, par)
+#define TC_WAITN(bar, par) tc::mbar_wait_suspend(bar, par)
 constexpr int kTeams = 4;                      // conversion teams (token tiles up to 128)
 constexpr int kTeamWarps = kDqWarps / kTeams;  // 4 warps = 128 threads = one weight row per thread
 
@@ -281,47 +298,57 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
 
   if (warp == 0) {
     // ---------------- TMA producer: packed-weight chunks (running ahead) and activation tiles ----------------
+    // One thread paces the whole pipeline together with the MMA issuer, so its loop keeps ring positions and
+    // phases as counters and works on shared-window addresses computed once (no divisions, no generic-to-shared
+    // conversions per k-block).
     if (lane == 0) {
-      uint32_t it = 0;   // activation stage ring position
-      uint32_t pit = 0;  // packed chunk ring position
       bool ok = true;
-      // Issues the next packed chunk if its ring slot is free (or, when `must`, waits for the slot).
-      int ptile = blockIdx.x, pchunk = 0;  // next chunk to issue
+#ifdef ZT_TCPROF
+      long long pc_total = 0, pc_emptyx = 0, pc_must = 0;
+      bool tcp_warm = false;
+      uint32_t it = 0;
+#endif
+      const uint32_t full_p0 = smem_u32(full_p), empty_p0 = smem_u32(empty_p);
+      const uint32_t full_x0 = smem_u32(full_x), empty_x0 = smem_u32(empty_x);
+      const uint32_t packed0 = smem_u32(packed), sc0 = smem_u32(sc_ring), x0 = smem_u32(smem + L::kWRingBytes);
+      const uint32_t chunk_tx = kChunkBytes + (ASYM ? 2u : 1u) * (uint32_t)p.staged_gpc * kBN * (p.scale_dtype == ZT_F32 ? 4u : 2u);
+      // packed chunks: next chunk to issue = (ptile, pchunk); its tile's coordinates are decoded when the tile changes
+      int ptile = blockIdx.x, pchunk = 0;
+      uint32_t p_s = 0, p_ph = 1;          // ring slot and the parity of its "free" barrier
+      int issued = 0;                      // chunks issued so far
+      TileInfo pt = decode_tile(p, ptile < total_tiles ? ptile : 0, n_mt, BT);
       auto issue_packed = [&](bool must) -> bool {
         if (ptile >= total_tiles) return false;
-        const uint32_t ps = pit % PSTAGES;
-        const uint32_t pph = (pit / PSTAGES) & 1;
         if (must) {
-          if (!tc::mbar_wait(&empty_p[ps], pph ^ 1)) {
+          if (!TC_WAIT1(&empty_p[p_s], p_ph)) {
             tc::report_timeout(p.status, kStatusProducerTimeout);
             ok = false;
             return false;
           }
-        } else {
-          uint32_t done;
-          asm volatile(
-              "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-              : "=r"(done)
-              : "r"(smem_u32(&empty_p[ps])), "r"(pph ^ 1)
-              : "memory");
-          if (!done) return false;
+        } else if (!tc::mbar_test_addr(empty_p0 + p_s * 8, p_ph)) {
+          // test_wait returns at once: this thread has the activation tiles to request in the meantime
+          return false;
         }
-        const TileInfo t = decode_tile(p, ptile, n_mt, BT);
-        const int chunk = t.kb0 / kChunkKB + pchunk;            // chunk of 256 k within K
-        const uint32_t sc_bytes = (uint32_t)p.staged_gpc * kBN * (p.scale_dtype == ZT_F32 ? 4u : 2u);
-        tc::mbar_expect_tx(&full_p[ps], kChunkBytes + (ASYM ? 2u : 1u) * sc_bytes);
+        const int chunk = pt.kb0 / kChunkKB + pchunk;            // chunk of 256 k within K
+        const uint32_t bar = full_p0 + p_s * 8;
+        tc::mbar_expect_tx_addr(bar, chunk_tx);
         // rows of the stacked weight: expert * N + n0 ; 32 words (four k-blocks) per row
-        tc::tma_load_2d(packed + ps * kChunkBytes, &tmap_w, &full_p[ps], chunk * (kChunkKB * 8), t.expert * p.N + t.n0);
+        tc::tma_load_2d_addr(packed0 + p_s * kChunkBytes, &tmap_w, bar, chunk * (kChunkKB * 8), pt.expert * p.N + pt.n0);
         if (p.staged_gpc) {
           // the chunk's groups x 128 columns of the scale table (rows = expert * groups + group)
-          const int g0 = t.expert * p.groups + ((chunk * (kChunkKB * kBK)) >> p.gs_log2);
-          tc::tma_load_2d(sc_ring + ps * kScaleSlotBytes, &tmap_s, &full_p[ps], t.n0, g0);
-          if (ASYM) tc::tma_load_2d(sc_ring + ps * kScaleSlotBytes + kZeroSlotOffset, &tmap_z, &full_p[ps], t.n0, g0);
+          const int g0 = pt.expert * p.groups + ((chunk * (kChunkKB * kBK)) >> p.gs_log2);
+          tc::tma_load_2d_addr(sc0 + p_s * kScaleSlotBytes, &tmap_s, bar, pt.n0, g0);
+          if (ASYM) tc::tma_load_2d_addr(sc0 + p_s * kScaleSlotBytes + kZeroSlotOffset, &tmap_z, bar, pt.n0, g0);
         }
-        ++pit;
+        ++issued;
+        if (++p_s == PSTAGES) {
+          p_s = 0;
+          p_ph ^= 1;
+        }
         if (++pchunk == num_chunks) {
           pchunk = 0;
           ptile += gridDim.x;
+          if (ptile < total_tiles) pt = decode_tile(p, ptile, n_mt, BT);
         }
         return true;
       };
@@ -329,63 +356,149 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
       while (issue_packed(false)) {
       }
       grid_dependency_wait();
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      uint32_t x_s = 0, x_ph = 1;          // activation slot and the parity of its "free" barrier
+      int need_base = 0;                   // chunks of the tiles before this one
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, need_base += num_chunks) {
         const TileInfo t = decode_tile(p, tile, n_mt, BT);
-        for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+        int kx = t.kb0 * kBK;
+        for (int kb = 0; kb < num_kb && ok; ++kb, kx += kBK) {
+#ifdef ZT_TCPROF
+          if (it == 8) { tcp_warm = true; pc_total = clock64(); }
+          ++it;
+#endif
           // keep the packed ring full without blocking; the chunk this k-block needs must be issued
           while (issue_packed(false)) {
           }
-          const long long need = (long long)((tile - blockIdx.x) / gridDim.x) * num_chunks + kb / kChunkKB;
-          while (ok && (long long)pit <= need) issue_packed(true);
-          const uint32_t s = it % XSTAGES;
-          const uint32_t ph = (it / XSTAGES) & 1;
-          if (!tc::mbar_wait(&empty_x[s], ph ^ 1)) {
-            tc::report_timeout(p.status, kStatusProducerTimeout);
-            ok = false;
-            break;
+          {
+            TCP_T0();
+            const int need = need_base + (kb >> 2);
+            while (ok && issued <= need) issue_packed(true);
+            TCP_ADD(pc_must);
           }
-          tc::mbar_expect_tx(&full_x[s], L::kXBytes);
-          tc::tma_load_2d(smem + L::kWRingBytes + s * L::kXBytes, &tmap_x, &full_x[s], (t.kb0 + kb) * kBK, t.m0);
+          if (TCP_DBG(2)) continue;
+          {
+            TCP_T0();
+            const bool got = TC_WAIT1(&empty_x[x_s], x_ph);
+            TCP_ADD(pc_emptyx);
+            if (!got) {
+              tc::report_timeout(p.status, kStatusProducerTimeout);
+              ok = false;
+              break;
+            }
+          }
+          const uint32_t bar = full_x0 + x_s * 8;
+          tc::mbar_expect_tx_addr(bar, L::kXBytes);
+          tc::tma_load_2d_addr(x0 + x_s * L::kXBytes, &tmap_x, bar, kx, t.m0);
+          if (++x_s == XSTAGES) {
+            x_s = 0;
+            x_ph ^= 1;
+          }
         }
       }
+      (void)empty_x0;
+#ifdef ZT_TCPROF
+      if (p.prof.base) {
+        unsigned long long *o = p.prof.base + ((size_t)blockIdx.x * 4 + 2) * kTimelineSlots;
+        o[0] = clock64() - pc_total; o[1] = pc_emptyx; o[2] = pc_must; o[3] = it - 8;
+      }
+#endif
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
+    // The other thread that paces the pipeline: ring positions and phases as counters, descriptors put together
+    // from a constant high word and a start-address field that advances by a constant per stage.
     if (lane == 0) {
       constexpr uint32_t idesc = tc::instr_desc(1u, 1u, 1u, kBN, BT);  // f32 accumulate, bf16 x bf16
-      uint32_t it = 0;
       bool ok = true;
       int local = 0;
+#ifdef ZT_TCPROF
+      long long mc_total = 0, mc_fullx = 0, mc_fullw = 0, mc_issue = 0, mc_tmem = 0, mc_commit = 0;
+      bool tcp_warm = false;
+      uint32_t it = 0;
+#endif
+      const uint64_t d0 = tc::smem_desc_k_sw128(0);
+      const uint32_t desc_hi = (uint32_t)(d0 >> 32), desc_lo = (uint32_t)d0;
+      const uint32_t w_field0 = desc_lo | ((smem_u32(smem) & 0x3FFFF) >> 4);
+      const uint32_t x_field0 = desc_lo | ((smem_u32(smem + L::kWRingBytes) & 0x3FFFF) >> 4);
+      const uint32_t full_x0 = smem_u32(full_x), empty_x0 = smem_u32(empty_x);
+      const uint32_t full_w0 = smem_u32(full_w), empty_w0 = smem_u32(empty_bar);
+      uint32_t w_s = 0, w_ph = 0, x_s = 0, x_ph = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
         const uint32_t buf = local & 1;
         const uint32_t use = (uint32_t)local >> 1;
-        if (ok && !tc::mbar_wait(&tmem_empty[buf], (use & 1) ^ 1)) {
-          tc::report_timeout(p.status, kStatusMmaTimeout);
-          ok = false;
+        {
+          TCP_T0();
+          if (ok && !TC_WAIT1(&tmem_empty[buf], (use & 1) ^ 1)) {
+            tc::report_timeout(p.status, kStatusMmaTimeout);
+            ok = false;
+          }
+          TCP_ADD(mc_tmem);
         }
         tc::fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BT;
-        for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
-          const uint32_t s = it % STAGES, xs = it % XSTAGES;
-          const uint32_t ph = (it / STAGES) & 1, xph = (it / XSTAGES) & 1;
-          if (!tc::mbar_wait(&full_x[xs], xph) || !tc::mbar_wait(&full_w[s], ph)) {
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+#ifdef ZT_TCPROF
+          if (it == 8) { tcp_warm = true; mc_total = clock64(); }
+#endif
+          bool got;
+          {
+            TCP_T0();
+            got = TCP_DBG(2) || tc::mbar_wait_addr(full_x0 + x_s * 8, x_ph);
+            TCP_ADD(mc_fullx);
+          }
+          {
+            TCP_T0();
+            got = got && tc::mbar_wait_addr(full_w0 + w_s * 8, w_ph);
+            TCP_ADD(mc_fullw);
+          }
+          if (!got) {
             tc::report_timeout(p.status, kStatusMmaTimeout);
             ok = false;
             break;
           }
+#ifdef ZT_TCPROF
+          if (p.prof.base && it == 16) p.prof.base[((size_t)blockIdx.x * 4 + 3) * kTimelineSlots + 1] = clock64();   // MMA issuer saw W(16)
+#endif
+          TCP_T0();
           tc::fence_after_sync();
-          const uint64_t a_desc = tc::smem_desc_k_sw128(smem_u32(smem + s * L::kWBytes));
-          const uint64_t b_desc = tc::smem_desc_k_sw128(smem_u32(smem + L::kWRingBytes + xs * L::kXBytes));
+          const uint32_t a_lo = w_field0 + w_s * (L::kWBytes >> 4);
+          const uint32_t b_lo = x_field0 + x_s * (L::kXBytes >> 4);
+          if (!TCP_DBG(1)) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            // 16 bf16 = 32 bytes of K per instruction: advance the start addresses by 32 >> 4 = 2
-            tc::mma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kBK / 16; ++k) {
+              // 16 bf16 = 32 bytes of K per instruction: the start-address fields advance by 32 >> 4 = 2
+              tc::mma_f16(d_tmem, tc::smem_desc_from_words(a_lo + 2 * k, desc_hi), tc::smem_desc_from_words(b_lo + 2 * k, desc_hi),
+                          idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
           }
-          tc::mma_commit(&empty_bar[s]);   // both rings' slots are free once these MMAs have read them
-          tc::mma_commit(&empty_x[xs]);
+#ifdef ZT_TCPROF
+          const long long tcp_c0 = clock64();
+          if (p.prof.base && it == 16) p.prof.base[((size_t)blockIdx.x * 4 + 3) * kTimelineSlots + 2] = tcp_c0;      // MMAs of block 16 issued
+          ++it;
+#endif
+          tc::mma_commit_addr(empty_w0 + w_s * 8);   // both rings' slots are free once these MMAs have read them
+          if (!TCP_DBG(2)) tc::mma_commit_addr(empty_x0 + x_s * 8);
+          TCP_ADD(mc_issue);
+#ifdef ZT_TCPROF
+          if (tcp_warm) mc_commit += clock64() - tcp_c0;
+#endif
+          if (++w_s == STAGES) {
+            w_s = 0;
+            w_ph ^= 1;
+          }
+          if (++x_s == XSTAGES) {
+            x_s = 0;
+            x_ph ^= 1;
+          }
         }
         tc::mma_commit(&tmem_full[buf]);
       }
+#ifdef ZT_TCPROF
+      if (p.prof.base) {
+        unsigned long long *o = p.prof.base + ((size_t)blockIdx.x * 4 + 1) * kTimelineSlots;
+        o[0] = clock64() - mc_total; o[1] = mc_fullx; o[2] = mc_fullw; o[3] = mc_issue; o[4] = mc_tmem; o[5] = mc_commit; o[6] = it - 8;
+      }
+#endif
     }
   } else if (kUseTeams && warp < 2 + kDqWarps) {
     // ---------------- dequantisation warps, four teams: a thread converts one weight row of a k-block ----------------
@@ -424,18 +537,29 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
     if (!staged) fetch(0, 0, nxt);
     uint32_t pit = 0;   // packed chunks walked so far (every team walks every chunk)
     bool ok = true;
+#ifdef ZT_TCPROF
+    long long tc_total = 0, tc_fullp = 0, tc_empty = 0, tc_conv = 0, tc_blocks = 0;
+    bool tcp_warm = false;
+#endif
     for (int local = 0; local < my_tiles; ++local) {
       const uint32_t it0 = (uint32_t)local * (uint32_t)num_kb;   // ring position of the tile's first k-block
       const uint32_t jt = (team - it0) & 3u;
       for (int chunk = 0; chunk < num_chunks; ++chunk, ++pit) {
+#ifdef ZT_TCPROF
+        if (pit == 2) { tcp_warm = true; tc_total = clock64(); }
+#endif
         Sc cur = nxt;
         if (!staged) {
           if (chunk + 1 < num_chunks) fetch(local, chunk + 1, nxt); else fetch(local + 1, 0, nxt);
         }
         const uint32_t ps = pit % PSTAGES;
-        if (ok && !tc::mbar_wait(&full_p[ps], (pit / PSTAGES) & 1)) {
-          tc::report_timeout(p.status, kStatusConvertTimeout);
-          ok = false;
+        {
+          TCP_T0();
+          if (ok && !TC_WAITN(&full_p[ps], (pit / PSTAGES) & 1)) {
+            tc::report_timeout(p.status, kStatusConvertTimeout);
+            ok = false;
+          }
+          TCP_ADD(tc_fullp);
         }
         if (staged && ok) {
           // groups are at least 128 k wide here, so both halves of a k-block share one; with two groups per chunk
@@ -450,11 +574,19 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
           const uint32_t it = it0 + (uint32_t)kb;
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (ok && !tc::mbar_wait(&empty_bar[s], ph ^ 1)) {
-            tc::report_timeout(p.status, kStatusConvertTimeout);
-            ok = false;
+          {
+            TCP_T0();
+            if (ok && !TC_WAITN(&empty_bar[s], ph ^ 1)) {
+              tc::report_timeout(p.status, kStatusConvertTimeout);
+              ok = false;
+            }
+            TCP_ADD(tc_empty);
           }
-          if (ok) {
+#ifdef ZT_TCPROF
+          if (p.prof.base && dw == 0 && lane == 0 && it == 20) p.prof.base[((size_t)blockIdx.x * 4 + 3) * kTimelineSlots + 3] = clock64();   // team saw stage of block 16 free
+#endif
+          TCP_T0();
+          if (ok && !TCP_DBG(4)) {
             // the row's 32 packed bytes of this k-block: 16-byte chunks 2 jt and 2 jt + 1 of the swizzled 128-byte row
             const unsigned char *prow = packed + ps * kChunkBytes + row * 128;
             const uint4 w0 = *reinterpret_cast<const uint4 *>(prow + (((2u * jt) ^ row_x) << 4));
@@ -505,11 +637,25 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
           }
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(&full_w[s]);
+#ifdef ZT_TCPROF
+          if (p.prof.base && dw == 0 && lane == 0 && it == 16) p.prof.base[((size_t)blockIdx.x * 4 + 3) * kTimelineSlots + 0] = clock64();   // W(16) announced
+          if (p.prof.base && dw == 0 && lane == 0 && it == 20) p.prof.base[((size_t)blockIdx.x * 4 + 3) * kTimelineSlots + 4] = clock64();   // W(20) announced
+#endif
+          TCP_ADD(tc_conv);
+#ifdef ZT_TCPROF
+          if (tcp_warm) ++tc_blocks;
+#endif
         }
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&empty_p[ps]);   // this warp is done with the chunk (or had nothing in it)
       }
     }
+#ifdef ZT_TCPROF
+    if (p.prof.base && dw == 0 && lane == 0) {
+      unsigned long long *o = p.prof.base + ((size_t)blockIdx.x * 4 + 0) * kTimelineSlots;
+      o[0] = clock64() - tc_total; o[1] = tc_fullp; o[2] = tc_empty; o[3] = tc_conv; o[4] = tc_blocks;
+    }
+#endif
   } else if (warp < 2 + kDqWarps) {
     // ---------------- dequantisation warps ----------------
     const int d = threadIdx.x - 64;                 // 0 .. 32 * kDqWarps - 1
@@ -663,7 +809,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
       const int m_end = ti.m0 + ti.rows;  // rows past the tile's valid rows belong to nobody (or to the next expert)
       const uint32_t buf = local & 1;
       const uint32_t use = (uint32_t)local >> 1;
-      if (ok && !tc::mbar_wait(&tmem_full[buf], use & 1)) {
+      if (ok && !TC_WAITN(&tmem_full[buf], use & 1)) {
         tc::report_timeout(p.status, kStatusEpilogueTimeout);
         ok = false;
       }
@@ -826,6 +972,13 @@ int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows,
   const long long tiles = (long long)(p.g_count ? max_row_tiles : p.m_tiles) * p.n_tiles * p.ksplit;
   const int sms = sm_count();
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));
+#ifdef ZT_TCPROF
+  p.prof = timeline_for_launch((int)grid.x * 4);
+  {
+    const char *e = getenv("ZENTORCH_B200_TCDBG");
+    p.dbg = e ? atoi(e) : 0;
+  }
+#endif
   if (asym) {
     auto kern = woq_tcgen05_kernel<BT, STAGES, XSTAGES, PSTAGES, true>;
     static PerDeviceOnce configured;

@@ -60,7 +60,10 @@ def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool =
     for src in sources:
         obj = OBJ_DIR / (src.stem + ".o")
         if force or not _newer(obj, [src, *headers]):
-            cmd = [_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if ptxas_info else []), "-c", src, "-o", obj]
+            # ZENTORCH_B200_NVCC_DEFINES: extra -D switches for a diagnostic build, e.g. "-DZT_TCPROF" compiles the
+            # per-role cycle counters of the tcgen05 weight-only kernel (read by `bench.py --profile woq_roles`)
+            extra = os.environ.get("ZENTORCH_B200_NVCC_DEFINES", "").split()
+            cmd = [_nvcc(), *NVCC_FLAGS, *extra, *(["-Xptxas", "-v"] if ptxas_info else []), "-c", src, "-o", obj]
             jobs.append(cmd)
     logs = []
     if jobs:
