@@ -783,6 +783,7 @@ def run_profile_case(name):
     elif name == "moe":
         pk = peaks()
         print(json.dumps(bench_moe_config(torch, _capi, dev, pk)))
+        return
     elif name == "woq_timeline":          # config 1 (small layer)
         print(json.dumps(woq_timeline(torch, _capi, lib, dev)))
         return

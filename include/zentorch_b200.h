@@ -79,6 +79,8 @@ typedef enum {
 /* An `algo` argument may carry a tile-width hint for the tcgen05 kernels in bits 8..23 (0 = choose);
  * tests and benchmarks use it to exercise every compiled tile shape. */
 #define ZT_ALGO_WITH_TILE(algo, tile_n) ((int32_t)(algo) | ((int32_t)(tile_n) << 8))
+/* Bit 24: the weight-only tcgen05 kernel with a single MMA issuer instead of two (tests compare the two forms). */
+#define ZT_ALGO_SINGLE_ISSUER (1 << 24)
 
 ZT_API const char *zt_last_error(void);
 ZT_API const char *zt_version(void);

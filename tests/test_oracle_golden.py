@@ -95,6 +95,19 @@ def test_static_qlinear_matches_reference_formula():
     assert {e for _, _, e in seen} == {"none", "relu", "sigmoid", "mul_add"}
 
 
+def test_u8_dynamic_rows_are_static_qlinear_rows():
+    """The per-token u8 mode (no reference counterpart) shares everything after the choice of a row's scale and
+    zero point with the static qlinear, whose arithmetic is pinned by the reference's formula above: feeding a
+    row's quantised bytes, scale and zero point to the static form gives the same fp32 row bit for bit."""
+    x, w, ws, b = make_int8_case(5, 192, 40, seed=3)
+    xf = x.float()
+    q, s, zp, acc, y = O.dynamic_qlinear(xf, w, ws, b, act_quant="u8_asym", return_parts=True)
+    for m in range(x.shape[0]):
+        row = O.static_qlinear(q[m:m + 1], w, s[m:m + 1].clone(), zp[m:m + 1].clone(), ws.reshape(-1).float(), None, b,
+                               output_dtype=torch.float32)
+        assert torch.equal(row, y[m:m + 1])
+
+
 def test_static_qlinear_error_messages():
     import pytest
     x, w = torch.zeros(2, 8), torch.zeros(4, 8, dtype=torch.int8)

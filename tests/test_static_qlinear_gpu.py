@@ -133,6 +133,25 @@ def test_post_ops(capi, post, name, out_kind, buf_dtype):
                  exact=(name != "sigmoid"))
 
 
+def test_u8_dynamic_rows_agree_with_the_static_form(capi):
+    """Ties the per-token u8 mode of the dynamic linear (an extension without a reference fixture) to the static
+    form, which is pinned by the reference's formula: a row's quantised bytes, scale and zero point from
+    zt_dynamic_quantize, fed to zt_static_qlinear, give the dynamic linear's row (the two epilogues differ only in
+    whether product and sum are fused: 1e-6 relative)."""
+    from _util import make_int8_case
+    x, w, ws, b = make_int8_case(6, 512, 96, seed=8)
+    xd, wd, wsd, bd = x.float().cuda(), w.cuda(), ws.reshape(-1).float().cuda(), b.float().cuda()
+    y = capi.dynamic_qlinear(xd, wd, wsd, bd, act_quant=capi.ZT_ACT_U8_ASYM)
+    q, s, zp = capi.dynamic_quantize(xd, capi.ZT_ACT_U8_ASYM)
+    for m in range(x.shape[0]):
+        row = capi.static_qlinear(q[m:m + 1].contiguous(), wd, s[m:m + 1].contiguous(), zp[m:m + 1].contiguous(), wsd, bd,
+                                  out_dtype=torch.float32)
+        assert torch.allclose(row, y[m:m + 1], rtol=1e-6, atol=1e-6 * float(y.abs().max()))
+        ref = O.static_qlinear(q[m:m + 1].cpu(), w, s[m:m + 1].cpu(), zp[m:m + 1].cpu(), ws.reshape(-1).float(), None,
+                               b.float(), output_dtype=torch.float32)
+        assert torch.equal(row.cpu(), ref)
+
+
 def test_strided_output(capi):
     """The .out operators write into views of wider buffers: rows ldy elements apart, the rest untouched."""
     m, k, n = 70, 256, 48

@@ -194,6 +194,24 @@ def test_tcgen05_kernel(capi, tile, asym, scale_dtype):
         assert (y.float() - ref.float()).abs().max() <= tight * max(1.0, float(ref.float().abs().max())), (m, k, n)
 
 
+@pytest.mark.parametrize("m,k,n", [(40, 128, 136), (33, 192, 128), (64, 4096, 256), (128, 1024, 384), (300, 2048, 200)])
+def test_tcgen05_one_and_two_issuers_agree(capi, m, k, n):
+    """The kernel's default form has two MMA issuers, each summing every other k-block into an accumulator of
+    its own (the epilogue adds them); the one-issuer form sums all k-blocks in order.  Both against the oracle,
+    and against each other to fp32 summation-order noise (K = 192: three k-blocks, the issuers swap parity from
+    tile to tile)."""
+    x, q, s, z, b = make_woq_case(m, k, n, 64, seed=k + n)
+    y2, packed = _run(capi, x, q, s, None, b, capi.ZT_ALGO_TCGEN05)
+    y1, _ = _run(capi, x, q, s, None, b, capi.ZT_ALGO_TCGEN05 | capi.ZT_ALGO_SINGLE_ISSUER)
+    ref = O.woq_linear(x, packed.t(), s, None, b)
+    assert_close_bf16(y2, ref, what=f"two issuers {m}x{k}x{n}")
+    assert_close_bf16(y1, ref, what=f"one issuer {m}x{k}x{n}")
+    # the two forms round one fp32 sum differently: at most one bf16 ulp apart, and mostly equal
+    d = (y1.float() - y2.float()).abs()
+    assert float(d.max()) <= 2 ** -7 * max(1.0, float(ref.float().abs().max()))
+    assert float((d == 0).float().mean()) > 0.9
+
+
 @pytest.mark.parametrize("name", sorted(["relu", "gelu_erf", "silu", "add", "mul_add", "add_add"]))
 def test_tcgen05_post_ops(capi, name):
     ops, nbuf = POST_CASES[name]

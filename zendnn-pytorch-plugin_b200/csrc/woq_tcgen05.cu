@@ -59,7 +59,10 @@ constexpr int kBK = 64;   // k per stage: 128 bytes of bf16
 constexpr int kDqWarps = 16;
 constexpr int kWPT = 32 / kDqWarps;   // packed words per dequantisation thread and k-block (4 with 8 warps, 2 with 16)
 constexpr int kEpiWarps = 4;
-constexpr int kThreads = 64 + 32 * (kDqWarps + kEpiWarps);
+constexpr int kAuxWarps = 2;        // second activation producer, second MMA issuer
+constexpr int kThreads = 64 + 32 * (kDqWarps + kEpiWarps + kAuxWarps);
+constexpr int kProducerB = 2 + kDqWarps + kEpiWarps;   // warp index
+constexpr int kIssuerB = kProducerB + 1;
 constexpr int kEpiRowStride = 36;  // floats; 144 bytes keeps 16-byte alignment and spreads banks
 constexpr int kChunkKB = 4;        // k-blocks per packed-weight chunk: 4 x 32 B = one 128-byte row
 constexpr int kChunkBytes = kBN * 128;
@@ -92,6 +95,7 @@ struct TcParams {
   // Scales (and zero points) staged in shared memory with every packed chunk: groups per chunk (1 or 2; 0 = the
   // conversion threads fetch them from global memory), log2 of the group size, groups per expert.
   int staged_gpc, gs_log2, groups;
+  int single_issuer;   // host side: launch the one-issuer form
 #ifdef ZT_TCPROF
   TimelineSink prof;   // 4 records of 8 counters per CTA: conversion team 0, MMA issuer, producer, epilogue warp 0
   int dbg;             // ZENTORCH_B200_TCDBG: 1 no MMA issue, 2 no activation loads, 4 no conversion arithmetic (timing only, results are garbage)
@@ -230,7 +234,12 @@ __global__ void __launch_bounds__(256) woq_splitk_reduce_kernel(const float *__r
 constexpr int kTeams = 4;                      // conversion teams (token tiles up to 128)
 constexpr int kTeamWarps = kDqWarps / kTeams;  // 4 warps = 128 threads = one weight row per thread
 
-template <int BT, int STAGES, int XSTAGES, int PSTAGES, bool ASYM>
+// NI = 2: two MMA issuers (and two activation producers) take alternate ring positions, each issuer summing its
+// k-blocks into an accumulator of its own; the epilogue adds the two.  One thread issuing a block's MMAs, its two
+// commits and waiting on its two barriers needs about a thousand cycles per block whatever the tile, which is
+// what paced the kernel with a single issuer.  The accumulators are double buffered when NI * 2 * BT columns fit
+// tensor memory (BT <= 128), single buffered otherwise.
+template <int BT, int STAGES, int XSTAGES, int PSTAGES, bool ASYM, int NI>
 __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                   const __grid_constant__ CUtensorMap tmap_w,
                                                                   const __grid_constant__ CUtensorMap tmap_s,
@@ -252,7 +261,15 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
   uint64_t *tmem_empty = tmem_full + 2;      // [2]
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
 
-  constexpr uint32_t kTmemCols = 2 * BT <= 32 ? 32 : 2 * BT <= 64 ? 64 : 2 * BT <= 128 ? 128 : 2 * BT <= 256 ? 256 : 512;
+  // With two issuers (and two activation producers) alternate ring positions belong to different threads.  A ring
+  // of even length keeps every slot with one thread, which then waits on the slot's barriers strictly in order;
+  // on an odd ring two threads would share a slot, one could reach its wait two phases ahead of the barrier,
+  // and an mbarrier parity wait that far ahead passes at once.
+  static_assert(NI == 1 || (STAGES % 2 == 0 && XSTAGES % 2 == 0), "two issuers need rings of even length");
+  constexpr int NBUF = (2 * NI * BT <= 512) ? 2 : 1;
+  static_assert(NBUF * NI * BT <= 512, "accumulators exceed tensor memory");
+  constexpr uint32_t kAccCols = NBUF * NI * BT;
+  constexpr uint32_t kTmemCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128 : kAccCols <= 256 ? 256 : 512;
   constexpr bool kUseTeams = (STAGES % kTeams == 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Programmatic dependent launch: packed weights and scales are read before the wait for the preceding
@@ -284,7 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
       tc::mbar_init(&empty_p[s], kDqWarps);
     }
     for (int b = 0; b < 2; ++b) {
-      tc::mbar_init(&tmem_full[b], 1);
+      tc::mbar_init(&tmem_full[b], NI);
       tc::mbar_init(&tmem_empty[b], kEpiWarps);
     }
     tc::mbar_fence_init();
@@ -357,6 +374,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
       }
       grid_dependency_wait();
       uint32_t x_s = 0, x_ph = 1;          // activation slot and the parity of its "free" barrier
+      uint32_t x_it = 0;                   // ring position (k-blocks of all tiles so far)
       int need_base = 0;                   // chunks of the tiles before this one
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, need_base += num_chunks) {
         const TileInfo t = decode_tile(p, tile, n_mt, BT);
@@ -376,19 +394,22 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
             TCP_ADD(pc_must);
           }
           if (TCP_DBG(2)) continue;
-          {
-            TCP_T0();
-            const bool got = TC_WAIT1(&empty_x[x_s], x_ph);
-            TCP_ADD(pc_emptyx);
-            if (!got) {
-              tc::report_timeout(p.status, kStatusProducerTimeout);
-              ok = false;
-              break;
+          if (NI == 1 || (x_it & 1u) == 0) {       // with two producers this one takes the even ring positions
+            {
+              TCP_T0();
+              const bool got = TC_WAIT1(&empty_x[x_s], x_ph);
+              TCP_ADD(pc_emptyx);
+              if (!got) {
+                tc::report_timeout(p.status, kStatusProducerTimeout);
+                ok = false;
+                break;
+              }
             }
+            const uint32_t bar = full_x0 + x_s * 8;
+            tc::mbar_expect_tx_addr(bar, L::kXBytes);
+            tc::tma_load_2d_addr(x0 + x_s * L::kXBytes, &tmap_x, bar, kx, t.m0);
           }
-          const uint32_t bar = full_x0 + x_s * 8;
-          tc::mbar_expect_tx_addr(bar, L::kXBytes);
-          tc::tma_load_2d_addr(x0 + x_s * L::kXBytes, &tmap_x, bar, kx, t.m0);
+          ++x_it;
           if (++x_s == XSTAGES) {
             x_s = 0;
             x_ph ^= 1;
@@ -403,11 +424,13 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
       }
 #endif
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    // The other thread that paces the pipeline: ring positions and phases as counters, descriptors put together
-    // from a constant high word and a start-address field that advances by a constant per stage.
+  } else if (warp == 1 || (NI == 2 && warp == kIssuerB)) {
+    // ---------------- MMA issuer(s) ----------------
+    // A thread that paces the pipeline: ring positions and phases as counters, descriptors put together from a
+    // constant high word and a start-address field that advances by a constant per stage.  With two issuers
+    // each takes every other ring position and accumulates into its own columns of tensor memory.
     if (lane == 0) {
+      const uint32_t which = warp == 1 ? 0u : 1u;
       constexpr uint32_t idesc = tc::instr_desc(1u, 1u, 1u, kBN, BT);  // f32 accumulate, bf16 x bf16
       bool ok = true;
       int local = 0;
@@ -422,10 +445,10 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
       const uint32_t x_field0 = desc_lo | ((smem_u32(smem + L::kWRingBytes) & 0x3FFFF) >> 4);
       const uint32_t full_x0 = smem_u32(full_x), empty_x0 = smem_u32(empty_x);
       const uint32_t full_w0 = smem_u32(full_w), empty_w0 = smem_u32(empty_bar);
-      uint32_t w_s = 0, w_ph = 0, x_s = 0, x_ph = 0;
+      uint32_t w_s = 0, w_ph = 0, x_s = 0, x_ph = 0, pos = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
-        const uint32_t buf = local & 1;
-        const uint32_t use = (uint32_t)local >> 1;
+        const uint32_t buf = (uint32_t)local % NBUF;
+        const uint32_t use = (uint32_t)local / NBUF;
         {
           TCP_T0();
           if (ok && !TC_WAIT1(&tmem_empty[buf], (use & 1) ^ 1)) {
@@ -435,52 +458,58 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
           TCP_ADD(mc_tmem);
         }
         tc::fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * BT;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const uint32_t d_tmem = tmem_base + (buf * NI + which) * BT;
+        bool first = true;                 // this issuer's first block of the tile overwrites its accumulator
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++pos) {
+          if (NI == 1 || (pos & 1u) == which) {
 #ifdef ZT_TCPROF
-          if (it == 8) { tcp_warm = true; mc_total = clock64(); }
+            if (it == 8) { tcp_warm = true; mc_total = clock64(); }
 #endif
-          bool got;
-          {
-            TCP_T0();
-            got = TCP_DBG(2) || tc::mbar_wait_addr(full_x0 + x_s * 8, x_ph);
-            TCP_ADD(mc_fullx);
-          }
-          {
-            TCP_T0();
-            got = got && tc::mbar_wait_addr(full_w0 + w_s * 8, w_ph);
-            TCP_ADD(mc_fullw);
-          }
-          if (!got) {
-            tc::report_timeout(p.status, kStatusMmaTimeout);
-            ok = false;
-            break;
-          }
-#ifdef ZT_TCPROF
-          if (p.prof.base && it == 16) p.prof.base[((size_t)blockIdx.x * 4 + 3) * kTimelineSlots + 1] = clock64();   // MMA issuer saw W(16)
-#endif
-          TCP_T0();
-          tc::fence_after_sync();
-          const uint32_t a_lo = w_field0 + w_s * (L::kWBytes >> 4);
-          const uint32_t b_lo = x_field0 + x_s * (L::kXBytes >> 4);
-          if (!TCP_DBG(1)) {
-#pragma unroll
-            for (int k = 0; k < kBK / 16; ++k) {
-              // 16 bf16 = 32 bytes of K per instruction: the start-address fields advance by 32 >> 4 = 2
-              tc::mma_f16(d_tmem, tc::smem_desc_from_words(a_lo + 2 * k, desc_hi), tc::smem_desc_from_words(b_lo + 2 * k, desc_hi),
-                          idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            bool got;
+            {
+              TCP_T0();
+              got = TCP_DBG(2) || tc::mbar_wait_addr(full_x0 + x_s * 8, x_ph);
+              TCP_ADD(mc_fullx);
             }
+            {
+              TCP_T0();
+              got = got && tc::mbar_wait_addr(full_w0 + w_s * 8, w_ph);
+              TCP_ADD(mc_fullw);
+            }
+            if (!got) {
+              tc::report_timeout(p.status, kStatusMmaTimeout);
+              ok = false;
+              break;
+            }
+#ifdef ZT_TCPROF
+            if (p.prof.base && which == 0 && it == 16) p.prof.base[((size_t)blockIdx.x * 4 + 3) * kTimelineSlots + 1] = clock64();   // MMA issuer saw W(16)
+#endif
+            TCP_T0();
+            tc::fence_after_sync();
+            const uint32_t a_lo = w_field0 + w_s * (L::kWBytes >> 4);
+            const uint32_t b_lo = x_field0 + x_s * (L::kXBytes >> 4);
+            if (!TCP_DBG(1)) {
+#pragma unroll
+              for (int k = 0; k < kBK / 16; ++k) {
+                // 16 bf16 = 32 bytes of K per instruction: the start-address fields advance by 32 >> 4 = 2
+                tc::mma_f16(d_tmem, tc::smem_desc_from_words(a_lo + 2 * k, desc_hi), tc::smem_desc_from_words(b_lo + 2 * k, desc_hi),
+                            idesc, (!first || k > 0) ? 1u : 0u);
+              }
+            }
+            first = false;
+#ifdef ZT_TCPROF
+            const long long tcp_c0 = clock64();
+            if (p.prof.base && which == 0 && it == 16) p.prof.base[((size_t)blockIdx.x * 4 + 3) * kTimelineSlots + 2] = tcp_c0;      // MMAs of block 16 issued
+#endif
+            tc::mma_commit_addr(empty_w0 + w_s * 8);   // both rings' slots are free once these MMAs have read them
+            if (!TCP_DBG(2)) tc::mma_commit_addr(empty_x0 + x_s * 8);
+            TCP_ADD(mc_issue);
+#ifdef ZT_TCPROF
+            if (tcp_warm) mc_commit += clock64() - tcp_c0;
+#endif
           }
 #ifdef ZT_TCPROF
-          const long long tcp_c0 = clock64();
-          if (p.prof.base && it == 16) p.prof.base[((size_t)blockIdx.x * 4 + 3) * kTimelineSlots + 2] = tcp_c0;      // MMAs of block 16 issued
           ++it;
-#endif
-          tc::mma_commit_addr(empty_w0 + w_s * 8);   // both rings' slots are free once these MMAs have read them
-          if (!TCP_DBG(2)) tc::mma_commit_addr(empty_x0 + x_s * 8);
-          TCP_ADD(mc_issue);
-#ifdef ZT_TCPROF
-          if (tcp_warm) mc_commit += clock64() - tcp_c0;
 #endif
           if (++w_s == STAGES) {
             w_s = 0;
@@ -491,14 +520,43 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
             x_ph ^= 1;
           }
         }
-        tc::mma_commit(&tmem_full[buf]);
+        tc::mma_commit(&tmem_full[buf]);     // one arrival per issuer
       }
 #ifdef ZT_TCPROF
-      if (p.prof.base) {
+      if (p.prof.base && which == 0) {
         unsigned long long *o = p.prof.base + ((size_t)blockIdx.x * 4 + 1) * kTimelineSlots;
-        o[0] = clock64() - mc_total; o[1] = mc_fullx; o[2] = mc_fullw; o[3] = mc_issue; o[4] = mc_tmem; o[5] = mc_commit; o[6] = it - 8;
+        o[0] = clock64() - mc_total; o[1] = mc_fullx; o[2] = mc_fullw; o[3] = mc_issue; o[4] = mc_tmem; o[5] = mc_commit; o[6] = (it - 8) / NI;
       }
 #endif
+    }
+  } else if (NI == 2 && warp == kProducerB) {
+    // ---------------- second activation producer: the odd ring positions ----------------
+    if (lane == 0) {
+      const uint32_t full_x0 = smem_u32(full_x), empty_x0 = smem_u32(empty_x);
+      const uint32_t x0 = smem_u32(smem + L::kWRingBytes);
+      grid_dependency_wait();
+      uint32_t x_s = 0, x_ph = 1, x_it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const TileInfo t = decode_tile(p, tile, n_mt, BT);
+        int kx = t.kb0 * kBK;
+        for (int kb = 0; kb < num_kb; ++kb, kx += kBK, ++x_it) {
+          if (x_it & 1u) {
+            if (!tc::mbar_wait_addr(empty_x0 + x_s * 8, x_ph)) {
+              tc::report_timeout(p.status, kStatusProducerTimeout);
+              ok = false;
+              break;
+            }
+            const uint32_t bar = full_x0 + x_s * 8;
+            tc::mbar_expect_tx_addr(bar, L::kXBytes);
+            tc::tma_load_2d_addr(x0 + x_s * L::kXBytes, &tmap_x, bar, kx, t.m0);
+          }
+          if (++x_s == XSTAGES) {
+            x_s = 0;
+            x_ph ^= 1;
+          }
+        }
+      }
     }
   } else if (kUseTeams && warp < 2 + kDqWarps) {
     // ---------------- dequantisation warps, four teams: a thread converts one weight row of a k-block ----------------
@@ -795,7 +853,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
         }
       }
     }
-  } else {
+  } else if (warp >= 2 + kDqWarps && warp < 2 + kDqWarps + kEpiWarps) {
     // ---------------- epilogue warps ----------------
     grid_dependency_wait();                // output, partial sums and post-op operands are shared with earlier work
     const int ew = warp - (2 + kDqWarps);  // 0..3
@@ -807,14 +865,14 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
       const TileInfo ti = decode_tile(p, tile, n_mt, BT);
       const int m0 = ti.m0, n0 = ti.n0;
       const int m_end = ti.m0 + ti.rows;  // rows past the tile's valid rows belong to nobody (or to the next expert)
-      const uint32_t buf = local & 1;
-      const uint32_t use = (uint32_t)local >> 1;
+      const uint32_t buf = (uint32_t)local % NBUF;
+      const uint32_t use = (uint32_t)local / NBUF;
       if (ok && !TC_WAITN(&tmem_full[buf], use & 1)) {
         tc::report_timeout(p.status, kStatusEpilogueTimeout);
         ok = false;
       }
       tc::fence_after_sync();
-      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BT;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * NI * BT;
       const int nq = n0 + quarter * 32;        // first output column of this warp
       // phase-2 mapping: lane -> (token row within a group of 4, four consecutive columns)
       const int sub_row = lane >> 3;
@@ -833,6 +891,13 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
         // phase 1: scratch[token j][column lane]
 #pragma unroll
         for (int j = 0; j < 32; ++j) scratch[j * kEpiRowStride + lane] = __uint_as_float(r[j]);
+        if (NI == 2) {
+          // the second issuer's accumulator: same lanes, BT columns further
+          tc::tmem_ld_32x32b_x32(t_row + BT + c, r);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) scratch[j * kEpiRowStride + lane] += __uint_as_float(r[j]);
+        }
         __syncwarp();
         // phase 2: rows of 32 columns, 4 token rows per pass
 #pragma unroll 1
@@ -929,7 +994,7 @@ int cached_map(CUtensorMap *out, const void *ptr, CUtensorMapDataType dt, uint64
   return ZT_SUCCESS;
 }
 
-template <int BT, int STAGES, int XSTAGES, int PSTAGES>
+template <int BT, int STAGES, int XSTAGES, int PSTAGES, int NI>
 int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows, int max_row_tiles, bool asym,
               cudaStream_t st) {
   using L = SmemLayout<BT, STAGES, XSTAGES, PSTAGES>;
@@ -979,29 +1044,42 @@ int launch_bt(const TcParams &p0, const void *x, int64_t x_rows, int64_t w_rows,
     p.dbg = e ? atoi(e) : 0;
   }
 #endif
-  if (asym) {
-    auto kern = woq_tcgen05_kernel<BT, STAGES, XSTAGES, PSTAGES, true>;
-    static PerDeviceOnce configured;
-    if (int rc_cfg = allow_dynamic_smem(configured, kern, L::kTotal)) return rc_cfg;
+  // every instantiation needs its own once-per-device attribute set-up
+  static PerDeviceOnce configured[2];
+  auto launch = [&](auto kern, int which) -> int {
+    if (int rc_cfg = allow_dynamic_smem(configured[which], kern, L::kTotal)) return rc_cfg;
     ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, ts, tz, p));
-  } else {
-    auto kern = woq_tcgen05_kernel<BT, STAGES, XSTAGES, PSTAGES, false>;
-    static PerDeviceOnce configured;
-    if (int rc_cfg = allow_dynamic_smem(configured, kern, L::kTotal)) return rc_cfg;
-    ZT_CUDA_OK(launch_overlapped(kern, grid, dim3(kThreads), (size_t)L::kTotal, st, tx, tw, ts, tz, p));
-  }
+    return ZT_SUCCESS;
+  };
+  rc = asym ? launch(woq_tcgen05_kernel<BT, STAGES, XSTAGES, PSTAGES, true, NI>, 0)
+            : launch(woq_tcgen05_kernel<BT, STAGES, XSTAGES, PSTAGES, false, NI>, 1);
+  if (rc != ZT_SUCCESS) return rc;
   return launch_status("woq_tcgen05_kernel");
 }
 
 int launch_any(int bt, const TcParams &p, const void *x, int64_t x_rows, int64_t w_rows, int max_row_tiles, bool asym,
                cudaStream_t st) {
-  switch (bt) {
-    // <token tile, converted-weight stages, activation slots, packed chunks>
-    case 32: return launch_bt<32, 4, 12, 5>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
-    case 64: return launch_bt<64, 4, 6, 5>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
-    case 128: return launch_bt<128, 4, 4, 4>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
-    case 256: return launch_bt<256, 4, 3, 2>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
-    default: break;
+  // two issuers need at least two k-blocks per work item; ZENTORCH_B200_WOQ_ISSUERS=1 keeps the single issuer
+  static const int forced_ni = [] { const char *e = getenv("ZENTORCH_B200_WOQ_ISSUERS"); return e ? atoi(e) : 0; }();
+  // 256-token tiles keep one issuer: two would leave room for two activation slots and one accumulator buffer
+  // only, which measured 13 - 40 % slower than three slots and double-buffered accumulators.
+  const bool two = forced_ni != 1 && !p.single_issuer && p.kps >= 2 && bt <= 128;
+  if (two) {
+    switch (bt) {
+      // <token tile, converted-weight stages, activation slots, packed chunks, issuers>; rings of even length
+      case 32: return launch_bt<32, 4, 12, 5, 2>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+      case 64: return launch_bt<64, 4, 6, 5, 2>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+      case 128: return launch_bt<128, 4, 4, 4, 2>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+      default: break;
+    }
+  } else {
+    switch (bt) {
+      case 32: return launch_bt<32, 4, 12, 5, 1>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+      case 64: return launch_bt<64, 4, 6, 5, 1>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+      case 128: return launch_bt<128, 4, 4, 4, 1>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+      case 256: return launch_bt<256, 4, 3, 2, 1>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+      default: break;
+    }
   }
   set_error("zt_woq_linear: unsupported token-tile width %d for the tcgen05 kernel", bt);
   return ZT_UNSUPPORTED;
@@ -1058,6 +1136,7 @@ int woq_tcgen05_launch(const zt_woq_linear_args_t &a, cudaStream_t st) {
   p.status = device_status_ptr();
   const bool asym = a.zeros != nullptr;
   int bt = (a.algo >> 8) & 0xffff;
+  p.single_issuer = (a.algo & ZT_ALGO_SINGLE_ISSUER) ? 1 : 0;
   p.ksplit = 1;
   p.kps = (int)(a.K / kBK);
   if (bt == 0) {

@@ -17,6 +17,7 @@ ZT_BF16, ZT_F32, ZT_U8, ZT_S8 = 0, 1, 2, 3
 ZT_MAX_POST_OPS = 4
 ZT_WOQ_COUNTER_BYTES = 16384
 ZT_ALGO_AUTO, ZT_ALGO_GENERIC, ZT_ALGO_SKINNY, ZT_ALGO_TCGEN05 = 0, 1, 2, 3
+ZT_ALGO_SINGLE_ISSUER = 1 << 24
 ZT_ACT_S8_SYM, ZT_ACT_U8_ASYM = 0, 1
 ZT_FLAG_WEIGHTS_VOLATILE = 1
 ZT_STATIC_SCRATCH_Q_BYTES, ZT_STATIC_SCRATCH_MAX_ROWS = 8 << 20, 16384
