@@ -59,10 +59,10 @@ constexpr int kBK = 64;   // k per stage: 128 bytes of bf16
 constexpr int kDqWarps = 16;
 constexpr int kWPT = 32 / kDqWarps;   // packed words per dequantisation thread and k-block (4 with 8 warps, 2 with 16)
 constexpr int kEpiWarps = 4;
-constexpr int kAuxWarps = 2;        // second activation producer, second MMA issuer
+constexpr int kAuxWarps = 2;        // packed-weight producer, second MMA issuer (24 warps leave 80 registers a thread)
 constexpr int kThreads = 64 + 32 * (kDqWarps + kEpiWarps + kAuxWarps);
-constexpr int kProducerB = 2 + kDqWarps + kEpiWarps;   // warp index
-constexpr int kIssuerB = kProducerB + 1;
+constexpr int kPackedProducer = 2 + kDqWarps + kEpiWarps;   // warp index
+constexpr int kIssuerB = kPackedProducer + 1;
 constexpr int kEpiRowStride = 36;  // floats; 144 bytes keeps 16-byte alignment and spreads banks
 constexpr int kChunkKB = 4;        // k-blocks per packed-weight chunk: 4 x 32 B = one 128-byte row
 constexpr int kChunkBytes = kBN * 128;
@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(256) woq_splitk_reduce_kernel(const float *__r
 constexpr int kTeams = 4;                      // conversion teams (token tiles up to 128)
 constexpr int kTeamWarps = kDqWarps / kTeams;  // 4 warps = 128 threads = one weight row per thread
 
-// NI = 2: two MMA issuers (and two activation producers) take alternate ring positions, each issuer summing its
+// NI = 2: two MMA issuers take alternate ring positions, each issuer summing its
 // k-blocks into an accumulator of its own; the epilogue adds the two.  One thread issuing a block's MMAs, its two
 // commits and waiting on its two barriers needs about a thousand cycles per block whatever the tile, which is
 // what paced the kernel with a single issuer.  The accumulators are double buffered when NI * 2 * BT columns fit
@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
   uint64_t *tmem_empty = tmem_full + 2;      // [2]
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
 
-  // With two issuers (and two activation producers) alternate ring positions belong to different threads.  A ring
+  // With two issuers alternate ring positions belong to different threads.  A ring
   // of even length keeps every slot with one thread, which then waits on the slot's barriers strictly in order;
   // on an odd ring two threads would share a slot, one could reach its wait two phases ahead of the barrier,
   // and an mbarrier parity wait that far ahead passes at once.
@@ -313,91 +313,68 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
   const uint32_t tmem_base = *tmem_slot;
   grid_launch_dependents();
 
-  if (warp == 0) {
-    // ---------------- TMA producer: packed-weight chunks (running ahead) and activation tiles ----------------
-    // One thread paces the whole pipeline together with the MMA issuer, so its loop keeps ring positions and
-    // phases as counters and works on shared-window addresses computed once (no divisions, no generic-to-shared
-    // conversions per k-block).
+  if (warp == kPackedProducer) {
+    // ---------------- TMA producer of the packed-weight chunks (with their scales / zero points) ----------------
+    // Weights are constants: this thread never waits for the preceding kernel, it runs as far ahead as its ring
+    // allows.  It has a thread of its own because every bulk-copy or barrier instruction costs the issuing thread
+    // a few hundred cycles, and the activation producers are on the pipeline's critical path.
     if (lane == 0) {
+      const uint32_t full_p0 = smem_u32(full_p), empty_p0 = smem_u32(empty_p);
+      const uint32_t packed0 = smem_u32(packed), sc0 = smem_u32(sc_ring);
+      const uint32_t chunk_tx = kChunkBytes + (ASYM ? 2u : 1u) * (uint32_t)p.staged_gpc * kBN * (p.scale_dtype == ZT_F32 ? 4u : 2u);
+      uint32_t p_s = 0, p_ph = 1;          // ring slot and the parity of its "free" barrier
       bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const TileInfo pt = decode_tile(p, tile, n_mt, BT);
+        const int row = pt.expert * p.N + pt.n0;     // rows of the stacked weight: expert * N + n0
+        for (int pchunk = 0; pchunk < num_chunks; ++pchunk) {
+          if (!tc::mbar_wait_addr(empty_p0 + p_s * 8, p_ph)) {
+            tc::report_timeout(p.status, kStatusProducerTimeout);
+            ok = false;
+            break;
+          }
+          const int chunk = pt.kb0 / kChunkKB + pchunk;            // chunk of 256 k within K
+          const uint32_t bar = full_p0 + p_s * 8;
+          tc::mbar_expect_tx_addr(bar, chunk_tx);
+          tc::tma_load_2d_addr(packed0 + p_s * kChunkBytes, &tmap_w, bar, chunk * (kChunkKB * 8), row);   // 32 words per row
+          if (p.staged_gpc) {
+            // the chunk's groups x 128 columns of the scale table (rows = expert * groups + group)
+            const int g0 = pt.expert * p.groups + ((chunk * (kChunkKB * kBK)) >> p.gs_log2);
+            tc::tma_load_2d_addr(sc0 + p_s * kScaleSlotBytes, &tmap_s, bar, pt.n0, g0);
+            if (ASYM) tc::tma_load_2d_addr(sc0 + p_s * kScaleSlotBytes + kZeroSlotOffset, &tmap_z, bar, pt.n0, g0);
+          }
+          if (++p_s == PSTAGES) {
+            p_s = 0;
+            p_ph ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 0) {
+    // ---------------- TMA producer of the activation tiles ----------------
+    // Ring positions and phases as counters, shared-window addresses computed once.
+    if (lane == 0) {
+      const uint32_t which = 0u;
+      const uint32_t full_x0 = smem_u32(full_x), empty_x0 = smem_u32(empty_x);
+      const uint32_t x0 = smem_u32(smem + L::kWRingBytes);
 #ifdef ZT_TCPROF
       long long pc_total = 0, pc_emptyx = 0, pc_must = 0;
       bool tcp_warm = false;
-      uint32_t it = 0;
 #endif
-      const uint32_t full_p0 = smem_u32(full_p), empty_p0 = smem_u32(empty_p);
-      const uint32_t full_x0 = smem_u32(full_x), empty_x0 = smem_u32(empty_x);
-      const uint32_t packed0 = smem_u32(packed), sc0 = smem_u32(sc_ring), x0 = smem_u32(smem + L::kWRingBytes);
-      const uint32_t chunk_tx = kChunkBytes + (ASYM ? 2u : 1u) * (uint32_t)p.staged_gpc * kBN * (p.scale_dtype == ZT_F32 ? 4u : 2u);
-      // packed chunks: next chunk to issue = (ptile, pchunk); its tile's coordinates are decoded when the tile changes
-      int ptile = blockIdx.x, pchunk = 0;
-      uint32_t p_s = 0, p_ph = 1;          // ring slot and the parity of its "free" barrier
-      int issued = 0;                      // chunks issued so far
-      TileInfo pt = decode_tile(p, ptile < total_tiles ? ptile : 0, n_mt, BT);
-      auto issue_packed = [&](bool must) -> bool {
-        if (ptile >= total_tiles) return false;
-        if (must) {
-          if (!TC_WAIT1(&empty_p[p_s], p_ph)) {
-            tc::report_timeout(p.status, kStatusProducerTimeout);
-            ok = false;
-            return false;
-          }
-        } else if (!tc::mbar_test_addr(empty_p0 + p_s * 8, p_ph)) {
-          // test_wait returns at once: this thread has the activation tiles to request in the meantime
-          return false;
-        }
-        const int chunk = pt.kb0 / kChunkKB + pchunk;            // chunk of 256 k within K
-        const uint32_t bar = full_p0 + p_s * 8;
-        tc::mbar_expect_tx_addr(bar, chunk_tx);
-        // rows of the stacked weight: expert * N + n0 ; 32 words (four k-blocks) per row
-        tc::tma_load_2d_addr(packed0 + p_s * kChunkBytes, &tmap_w, bar, chunk * (kChunkKB * 8), pt.expert * p.N + pt.n0);
-        if (p.staged_gpc) {
-          // the chunk's groups x 128 columns of the scale table (rows = expert * groups + group)
-          const int g0 = pt.expert * p.groups + ((chunk * (kChunkKB * kBK)) >> p.gs_log2);
-          tc::tma_load_2d_addr(sc0 + p_s * kScaleSlotBytes, &tmap_s, bar, pt.n0, g0);
-          if (ASYM) tc::tma_load_2d_addr(sc0 + p_s * kScaleSlotBytes + kZeroSlotOffset, &tmap_z, bar, pt.n0, g0);
-        }
-        ++issued;
-        if (++p_s == PSTAGES) {
-          p_s = 0;
-          p_ph ^= 1;
-        }
-        if (++pchunk == num_chunks) {
-          pchunk = 0;
-          ptile += gridDim.x;
-          if (ptile < total_tiles) pt = decode_tile(p, ptile, n_mt, BT);
-        }
-        return true;
-      };
-      // the packed ring fills before the wait for the preceding kernel, the activation tiles follow it
-      while (issue_packed(false)) {
-      }
       grid_dependency_wait();
-      uint32_t x_s = 0, x_ph = 1;          // activation slot and the parity of its "free" barrier
-      uint32_t x_it = 0;                   // ring position (k-blocks of all tiles so far)
-      int need_base = 0;                   // chunks of the tiles before this one
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, need_base += num_chunks) {
+      uint32_t x_s = 0, x_ph = 1, x_it = 0;   // slot, parity of its "free" barrier, ring position
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const TileInfo t = decode_tile(p, tile, n_mt, BT);
         int kx = t.kb0 * kBK;
-        for (int kb = 0; kb < num_kb && ok; ++kb, kx += kBK) {
+        for (int kb = 0; kb < num_kb; ++kb, kx += kBK, ++x_it) {
 #ifdef ZT_TCPROF
-          if (it == 8) { tcp_warm = true; pc_total = clock64(); }
-          ++it;
+          if (x_it == 8) { tcp_warm = true; pc_total = clock64(); }
 #endif
-          // keep the packed ring full without blocking; the chunk this k-block needs must be issued
-          while (issue_packed(false)) {
-          }
-          {
-            TCP_T0();
-            const int need = need_base + (kb >> 2);
-            while (ok && issued <= need) issue_packed(true);
-            TCP_ADD(pc_must);
-          }
-          if (TCP_DBG(2)) continue;
-          if (NI == 1 || (x_it & 1u) == 0) {       // with two producers this one takes the even ring positions
+          if (!TCP_DBG(2)) {
             {
               TCP_T0();
-              const bool got = TC_WAIT1(&empty_x[x_s], x_ph);
+              const bool got = tc::mbar_wait_addr(empty_x0 + x_s * 8, x_ph);
               TCP_ADD(pc_emptyx);
               if (!got) {
                 tc::report_timeout(p.status, kStatusProducerTimeout);
@@ -409,18 +386,16 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
             tc::mbar_expect_tx_addr(bar, L::kXBytes);
             tc::tma_load_2d_addr(x0 + x_s * L::kXBytes, &tmap_x, bar, kx, t.m0);
           }
-          ++x_it;
           if (++x_s == XSTAGES) {
             x_s = 0;
             x_ph ^= 1;
           }
         }
       }
-      (void)empty_x0;
 #ifdef ZT_TCPROF
-      if (p.prof.base) {
+      if (p.prof.base && which == 0) {
         unsigned long long *o = p.prof.base + ((size_t)blockIdx.x * 4 + 2) * kTimelineSlots;
-        o[0] = clock64() - pc_total; o[1] = pc_emptyx; o[2] = pc_must; o[3] = it - 8;
+        o[0] = clock64() - pc_total; o[1] = pc_emptyx; o[2] = pc_must; o[3] = x_it - 8;
       }
 #endif
     }
@@ -528,35 +503,6 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
         o[0] = clock64() - mc_total; o[1] = mc_fullx; o[2] = mc_fullw; o[3] = mc_issue; o[4] = mc_tmem; o[5] = mc_commit; o[6] = (it - 8) / NI;
       }
 #endif
-    }
-  } else if (NI == 2 && warp == kProducerB) {
-    // ---------------- second activation producer: the odd ring positions ----------------
-    if (lane == 0) {
-      const uint32_t full_x0 = smem_u32(full_x), empty_x0 = smem_u32(empty_x);
-      const uint32_t x0 = smem_u32(smem + L::kWRingBytes);
-      grid_dependency_wait();
-      uint32_t x_s = 0, x_ph = 1, x_it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const TileInfo t = decode_tile(p, tile, n_mt, BT);
-        int kx = t.kb0 * kBK;
-        for (int kb = 0; kb < num_kb; ++kb, kx += kBK, ++x_it) {
-          if (x_it & 1u) {
-            if (!tc::mbar_wait_addr(empty_x0 + x_s * 8, x_ph)) {
-              tc::report_timeout(p.status, kStatusProducerTimeout);
-              ok = false;
-              break;
-            }
-            const uint32_t bar = full_x0 + x_s * 8;
-            tc::mbar_expect_tx_addr(bar, L::kXBytes);
-            tc::tma_load_2d_addr(x0 + x_s * L::kXBytes, &tmap_x, bar, kx, t.m0);
-          }
-          if (++x_s == XSTAGES) {
-            x_s = 0;
-            x_ph ^= 1;
-          }
-        }
-      }
     }
   } else if (kUseTeams && warp < 2 + kDqWarps) {
     // ---------------- dequantisation warps, four teams: a thread converts one weight row of a k-block ----------------
