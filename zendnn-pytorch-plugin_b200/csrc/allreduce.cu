@@ -11,6 +11,10 @@
 // computes the same sum in the same order, so the results are identical on all ranks.  One NVLink crossing
 // lies on the critical path.  No multimem, no TMA to or from peer memory, nothing but ld / st.
 //
+// Words travel two at a time (st.v2.u64: two 8-byte elements, each whole) and a slot is laid out in two planes,
+// plane j holding words 2j and 2j + 1 of every 16-byte input vector, so that the lanes of a warp write
+// consecutive 16-byte pieces: 512 contiguous bytes per store instruction instead of 32 scattered 8-byte ones.
+//
 // Work is cut into independent slices, one per CTA, so there is no grid-wide step.  Calls are numbered by an
 // epoch kept in this GPU's memory and advanced by the kernel itself (by the last CTA to finish, so that every
 // CTA of a launch reads the same number), which makes a captured launch replayable.  A word's number is that
@@ -39,14 +43,14 @@ struct ArParams {
   int *status;
 };
 
-// {data, call number} as one aligned 8-byte access
-__device__ __forceinline__ void st_word(uint2 *p, uint32_t data, uint32_t epoch) {
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(epoch) : "memory");
+// two {data, call number} words as one 16-byte access of two 8-byte elements
+__device__ __forceinline__ void st_pair(void *p, uint32_t d0, uint32_t d1, uint32_t epoch) {
+  const unsigned long long w0 = (unsigned long long)d0 | ((unsigned long long)epoch << 32);
+  const unsigned long long w1 = (unsigned long long)d1 | ((unsigned long long)epoch << 32);
+  asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(w0), "l"(w1) : "memory");
 }
-__device__ __forceinline__ uint2 ld_word(const uint2 *p) {
-  uint2 r;
-  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
-  return r;
+__device__ __forceinline__ void ld_pair(const void *p, unsigned long long &w0, unsigned long long &w1) {
+  asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(p) : "memory");
 }
 
 __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArParams p) {
@@ -62,39 +66,41 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArP
   const uint32_t epoch = p.epochs[0] + 1;                   // this call's number (own memory)
   const size_t buf_off = (size_t)(epoch & 1) * p.buf_bytes;
   const size_t my_slot = buf_off + (size_t)p.rank * p.slot_bytes;
+  const size_t plane = p.slot_bytes / 2;                    // bytes of one plane of a slot
   __syncthreads();
   bool ok = true;
   for (long long i = v0 + tid; i < v1; i += kArThreads) {
     const uint4 mine = p.in[i];
-    const uint32_t w[4] = {mine.x, mine.y, mine.z, mine.w};
-    // 1. push: four 8-byte words per 16 bytes of data into my slot of every peer's buffer
+    // 1. push: two 16-byte pieces per 16 bytes of data into my slot of every peer's buffer
 #pragma unroll
     for (int r = 0; r < ZT_AR_MAX_RANKS; ++r)
       if (r < p.world && r != p.rank) {
-        uint2 *dst = reinterpret_cast<uint2 *>(p.base[r] + my_slot) + 4 * i;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) st_word(dst + j, w[j], epoch);
+        unsigned char *dst = p.base[r] + my_slot + (size_t)i * 16;
+        st_pair(dst, mine.x, mine.y, epoch);
+        st_pair(dst + plane, mine.z, mine.w, epoch);
       }
-    // 2. collect: the same words of every peer's slot in my buffer, once they carry this call's number
+    // 2. collect: the same pieces of every peer's slot in my buffer, once they carry this call's number
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < ZT_AR_MAX_RANKS; ++r)
       if (r < p.world) {
-        uint32_t d[4] = {w[0], w[1], w[2], w[3]};
+        uint32_t d[4] = {mine.x, mine.y, mine.z, mine.w};
         if (r != p.rank) {
-          const uint2 *src = reinterpret_cast<const uint2 *>(p.base[p.rank] + buf_off + (size_t)r * p.slot_bytes) + 4 * i;
+          const unsigned char *src = p.base[p.rank] + buf_off + (size_t)r * p.slot_bytes + (size_t)i * 16;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint2 v = ld_word(src + j);
-            for (uint32_t spin = 0; v.y != epoch && ok; ++spin) {
+          for (int j = 0; j < 2; ++j) {
+            unsigned long long w0, w1;
+            ld_pair(src + j * plane, w0, w1);
+            for (uint32_t spin = 0; ((uint32_t)(w0 >> 32) != epoch || (uint32_t)(w1 >> 32) != epoch) && ok; ++spin) {
               if (spin >= tc::kSpinLimit) {
                 ok = false;
                 break;
               }
               if (spin > 64) __nanosleep(50);
-              v = ld_word(src + j);
+              ld_pair(src + j * plane, w0, w1);
             }
-            d[j] = v.x;
+            d[2 * j] = (uint32_t)w0;
+            d[2 * j + 1] = (uint32_t)w1;
           }
         }
         // 3. the sum, in rank order on every rank

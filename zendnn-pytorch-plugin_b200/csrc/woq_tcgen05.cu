@@ -266,6 +266,11 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
   // on an odd ring two threads would share a slot, one could reach its wait two phases ahead of the barrier,
   // and an mbarrier parity wait that far ahead passes at once.
   static_assert(NI == 1 || (STAGES % 2 == 0 && XSTAGES % 2 == 0), "two issuers need rings of even length");
+  // When the activation ring is as long as the converted-weight ring, a ring position is one stage: its "full"
+  // barrier counts the conversion team's warps and the activation producer (whose bulk copy adds the bytes), its
+  // "free" barrier is waited on by both.  The MMA issuer then waits once and commits once per k-block instead
+  // of twice -- barrier and tensor-core instructions are what a block's time is made of.
+  constexpr bool kUnified = (XSTAGES == STAGES);
   constexpr int NBUF = (2 * NI * BT <= 512) ? 2 : 1;
   static_assert(NBUF * NI * BT <= 512, "accumulators exceed tensor memory");
   constexpr uint32_t kAccCols = NBUF * NI * BT;
@@ -293,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
       tc::mbar_init(&empty_x[s], 1);
     }
     for (int s = 0; s < STAGES; ++s) {
-      tc::mbar_init(&full_w[s], kUseTeams ? kTeamWarps : kDqWarps);
+      tc::mbar_init(&full_w[s], (kUseTeams ? kTeamWarps : kDqWarps) + (kUnified ? 1 : 0));
       tc::mbar_init(&empty_bar[s], 1);
     }
     for (int s = 0; s < PSTAGES; ++s) {
@@ -355,7 +360,9 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
     // Ring positions and phases as counters, shared-window addresses computed once.
     if (lane == 0) {
       const uint32_t which = 0u;
-      const uint32_t full_x0 = smem_u32(full_x), empty_x0 = smem_u32(empty_x);
+      // unified stages: the activation tile is announced on, and its slot freed by, the stage's barriers
+      const uint32_t full_x0 = kUnified ? smem_u32(full_w) : smem_u32(full_x);
+      const uint32_t empty_x0 = kUnified ? smem_u32(empty_bar) : smem_u32(empty_x);
       const uint32_t x0 = smem_u32(smem + L::kWRingBytes);
 #ifdef ZT_TCPROF
       long long pc_total = 0, pc_emptyx = 0, pc_must = 0;
@@ -371,7 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
 #ifdef ZT_TCPROF
           if (x_it == 8) { tcp_warm = true; pc_total = clock64(); }
 #endif
-          if (!TCP_DBG(2)) {
+          if (kUnified || !TCP_DBG(2)) {      // (the no-activation-loads knob has no unified form)
             {
               TCP_T0();
               const bool got = tc::mbar_wait_addr(empty_x0 + x_s * 8, x_ph);
@@ -443,7 +450,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
             bool got;
             {
               TCP_T0();
-              got = TCP_DBG(2) || tc::mbar_wait_addr(full_x0 + x_s * 8, x_ph);
+              got = kUnified || TCP_DBG(2) || tc::mbar_wait_addr(full_x0 + x_s * 8, x_ph);
               TCP_ADD(mc_fullx);
             }
             {
@@ -477,7 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1) woq_tcgen05_kernel(const __grid_c
             if (p.prof.base && which == 0 && it == 16) p.prof.base[((size_t)blockIdx.x * 4 + 3) * kTimelineSlots + 2] = tcp_c0;      // MMAs of block 16 issued
 #endif
             tc::mma_commit_addr(empty_w0 + w_s * 8);   // both rings' slots are free once these MMAs have read them
-            if (!TCP_DBG(2)) tc::mma_commit_addr(empty_x0 + x_s * 8);
+            if (!kUnified && !TCP_DBG(2)) tc::mma_commit_addr(empty_x0 + x_s * 8);
             TCP_ADD(mc_issue);
 #ifdef ZT_TCPROF
             if (tcp_warm) mc_commit += clock64() - tcp_c0;
@@ -1013,15 +1020,15 @@ int launch_any(int bt, const TcParams &p, const void *x, int64_t x_rows, int64_t
   if (two) {
     switch (bt) {
       // <token tile, converted-weight stages, activation slots, packed chunks, issuers>; rings of even length
-      case 32: return launch_bt<32, 4, 12, 5, 2>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
-      case 64: return launch_bt<64, 4, 6, 5, 2>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+      case 32: return launch_bt<32, 4, 4, 5, 2>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+      case 64: return launch_bt<64, 4, 4, 5, 2>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
       case 128: return launch_bt<128, 4, 4, 4, 2>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
       default: break;
     }
   } else {
     switch (bt) {
-      case 32: return launch_bt<32, 4, 12, 5, 1>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
-      case 64: return launch_bt<64, 4, 6, 5, 1>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+      case 32: return launch_bt<32, 4, 4, 5, 1>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
+      case 64: return launch_bt<64, 4, 4, 5, 1>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
       case 128: return launch_bt<128, 4, 4, 4, 1>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
       case 256: return launch_bt<256, 4, 3, 2, 1>(p, x, x_rows, w_rows, max_row_tiles, asym, st);
       default: break;

@@ -182,8 +182,12 @@ class PeerAllReduce:
         self._args.epochs = self._epochs.data_ptr()
 
     def fits(self, t: torch.Tensor) -> bool:
-        return (t.dtype == torch.bfloat16 and t.is_contiguous() and t.numel() % 8 == 0
-                and t.numel() * 2 <= self.max_bytes and t.data_ptr() % 16 == 0)
+        """Every rank sends its whole tensor to every peer (twice the bytes: each word carries the call number), so
+        the one-shot form pays off while (world - 1) x bytes stays small; beyond 4 MB of that product the library's
+        bandwidth-optimal collective is the better choice."""
+        nbytes = t.numel() * 2
+        return (t.dtype == torch.bfloat16 and t.is_contiguous() and t.numel() % 8 == 0 and nbytes <= self.max_bytes
+                and (self.world - 1) * nbytes <= (4 << 20) and t.data_ptr() % 16 == 0)
 
     def __call__(self, t: torch.Tensor) -> torch.Tensor:
         a = self._args
