@@ -398,7 +398,11 @@ def bench_tp_layer(torch, dist, dev, stream, pk, world, rank, batches, kinds, re
     peer_ar = tp.PeerAllReduce(max_bytes=1 << 20, device=dev) if world > 1 and os.environ.get("ZENTORCH_B200_PEER_AR", "1") != "0" else None
     for kind in kinds:
         fulls = [make_layer_params(torch, _capi, dev, kind, LLAMA70B, seed0=100 * (s + 1)) for s in range(2)]
-        layers = [tp.DecoderLayerLinears(kind, f, rank, world, peer_allreduce=peer_ar) for f in fulls]
+        # ZENTORCH_B200_TP_OVERLAP_ROWS: smallest batch cut into two halves on two streams (0 = never; unset = the
+        # layer's own rule: from four ranks on, 2048 rows)
+        ov = os.environ.get("ZENTORCH_B200_TP_OVERLAP_ROWS")
+        layers = [tp.DecoderLayerLinears(kind, f, rank, world, peer_allreduce=peer_ar,
+                                         overlap_rows=None if ov is None else int(ov)) for f in fulls]
         ref_layer = tp.DecoderLayerLinears(kind, fulls[0], 0, 1) if world > 1 else None
         if world == 1:
             fulls = None      # the shards of a single rank are the parameters themselves

@@ -75,6 +75,27 @@ def _worker(rank, world, port, results):
             torch.cuda.synchronize()
             err = float((y1.float() - y2.float()).norm() / y2.float().norm())
             assert err < 1e-2, f"layer M={m}: peer all-reduce vs NCCL {err:.3e}"
+        # half batches on two streams (the form used for prefill sizes from four ranks on, forced here): the same
+        # rows through the same operators; a half batch may take another tile plan (K split over idle SMs) and the
+        # library may add in another order, so equal up to fp32 summation order; eagerly and replayed from a graph
+        split = tp.DecoderLayerLinears("woq", full, rank, world, overlap_rows=256)
+        m = 512
+        x = seeded_x(torch, dev, m, 4096, seed=5)
+        attn = seeded_x(torch, dev, m, 4096, seed=6)[:, rank * 4096 // world:(rank + 1) * 4096 // world].contiguous()
+        q0, y0 = with_nccl(x, attn)
+        q1, y1 = split(x, attn)
+        torch.cuda.synchronize()
+        def close(a, b):
+            return float((a.float() - b.float()).norm() / b.float().norm()) < 2e-3
+        assert close(q1, q0) and close(y1, y0)
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                q2, y2 = split(x, attn)
+            g.replay()
+            stream.synchronize()
+            assert torch.equal(y1, y2) and torch.equal(q1, q2)       # the graph replays the eager two-stream result
         assert _capi.poll_device_status() == 0
         results[rank] = "ok"
     except Exception as e:  # surface the failure in the parent

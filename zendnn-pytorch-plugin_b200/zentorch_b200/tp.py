@@ -234,9 +234,14 @@ class DecoderLayerLinears:
     Every step is plain launches on the current stream plus NCCL calls, so a whole step can be captured
     in a CUDA graph and replayed without host code between the kernels."""
 
-    def __init__(self, kind, full, rank=0, world=1, group=None, peer_allreduce=None):
+    def __init__(self, kind, full, rank=0, world=1, group=None, peer_allreduce=None, overlap_rows=None):
         self.kind, self.rank, self.world, self.group = kind, rank, world, group
         self.peer_allreduce = peer_allreduce     # a PeerAllReduce for the decode-size collectives, or None
+        # Batches of at least `overlap_rows` rows are cut into two halves that run on two streams, so that the
+        # library all-reduce of one half overlaps the GEMMs of the other (at eight ranks the two 64 MB
+        # all-reduces of a 4096-row batch take as long as its GEMMs).  None: from four ranks on, 2048 rows.
+        self.overlap_rows = overlap_rows if overlap_rows is not None else (2048 if world >= 4 else 0)
+        self._side = None
         shard = (lambda p, mode: shard_woq(*p, mode, rank, world)) if kind == "woq" else \
             (lambda p, mode: shard_int8(*p, mode, rank, world))
         fuse = fuse_woq_columns if kind == "woq" else fuse_int8_rows
@@ -257,13 +262,35 @@ class DecoderLayerLinears:
             dist.all_reduce(y, group=self.group)
         return y
 
-    def __call__(self, x, attn):
+    def _forward(self, x, attn):
         qkv = self._lin(x, self.qkv)
         o = self._reduce(self._lin(attn, self.o))
         gu = self._lin(o, self.gate_up)
         half = gu.shape[-1] // 2
         h = torch.nn.functional.silu(gu[..., :half]) * gu[..., half:]
         return qkv, self._reduce(self._lin(h, self.down))
+
+    def __call__(self, x, attn):
+        m = x.shape[0]
+        if self.world == 1 or not self.overlap_rows or m < self.overlap_rows or x.dim() != 2:
+            return self._forward(x, attn)
+        # two half batches on two streams; the collectives are issued in the same order on every rank (first
+        # half's, then second half's, per projection), which is all the library asks of one communicator used
+        # from several streams.  Works inside a stream capture: the side stream forks from and joins the
+        # capturing stream.
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=x.device)
+        main = torch.cuda.current_stream(x.device)
+        cut = (m // 2 + 127) // 128 * 128
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            qkv_b, down_b = self._forward(x[cut:], attn[cut:])
+        qkv_a, down_a = self._forward(x[:cut], attn[:cut])
+        main.wait_stream(self._side)
+        if not torch.cuda.is_current_stream_capturing():
+            for t in (qkv_b, down_b):
+                t.record_stream(main)
+        return torch.cat([qkv_a, qkv_b]), torch.cat([down_a, down_b])
 
     def weight_bytes(self):
         """Bytes of weights, scales and zero points this rank streams per step."""
