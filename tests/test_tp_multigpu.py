@@ -3,6 +3,7 @@ layer that uses it.  One child process per GPU (NCCL for the rendezvous and as t
 skipped on a box with a single GPU.  NVLS is switched off: the kernels under test use plain peer loads and
 stores, and a rank that dies while bound to a multicast object must not disturb its peers."""
 import os
+import time
 import sys
 from pathlib import Path
 
@@ -75,27 +76,6 @@ def _worker(rank, world, port, results):
             torch.cuda.synchronize()
             err = float((y1.float() - y2.float()).norm() / y2.float().norm())
             assert err < 1e-2, f"layer M={m}: peer all-reduce vs NCCL {err:.3e}"
-        # half batches on two streams (the form used for prefill sizes from four ranks on, forced here): the same
-        # rows through the same operators; a half batch may take another tile plan (K split over idle SMs) and the
-        # library may add in another order, so equal up to fp32 summation order; eagerly and replayed from a graph
-        split = tp.DecoderLayerLinears("woq", full, rank, world, overlap_rows=256)
-        m = 512
-        x = seeded_x(torch, dev, m, 4096, seed=5)
-        attn = seeded_x(torch, dev, m, 4096, seed=6)[:, rank * 4096 // world:(rank + 1) * 4096 // world].contiguous()
-        q0, y0 = with_nccl(x, attn)
-        q1, y1 = split(x, attn)
-        torch.cuda.synchronize()
-        def close(a, b):
-            return float((a.float() - b.float()).norm() / b.float().norm()) < 2e-3
-        assert close(q1, q0) and close(y1, y0)
-        stream = torch.cuda.Stream()
-        with torch.cuda.stream(stream):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                q2, y2 = split(x, attn)
-            g.replay()
-            stream.synchronize()
-            assert torch.equal(y1, y2) and torch.equal(q1, q2)       # the graph replays the eager two-stream result
         assert _capi.poll_device_status() == 0
         results[rank] = "ok"
     except Exception as e:  # surface the failure in the parent
@@ -111,5 +91,13 @@ def test_peer_allreduce_and_sharded_layer_two_ranks():
     port = 29600 + (os.getpid() % 2000)
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+    # bounded: ranks that wait for each other forever are killed (by their own process handles) and the test fails
+    ctx = mp.spawn(_worker, args=(world, port, results), nprocs=world, join=False)
+    deadline = time.time() + 300
+    while not ctx.join(timeout=5):
+        if time.time() > deadline:
+            for proc in ctx.processes:
+                if proc.is_alive():
+                    proc.kill()
+            pytest.fail(f"the ranks did not finish within 300 s: {dict(results)}")
     assert dict(results) == {0: "ok", 1: "ok"}, dict(results)

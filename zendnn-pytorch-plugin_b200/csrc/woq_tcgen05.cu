@@ -7,17 +7,19 @@
 // per k-block and reuses it for up to 256 tokens.  One persistent CTA per SM walks over
 // (128 columns) x (BT tokens) tiles; tiles that share a weight block are adjacent in the order.
 //
-//   warp 0        TMA producer (plain per-CTA loads): the activation tile of every k-block, and the packed
-//                 weights in chunks of four k-blocks (128 rows x 128 B, 128-byte swizzle) into a ring
-//                 of their own, several chunks ahead, so that enough weight bytes are in flight
+//   warp 0        TMA producer of the activation tiles (plain per-CTA loads)
 //   warp 1        TMEM allocation, tcgen05.mma.kind::f16 issue (bf16 x bf16 -> fp32), TMEM release
-//   warps 2..17   dequantisation (two packed words per thread and k-block): shared-memory loads of packed nibbles from the chunk ring
-//                 (the group's scale / zero point is prefetched from global memory), nibble -> bf16
-//                 with lop3, exact subtraction of the encoding bias, multiplication by the scale in
-//                 bf16x2 arithmetic, byte-permute into k order, 16-byte stores into the canonical
-//                 K-major 128-byte-swizzled operand layout, fence.proxy.async, mbarrier arrive
+//   warps 2..17   dequantisation in four teams (a thread converts one weight row of a k-block): shared-memory
+//                 loads of packed nibbles and of the group's scale / zero point from the chunk ring, nibble ->
+//                 bf16 with lop3, exact subtraction of the encoding bias, multiplication by the scale in bf16x2
+//                 arithmetic, byte-permute into k order, 16-byte stores into the canonical K-major
+//                 128-byte-swizzled operand layout, fence.proxy.async, mbarrier arrive
 //   warps 18..21  epilogue: tcgen05.ld (lane = output column n, register j = token), transpose
 //                 through shared memory so that stores run along n, bias + post-ops, bf16 stores
+//   warp 22       TMA producer of the packed weights in chunks of four k-blocks (128 rows x 128 B, 128-byte
+//                 swizzle) with their scales / zero points, into a ring of their own, several chunks ahead and
+//                 without ever waiting for the preceding kernel
+//   warp 23       second MMA issuer (token tiles up to 128): alternate ring positions, own accumulator
 //
 // Grouped mode (mixture-of-experts): the rows of X are sorted by expert, a device-side table lists the
 // row tiles {expert, first row, valid rows}, and each tile uses its expert's slice of the stacked

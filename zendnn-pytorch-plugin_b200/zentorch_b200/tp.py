@@ -237,10 +237,11 @@ class DecoderLayerLinears:
     def __init__(self, kind, full, rank=0, world=1, group=None, peer_allreduce=None, overlap_rows=None):
         self.kind, self.rank, self.world, self.group = kind, rank, world, group
         self.peer_allreduce = peer_allreduce     # a PeerAllReduce for the decode-size collectives, or None
-        # Batches of at least `overlap_rows` rows are cut into two halves that run on two streams, so that the
-        # library all-reduce of one half overlaps the GEMMs of the other (at eight ranks the two 64 MB
-        # all-reduces of a 4096-row batch take as long as its GEMMs).  None: from four ranks on, 2048 rows.
-        self.overlap_rows = overlap_rows if overlap_rows is not None else (2048 if world >= 4 else 0)
+        # Opt-in: batches of at least `overlap_rows` rows are cut into two halves that run on two streams, so that
+        # the library all-reduce of one half can overlap the GEMMs of the other.  Off by default (0 / None): at two
+        # ranks it measured 6 % slower, and it is never used while a stream capture is in progress (collectives of
+        # one communicator captured on two streams have no order between them in the graph).
+        self.overlap_rows = int(overlap_rows) if overlap_rows else 0
         self._side = None
         shard = (lambda p, mode: shard_woq(*p, mode, rank, world)) if kind == "woq" else \
             (lambda p, mode: shard_int8(*p, mode, rank, world))
@@ -272,12 +273,12 @@ class DecoderLayerLinears:
 
     def __call__(self, x, attn):
         m = x.shape[0]
-        if self.world == 1 or not self.overlap_rows or m < self.overlap_rows or x.dim() != 2:
+        if (self.world == 1 or not self.overlap_rows or m < self.overlap_rows or x.dim() != 2
+                or torch.cuda.is_current_stream_capturing()):
             return self._forward(x, attn)
-        # two half batches on two streams; the collectives are issued in the same order on every rank (first
-        # half's, then second half's, per projection), which is all the library asks of one communicator used
-        # from several streams.  Works inside a stream capture: the side stream forks from and joins the
-        # capturing stream.
+        # two half batches on two streams; the collectives are issued in the same order on every rank (second
+        # half's, then first half's), and outside a capture torch's process group runs them on its own stream in
+        # that order.
         if self._side is None:
             self._side = torch.cuda.Stream(device=x.device)
         main = torch.cuda.current_stream(x.device)
@@ -287,9 +288,8 @@ class DecoderLayerLinears:
             qkv_b, down_b = self._forward(x[cut:], attn[cut:])
         qkv_a, down_a = self._forward(x[:cut], attn[:cut])
         main.wait_stream(self._side)
-        if not torch.cuda.is_current_stream_capturing():
-            for t in (qkv_b, down_b):
-                t.record_stream(main)
+        for t in (qkv_b, down_b):
+            t.record_stream(main)
         return torch.cat([qkv_a, qkv_b]), torch.cat([down_a, down_b])
 
     def weight_bytes(self):
