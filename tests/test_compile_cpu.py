@@ -110,3 +110,91 @@ def test_gate_without_device(comp):
     comp.optimize(gm.graph)   # no sm_100 device here: the graph is left alone
     if not torch.cuda.is_available():
         assert torch.ops.aten.mm.default in _targets(gm)
+
+
+# ---- horizontal fusion of sibling weight-only linears (opt-in pass) ------------------------------------------
+class _OracleInterpreter(torch.fx.Interpreter):
+    """Runs an FX graph on CPU tensors with the zentorch operators evaluated by the CPU oracle."""
+
+    def call_function(self, target, args, kwargs):
+        import zentorch_oracle as O
+        if target == torch.ops.zentorch.zentorch_woq_repack_weight.default:
+            return O.woq_repack_weight(args[0])
+        if target == torch.ops.zentorch.zentorch_woq_linear.default:
+            x, w, s, z, b = (list(args) + [None] * 5)[:5]
+            return O.woq_linear(x, w, s, z, b)
+        return super().call_function(target, args, kwargs)
+
+
+def _qkv_graph(bias: bool, groups: int = 2):
+    g = torch.Generator().manual_seed(3)
+    k, ns = 128, (64, 32, 32)
+    x = torch.randn(5, k, generator=g).to(torch.bfloat16)
+    params = []
+    for n in ns:
+        q = torch.randint(-8, 8, (n, k), generator=g, dtype=torch.int8)
+        s = (torch.rand(groups, n, generator=g) * 0.05 + 0.01)
+        b = torch.randn(n, generator=g).to(torch.bfloat16) if bias else None
+        params += [q, s] + ([b] if bias else [])
+
+    def fn(x, *p):
+        step = 3 if bias else 2
+        outs = []
+        for i in range(3):
+            q, s = p[step * i], p[step * i + 1]
+            b = p[step * i + 2] if bias else None
+            w = torch.ops.zentorch.zentorch_woq_repack_weight(q).t()
+            outs.append(torch.ops.zentorch.zentorch_woq_linear(x, w, s, None, b))
+        return outs[0].float().sum(-1, keepdim=True) + outs[1].float().mean(-1, keepdim=True), outs[2] * 2
+
+    return fn, (x, *params)
+
+
+@pytest.mark.parametrize("bias", [False, True])
+def test_parallel_woq_linears_fuse_into_one(comp, bias):
+    fn, args = _qkv_graph(bias)
+    gm = _trace(fn, *args)
+    before = _OracleInterpreter(gm).run(*args)
+    assert _targets(gm).count(torch.ops.zentorch.zentorch_woq_linear.default) == 3
+    assert comp.fuse_parallel_woq_linears(gm.graph) == 1
+    gm.recompile()
+    t = _targets(gm)
+    assert t.count(torch.ops.zentorch.zentorch_woq_linear.default) == 1
+    assert comp.counters["zentorch"]["fused_parallel_woq_linear"] == 1
+    lin = next(n for n in gm.graph.nodes if n.target == torch.ops.zentorch.zentorch_woq_linear.default)
+    # the fused weight keeps the layout contract: [K/8, sum N] with strides (1, K/8); scales [groups, sum N]
+    assert tuple(lin.args[1].meta["val"].shape) == (16, 128) and tuple(lin.args[1].meta["val"].stride()) == (1, 16)
+    assert tuple(lin.args[2].meta["val"].shape) == (2, 128)
+    assert (lin.args[4] is None) == (not bias)
+    assert tuple(lin.meta["val"].shape) == (5, 128)
+    after = _OracleInterpreter(gm).run(*args)
+    for a, b in zip(before, after):
+        assert torch.equal(a, b)           # the same columns computed by the same arithmetic
+
+
+def test_parallel_woq_linears_left_alone_when_they_differ(comp):
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(3, 64, generator=g).to(torch.bfloat16)
+    q1 = torch.randint(-8, 8, (32, 64), generator=g, dtype=torch.int8)
+    q2 = torch.randint(0, 16, (32, 64), generator=g, dtype=torch.int8)
+    s1, s2 = torch.rand(1, 32, generator=g), torch.rand(2, 32, generator=g)
+    z2 = torch.rand(2, 32, generator=g)
+
+    def fn(x, q1, s1, q2, s2, z2):
+        a = torch.ops.zentorch.zentorch_woq_linear(x, torch.ops.zentorch.zentorch_woq_repack_weight(q1).t(), s1, None)
+        b = torch.ops.zentorch.zentorch_woq_linear(x, torch.ops.zentorch.zentorch_woq_repack_weight(q2).t(), s2, z2)
+        return a, b
+
+    gm = _trace(fn, x, q1, s1, q2, s2, z2)
+    assert comp.fuse_parallel_woq_linears(gm.graph) == 0      # different group counts and zero-point presence
+    assert _targets(gm).count(torch.ops.zentorch.zentorch_woq_linear.default) == 2
+
+    def chained(x, q1, s1):
+        w = torch.ops.zentorch.zentorch_woq_repack_weight(q1).t()
+        a = torch.ops.zentorch.zentorch_woq_linear(x, w, s1, None)
+        b = torch.ops.zentorch.zentorch_woq_linear(x, w, s1, None, a[0, :32].contiguous())   # bias from the sibling
+        return a, b
+
+    q3 = torch.randint(-8, 8, (64, 64), generator=g, dtype=torch.int8)
+    gm = _trace(chained, x, q3, torch.rand(1, 64, generator=g))
+    assert comp.fuse_parallel_woq_linears(gm.graph) == 0      # one depends on the other

@@ -219,6 +219,92 @@ def _register_all():
         _registered = True
 
 
+# ---- horizontal fusion of weight-only linears that share their input (q / k / v, gate / up) ------------------
+def _ancestors_include(node, targets, limit=64):
+    """True when one of `targets` is reachable upwards from `node` (bounded walk over parameter chains)."""
+    stack, seen = [node], set()
+    while stack and len(seen) < limit:
+        n = stack.pop()
+        if not isinstance(n, torch.fx.Node) or n in seen:
+            continue
+        if n in targets:
+            return True
+        seen.add(n)
+        stack.extend(a for a in n.all_input_nodes)
+    return False
+
+
+def _fake(target, args):
+    """meta["val"] of a new node, computed from its arguments' fake values."""
+    vals = torch.fx.node.map_arg(args, lambda n: n.meta["val"])
+    return target(*vals)
+
+
+def fuse_parallel_woq_linears(fx_graph: torch.fx.Graph) -> int:
+    """zentorch_woq_linear nodes with the same input (and no post-op, the same zero-point / bias presence, the
+    same group count and scale dtype) become one zentorch_woq_linear on concatenated parameters followed by
+    slices of its output: one launch instead of two or three, which is what a decode step is made of.  The
+    packed layout is N-major, so the fused weight is a row concatenation of the packed tensors
+    ([N_i, K/8] each) viewed back as [K/8, sum N_i]; scale and zero-point tables are concatenated along their
+    columns, biases along their only axis.
+
+    The concatenations are graph nodes: with frozen parameters (Inductor's freezing) they fold into
+    constants, otherwise they would run on every call and cost more than the launches they save, which is why
+    this pass is not part of `optimize()` and has to be asked for.  The reference fuses q / k / v of its bf16
+    linear the same way (src/cpu/python/zentorch/_custom_op_replacement.py:675-810: same input, exactly three
+    users, consistent bias and post-ops, `cat` of the weights, split of the output); this is that idea for
+    the weight-only operator, for any number of siblings.  Returns the number of fused groups."""
+    target = zt.zentorch_woq_linear.default
+    order = {n: i for i, n in enumerate(fx_graph.nodes)}
+    fused_groups = 0
+    for x in list(fx_graph.nodes):
+        group = [u for u in x.users if u.op == "call_function" and u.target == target and u.args[0] is x]
+        if len(group) < 2:
+            continue
+        group.sort(key=order.get)
+
+        def arg(n, i):
+            return n.args[i] if len(n.args) > i else None
+        vals = [(_val(arg(n, 1)), _val(arg(n, 2))) for n in group]
+        if any(w is None or sc is None for w, sc in vals):
+            continue
+        w0, s0 = vals[0]
+        same = all(w.shape[0] == w0.shape[0] and sc.shape[0] == s0.shape[0] and sc.dtype == s0.dtype for w, sc in vals)
+        same = same and len({arg(n, 3) is None for n in group}) == 1 and len({arg(n, 4) is None for n in group}) == 1
+        # parameters must not depend on a member of the group, and every consumer must come after the last member
+        members = set(group)
+        same = same and not any(_ancestors_include(a, members) for n in group for a in n.args[1:] if a is not None)
+        last = group[-1]
+        same = same and all(order[u] > order[last] for n in group for u in n.users)
+        if not same:
+            continue
+        with fx_graph.inserting_before(last):
+            def make(tgt, args):
+                node = fx_graph.call_function(tgt, args)
+                node.meta["val"] = _fake(tgt, args)
+                return node
+            rows = [make(aten.t.default, (arg(n, 1),)) for n in group]                  # [N_i, K/8] each
+            wf = make(aten.t.default, (make(aten.cat.default, (rows, 0)),))             # [K/8, sum N_i], strides (1, K/8)
+            sf = make(aten.cat.default, ([arg(n, 2) for n in group], 1))
+            zf = None if arg(group[0], 3) is None else make(aten.cat.default, ([arg(n, 3) for n in group], 1))
+            bf = None if arg(group[0], 4) is None else make(aten.cat.default, ([arg(n, 4) for n in group], 0))
+            fused = make(target, (x, wf, sf, zf, bf))
+            start = 0
+            for n in group:
+                width = _val(arg(n, 1)).shape[1]
+                piece = make(aten.slice.Tensor, (fused, -1, start, start + width))
+                n.replace_all_uses_with(piece)
+                start += width
+        for n in reversed(group):
+            fx_graph.erase_node(n)
+        counters["zentorch"]["fused_parallel_woq_linear"] += 1
+        fused_groups += 1
+    if fused_groups:
+        stable_topological_sort(fx_graph)
+        fx_graph.lint()
+    return fused_groups
+
+
 def device_gate() -> bool:
     """The replacement of the reference's AVX-512 gate (_optimize.py:87-91)."""
     from . import is_supported_device
