@@ -220,3 +220,49 @@ void zt_oracle_qlinear_epilogue(const int32_t *acc, int64_t m, int64_t n, const 
     }
   }
 }
+
+/* ---- static-quantisation qlinear (src/cpu/cpp/QLinear.cpp:66-366; float restatement the reference's tests
+ * compare with: test/unittests/quant_utils.py:13-83) ---------------------------------------------------- */
+
+/* q = clamp(rint(x * (1 / s)) + zp): unsigned 8 bit when is_u8 (zero point given), else signed with zp = 0. */
+void zt_oracle_static_quantize(const float *x, int64_t numel, float scale, int32_t zp, int is_u8, void *q) {
+  const float inv = 1.0f / scale;
+  const float lo = is_u8 ? 0.f : -128.f, hi = is_u8 ? 255.f : 127.f;
+  for (int64_t i = 0; i < numel; ++i) {
+    float r = nearbyintf(x[i] * inv) + (is_u8 ? (float)zp : 0.f);
+    r = r < lo ? lo : (r > hi ? hi : r);
+    if (is_u8)
+      ((uint8_t *)q)[i] = (uint8_t)(int)r;
+    else
+      ((int8_t *)q)[i] = (int8_t)(int)r;
+  }
+}
+
+/* v = post( acc' * (s_x * s_w[n]) + bias[n] ) with acc' = acc - zp_x * sum_k w[n,k]; then, when out_scale > 0,
+ * the requantised value clamp(rint(v * (1 / s_o)) + zp_o) in [0, 255] (out_is_u8) or [-128, 127], returned as
+ * float; else v itself.  w_scale has one element (w_per_tensor) or n.  post_id is one unary id or 0;
+ * mul / add (either may be NULL) are [m, n] operands applied as v * mul + add after it. */
+void zt_oracle_static_qlinear_epilogue(const int32_t *acc, int64_t m, int64_t n, float x_scale, int32_t x_zp,
+                                       const int32_t *wsum, const float *w_scale, int w_per_tensor,
+                                       const float *bias, int post_id, const float *mul, const float *add,
+                                       float out_scale, int32_t out_zp, int out_is_u8, float *y) {
+  const float inv_o = out_scale > 0.f ? 1.0f / out_scale : 0.f;
+  const float lo = out_is_u8 ? 0.f : -128.f, hi = out_is_u8 ? 255.f : 127.f;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < m; ++r) {
+    for (int64_t c = 0; c < n; ++c) {
+      int64_t a = acc[r * n + c];
+      if (wsum) a -= (int64_t)x_zp * (int64_t)wsum[c];
+      float v = (float)a * (x_scale * w_scale[w_per_tensor ? 0 : c]);
+      if (bias) v += bias[c];
+      v = post_op(v, post_id, 0.f);
+      if (mul) v *= mul[r * n + c];
+      if (add) v += add[r * n + c];
+      if (out_scale > 0.f) {
+        v = nearbyintf(v * inv_o) + (float)out_zp;
+        v = v < lo ? lo : (v > hi ? hi : v);
+      }
+      y[r * n + c] = v;
+    }
+  }
+}

@@ -2,7 +2,7 @@
 
 This module restates, on the CPU with plain torch/numpy arithmetic, what the reference
 operators ``zentorch_woq_linear`` (+ fused variants), ``zentorch_woq_repack_weight``,
-``zentorch_woq_repack_from_int4pack`` and ``zentorch_dynamic_qlinear`` compute.  Nothing in the
+``zentorch_woq_repack_from_int4pack``, ``zentorch_dynamic_qlinear`` and the ``zentorch_qlinear`` family compute.  Nothing in the
 shipped package imports it: only the tests, the smoke entry and the CPU-baseline leg of the
 benchmark do, and only as the checker.
 
@@ -19,6 +19,8 @@ formulas its own tests use as ground truth.  Pin status per function:
   ``test/unittests/model_tests/test_woq_linear.py:215-251``); formula ``dq = q * s[k // gs, n]``.
 * dynamic qlinear (symmetric s8) . pinned (formula of ``test/unittests/op_tests/test_dynamic_qlinear.py:32-36``
   and the integer restatement ``test/unittests/op_tests/test_group_matmul.py:394-409``).
+* static-quant qlinear family ..... pinned (the reference's own ``qdq_linear``,
+  ``test/unittests/quant_utils.py:13-83``, over input dtype x zero point x weight granularity x output dtype).
 * dynamic qlinear u8-asymmetric + fused post-op, int4 MoE, tensor-parallel shards: parity unpinned
   (no reference implementation); composed from the pinned pieces.
 """

@@ -233,3 +233,49 @@ def test_tp_shards_recompose():
             k0, k1 = r * 512 // world, (r + 1) * 512 // world
             rows.append(O.woq_linear(x[:, k0:k1].contiguous(), w_r, s_r, None, b_r, return_fp32=True))
         assert torch.allclose(sum(rows), full, rtol=1e-4, atol=1e-4)
+
+
+def test_c_oracle_static_qlinear_equals_python_and_golden(c_oracle):
+    """The C restatement of the static qlinear against the Python one on every golden case (float inputs are
+    quantised in C too), bit for bit; the Python one is pinned by the reference's qdq_linear above."""
+    lib = c_oracle
+    lib.zt_oracle_static_quantize.argtypes = [C.c_void_p, C.c_int64, C.c_float, C.c_int32, C.c_int, C.c_void_p]
+    lib.zt_oracle_static_qlinear_epilogue.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_int32,
+                                                      C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
+                                                      C.c_void_p, C.c_void_p, C.c_float, C.c_int32, C.c_int, C.c_void_p]
+    lib.zt_oracle_int8_gemm.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]
+    n_checked = 0
+    for c in qlinear_golden_cases():
+        x, w = c["x"], c["w"]
+        m, k, n = x.shape[0], x.shape[1], w.shape[0]
+        is_u8 = c["xzp"] is not None
+        xs, xzp = float(c["xs"]), (int(c["xzp"]) if is_u8 else 0)
+        if x.dtype in (torch.uint8, torch.int8):
+            q = x.contiguous()
+        else:
+            xf = x.float().contiguous()
+            q = torch.empty(m, k, dtype=torch.uint8 if is_u8 else torch.int8)
+            lib.zt_oracle_static_quantize(_ptr(xf), m * k, xs, xzp, int(is_u8), _ptr(q))
+        acc = torch.empty(m, n, dtype=torch.int32)
+        lib.zt_oracle_int8_gemm(_ptr(q), int(is_u8), _ptr(w), m, n, k, _ptr(acc))
+        wsum = w.sum(dim=1, dtype=torch.int32).contiguous()
+        ws = c["ws"].float().contiguous()
+        bias = c["bias"].float().contiguous()
+        unary = {"none": 0, "relu": O.POST_RELU, "sigmoid": O.POST_SIGMOID, "mul_add": 0}[c["eltwise"]]
+        mul, add = (c["buffers"][0].float().contiguous(), c["buffers"][1].float().contiguous()) if c["buffers"] else (None, None)
+        requant = c["os"] is not None
+        y = torch.empty(m, n)
+        lib.zt_oracle_static_qlinear_epilogue(
+            _ptr(acc), m, n, xs, xzp, _ptr(wsum) if is_u8 else None, _ptr(ws), int(ws.numel() == 1), _ptr(bias), unary,
+            _ptr(mul) if mul is not None else None, _ptr(add) if add is not None else None,
+            float(c["os"]) if requant else 0.0, int(c["ozp"]) if c["ozp"] is not None else 0,
+            int(c["out_dtype"] == torch.uint8), _ptr(y))
+        ref = O.static_qlinear(x, w, c["xs"], c["xzp"], c["ws"], None, c["bias"], c["os"], c["ozp"], c["out_dtype"],
+                               c["post"], c["buffers"])
+        got = y.to(c["out_dtype"])
+        if c["eltwise"] == "sigmoid":       # libm's and torch's exp differ in the last bits
+            assert_qlinear_close(got, ref, c["name"])
+        else:
+            assert torch.equal(got, ref), c["name"]
+        n_checked += 1
+    assert n_checked >= 48
