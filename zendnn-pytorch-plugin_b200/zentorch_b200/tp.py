@@ -234,8 +234,10 @@ class DecoderLayerLinears:
     Every step is plain launches on the current stream plus NCCL calls, so a whole step can be captured
     in a CUDA graph and replayed without host code between the kernels."""
 
-    def __init__(self, kind, full, rank=0, world=1, group=None, peer_allreduce=None, overlap_rows=None):
+    def __init__(self, kind, full, rank=0, world=1, group=None, peer_allreduce=None, overlap_rows=None,
+                 linear_fn=None):
         self.kind, self.rank, self.world, self.group = kind, rank, world, group
+        self.linear_fn = linear_fn               # replaces the CUDA op (CPU tests pass a checker here); None = the op
         self.peer_allreduce = peer_allreduce     # a PeerAllReduce for the decode-size collectives, or None
         # Opt-in: batches of at least `overlap_rows` rows are cut into two halves that run on two streams, so that
         # the library all-reduce of one half can overlap the GEMMs of the other.  Off by default (0 / None): at two
@@ -252,6 +254,8 @@ class DecoderLayerLinears:
         self.down = shard(full["down"], "row")
 
     def _lin(self, x, params):
+        if self.linear_fn is not None:
+            return self.linear_fn(x, *params)
         if self.kind == "woq":
             return torch.ops.zentorch.zentorch_woq_linear(x, *params)
         return torch.ops.zentorch.zentorch_dynamic_qlinear(x, *params)
@@ -273,7 +277,7 @@ class DecoderLayerLinears:
 
     def __call__(self, x, attn):
         m = x.shape[0]
-        if (self.world == 1 or not self.overlap_rows or m < self.overlap_rows or x.dim() != 2
+        if (self.world == 1 or not self.overlap_rows or m < self.overlap_rows or x.dim() != 2 or not x.is_cuda
                 or torch.cuda.is_current_stream_capturing()):
             return self._forward(x, attn)
         # two half batches on two streams; the collectives are issued in the same order on every rank (second
