@@ -126,3 +126,71 @@ def test_no_cpu_fallback(zt):
         torch.ops.zentorch.zentorch_woq_linear(x, w, torch.ones(1, 32), None, None)
     with pytest.raises((RuntimeError, NotImplementedError)):
         torch.ops.zentorch.zentorch_dynamic_qlinear(torch.zeros(2, 8), torch.zeros(4, 8, dtype=torch.int8), torch.ones(4), None)
+
+
+def test_static_qlinear_validation_schemas_and_meta(zt):
+    """The static-quantisation family on a box without a GPU: argument checks of the C entry point fail before any
+    device work with the reference's messages (src/cpu/cpp/QLinear.cpp:66-366), the schemas are the reference's
+    (QLinear.cpp:525-573), and the Meta kernels give the output shape and dtype rule."""
+    from zentorch_b200 import _capi
+    lib = _capi.lib()
+    one = C.c_void_p(16)  # never dereferenced: validation fails first
+    a = _capi.StaticQLinearArgs()
+    a.M, a.K, a.N, a.w_scales_numel, a.ldy = 2, 8, 4, 4, 4
+    a.x_dtype, a.y_dtype, a.post_buffer_dtype = 9, _capi.ZT_F32, _capi.ZT_F32
+    assert lib.zt_static_qlinear(C.byref(a), None) == 1
+    assert b"unsupported dtype for input tensor" in lib.zt_last_error()
+    a.x_dtype, a.y_dtype = _capi.ZT_F32, _capi.ZT_U8
+    assert lib.zt_static_qlinear(C.byref(a), None) == 1
+    assert b"only float32/bfloat16 is supported when output_scales are not defined" in lib.zt_last_error()
+    a.y_dtype, a.w_scales_numel = _capi.ZT_F32, 3
+    assert lib.zt_static_qlinear(C.byref(a), None) == 1
+    assert b"unsupported number of elements for weight_scales" in lib.zt_last_error()
+    a.w_scales_numel, a.x_dtype = 4, _capi.ZT_U8
+    assert lib.zt_static_qlinear(C.byref(a), None) == 1 and b"needs input_zero_points" in lib.zt_last_error()
+    a.x_dtype = _capi.ZT_F32
+    assert lib.zt_static_qlinear(C.byref(a), None) == 1 and b"null tensor pointer" in lib.zt_last_error()
+    a.x = a.x_scale = a.w = a.w_scales = a.y = one
+    a.x_zero_point = one
+    assert lib.zt_static_qlinear(C.byref(a), None) == 1 and b"need w_rowsum" in lib.zt_last_error()
+    a.x_zero_point, a.ldy = None, 3
+    assert lib.zt_static_qlinear(C.byref(a), None) == 1 and b"smaller than N" in lib.zt_last_error()
+    a.M = 0          # an empty batch succeeds without touching anything
+    assert lib.zt_static_qlinear(C.byref(a), None) == 0
+    assert lib.zt_static_quantize(None, _capi.ZT_F32, 0, None, None, None, None) == 0
+    assert lib.zt_static_quantize(None, _capi.ZT_F32, 4, None, None, None, None) == 1
+    assert lib.zt_static_qlinear_workspace_bytes(512, 4096, _capi.ZT_BF16) >= 512 * 4096
+    assert lib.zt_static_qlinear_workspace_bytes(512, 4096, _capi.ZT_U8) <= 256    # nothing to quantise
+
+    ops = torch.ops.zentorch
+    head = ("Tensor input, Tensor weight, Tensor input_scales, Tensor input_zero_points, Tensor weight_scales, "
+            "Tensor weight_zero_points, ")
+    tail = "Tensor? bias, Tensor? output_scales, Tensor? output_zero_points, ScalarType? output_dtype=None"
+    for name in ("zentorch_qlinear", "zentorch_qlinear_relu", "zentorch_qlinear_sigmoid"):
+        s = str(getattr(ops, name).default._schema)
+        assert head + tail in s and f'zentorch_op_name="zentorch::{name}"' in s
+    assert head + "Tensor mul_input, Tensor add_input, " + tail in str(ops.zentorch_qlinear_mul_add.default._schema)
+    for name in ("zentorch_qlinear", "zentorch_qlinear_relu"):
+        s = str(getattr(ops, name).out._schema)
+        assert "Tensor(a!) out, " + head + tail in s and s.endswith("-> ()")
+
+    x = torch.empty(3, 5, 64, device="meta")
+    w = torch.empty(48, 64, dtype=torch.int8, device="meta")
+    sc = torch.empty(1, device="meta")
+    zp = torch.empty(1, dtype=torch.int32, device="meta")
+    ws = torch.empty(48, device="meta")
+    wz = torch.empty(48, dtype=torch.int32, device="meta")
+    y = ops.zentorch_qlinear(x, w, sc, zp, ws, wz, None, None, None)
+    assert y.shape == (3, 5, 48) and y.dtype == torch.float32
+    y = ops.zentorch_qlinear(x, w, sc, zp, ws, wz, None, sc, zp, output_dtype=torch.uint8)
+    assert y.shape == (3, 5, 48) and y.dtype == torch.uint8
+    y = ops.zentorch_qlinear_relu(x.bfloat16(), w, sc, zp, ws, wz, None, None, None, output_dtype=torch.bfloat16)
+    assert y.dtype == torch.bfloat16
+    other = torch.empty(3, 5, 48, device="meta")
+    assert ops.zentorch_qlinear_mul_add(x, w, sc, zp, ws, wz, other, other, None, None, None).shape == (3, 5, 48)
+
+    # and no CPU kernel behind it
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        ops.zentorch_qlinear(torch.zeros(2, 8), torch.zeros(4, 8, dtype=torch.int8), torch.ones(1),
+                             torch.zeros(1, dtype=torch.int32), torch.ones(4), torch.zeros(4, dtype=torch.int32),
+                             None, None, None)
