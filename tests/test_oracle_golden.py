@@ -279,3 +279,41 @@ def test_c_oracle_static_qlinear_equals_python_and_golden(c_oracle):
             assert torch.equal(got, ref), c["name"]
         n_checked += 1
     assert n_checked >= 48
+
+
+def test_moe_oracle_equals_token_loop():
+    """The grouped-by-expert MoE oracle against a second, token-by-token statement of the same FFN built from the
+    raw int4 values and scales (no packing, no grouping): out[t] = sum_j w[t,j] * W2_e(silu(W1_e x) * W3_e x).
+    The reference has no int4 MoE to pin this on; the check is that grouping, slot weights and the gate-first
+    split of the fused w13 are consistent with the per-token definition, and that token order does not matter."""
+    g = torch.Generator().manual_seed(5)
+    t, h, inter, e, gs = 9, 128, 64, 4, 64
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16)
+    tw, ids = O.route_top2(torch.randn(t, e, generator=g))
+    assert torch.allclose(tw.sum(dim=1), torch.ones(t)) and (ids[:, 0] != ids[:, 1]).all()
+    w13q, s13, w2q, s2 = [], [], [], []
+    for _ in range(e):
+        q, s = O.quantize_woq_sym(torch.randn(2 * inter, h, generator=g) * 0.05, gs)
+        w13q.append(q), s13.append(s)
+        q, s = O.quantize_woq_sym(torch.randn(h, inter, generator=g) * 0.05, gs)
+        w2q.append(q), s2.append(s)
+    got = O.moe_woq(x, tw, ids, [O.woq_repack_weight(q).t() for q in w13q], s13,
+                    [O.woq_repack_weight(q).t() for q in w2q], s2)
+
+    def dense(q, s):                      # [N, K] int8, [K/gs, N] -> fp32 [N, K], rounded to bf16 like the op
+        w = q.float().view(q.shape[0], -1, gs) * s.t().unsqueeze(2)
+        return w.view(q.shape).to(torch.bfloat16).float()
+
+    want = torch.zeros(t, h)
+    for i in range(t):
+        for j in range(ids.shape[1]):
+            ex = int(ids[i, j])
+            hh = dense(w13q[ex], s13[ex]) @ x[i].float()
+            a = (torch.nn.functional.silu(hh[:inter]) * hh[inter:]).to(torch.bfloat16).float()
+            want[i] += tw[i, j] * (dense(w2q[ex], s2[ex]) @ a)
+    assert torch.allclose(got.float(), want, rtol=2e-2, atol=1e-3)
+
+    perm = torch.randperm(t, generator=g)
+    got_p = O.moe_woq(x[perm], tw[perm], ids[perm], [O.woq_repack_weight(q).t() for q in w13q], s13,
+                      [O.woq_repack_weight(q).t() for q in w2q], s2)
+    assert torch.equal(got_p, got[perm])
