@@ -317,3 +317,25 @@ def test_moe_oracle_equals_token_loop():
     got_p = O.moe_woq(x[perm], tw[perm], ids[perm], [O.woq_repack_weight(q).t() for q in w13q], s13,
                       [O.woq_repack_weight(q).t() for q in w2q], s2)
     assert torch.equal(got_p, got[perm])
+
+
+def test_c_oracle_quantisation_edge_rows(c_oracle):
+    """Rows the two restatements could round differently: all zero, constant of either sign, one huge outlier,
+    denormals, one-sided ranges.  Bytes, scales and zero points must agree bit for bit, and the u8 zero point of a
+    one-sided row sits at the matching end of the range."""
+    k = 64
+    x = torch.zeros(8, k)
+    x[1], x[2], x[4] = 3.0, -2.5, 1e-41
+    x[3, 5] = 1e30
+    x[5], x[6], x[7] = torch.linspace(-1, 1, k), torch.linspace(0, 5, k), torch.linspace(-5, -1, k)
+    q, s = O.dynamic_quantize_s8(x)
+    qc, sc = torch.empty_like(q), torch.empty_like(s)
+    c_oracle.zt_oracle_dynamic_quantize_s8(_ptr(x), 8, k, _ptr(qc), _ptr(sc))
+    assert torch.equal(q, qc) and torch.equal(s, sc)
+    assert (q[0] == 0).all() and (q[1] == 127).all() and (q[2] == -127).all() and int(q[3, 5]) == 127
+    qu, su, zp = O.dynamic_quantize_u8(x)
+    quc, suc, zpc = torch.empty_like(qu), torch.empty_like(su), torch.empty_like(zp)
+    c_oracle.zt_oracle_dynamic_quantize_u8(_ptr(x), 8, k, _ptr(quc), _ptr(suc), _ptr(zpc))
+    assert torch.equal(qu, quc) and torch.equal(su, suc) and torch.equal(zp, zpc)
+    assert zp.tolist() == [0, 0, 255, 0, 0, 127, 0, 255]
+    assert torch.isfinite(s).all() and torch.isfinite(su).all() and (s > 0).all() and (su > 0).all()
